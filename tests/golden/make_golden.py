@@ -1,0 +1,69 @@
+"""Writes tests/golden/reference_logits.safetensors: the logits of the reference's own Llama
+(fms.models.llama.LLaMA, loaded through its ``get_model(..., source="hf")`` path, float32, CPU) on the
+tiny random models of tests/tiny_models.py, for whole prompts and for prompt + cached one-token steps.
+
+Run once where the reference's sources are present:
+
+    python tests/golden/make_golden.py /path/to/foundation-model-stack
+
+The reference is not pip-installed there, and its ``fms/__init__.py`` asks importlib.metadata for the
+version of "ibm-fms"; only that lookup is patched.  Nothing of the reference is modified or copied.
+tests/test_plain_vs_golden.py compares the plain implementation with the stored file.
+"""
+import importlib.metadata as md
+import os
+import sys
+import tempfile
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(HERE))
+
+
+def main(reference_root: str):
+    os.environ["HF_HUB_OFFLINE"] = "1"
+    os.environ["TRANSFORMERS_OFFLINE"] = "1"
+    orig = md.version
+    md.version = lambda n: "0.0.0+ref" if n == "ibm-fms" else orig(n)
+    sys.path.insert(0, reference_root)
+    from fms.models import get_model
+    from safetensors.torch import save_file
+
+    from tiny_models import TINY, tiny_prompts, tiny_tensors, write_tiny
+
+    out = {}
+    for which in ("a", "b", "c"):
+        cfg, seed, gain_dtype = TINY[which]
+        folder = write_tiny(tempfile.mkdtemp(), which)
+        model = get_model("hf_pretrained", model_path=folder, data_type=torch.float32, device_type="cpu")
+        model.eval()
+        tensors = tiny_tensors(cfg, seed, gain_dtype)
+        out[f"{which}.weight_abs_sum"] = torch.stack(
+            [t.float().abs().sum() for _, t in sorted(tensors.items())]
+        ).sum().reshape(1).double()
+        for n, prompt in enumerate(tiny_prompts(which)):
+            ids = torch.tensor([prompt])
+            with torch.no_grad():
+                whole = model(ids)[0]
+                # the same prompt: all but the last 4 tokens at once, then one token per call from the cache
+                cut = max(1, len(prompt) - 4)
+                lg, cache = model(ids[:, :cut], use_cache=True)
+                parts = [lg[0]]
+                for t in range(cut, len(prompt)):
+                    lg, cache = model(ids[:, t : t + 1], past_key_value_states=cache, use_cache=True)
+                    parts.append(lg[0])
+                stepped = torch.cat(parts, 0)
+            assert (whole - stepped).abs().max() < 1e-4, (which, n, (whole - stepped).abs().max())
+            # stored: the first 4 and the last 12 positions (the file stays small)
+            sel = sorted(set(range(min(len(prompt), 4))) | set(range(max(0, len(prompt) - 12), len(prompt))))
+            out[f"{which}.{n}.ids"] = torch.tensor(prompt, dtype=torch.int32)
+            out[f"{which}.{n}.positions"] = torch.tensor(sel, dtype=torch.int32)
+            out[f"{which}.{n}.logits"] = whole[sel].float().contiguous()
+            print(which, n, len(prompt), "max|whole - stepped| =", (whole - stepped).abs().max().item())
+    save_file(out, os.path.join(HERE, "reference_logits.safetensors"))
+    print("wrote", os.path.join(HERE, "reference_logits.safetensors"))
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

@@ -1,0 +1,132 @@
+"""The tiny Llama configurations of the tests and a writer of model folders with random weights.
+
+The writer belongs to the tests (it does not use the library's own random-weights mode), so that the plain
+implementation and the stored reference outputs do not depend on the code under test.  The two
+configurations differ in every size and option: head counts and groups, head size, widths that are no
+power of two, number of layers, vocabulary, eps, rope theta, tied or untied head, context length and the
+dtype in which the norm gains are stored.
+"""
+from __future__ import annotations
+
+import json
+import os
+
+import torch
+
+TINY_A = {
+    "architectures": ["LlamaForCausalLM"],
+    "model_type": "llama",
+    "vocab_size": 256,
+    "hidden_size": 64,
+    "intermediate_size": 176,
+    "num_hidden_layers": 2,
+    "num_attention_heads": 4,
+    "num_key_value_heads": 2,
+    "rms_norm_eps": 1e-5,
+    "rope_theta": 10000.0,
+    "max_position_embeddings": 64,
+    "tie_word_embeddings": False,
+    "hidden_act": "silu",
+    "attention_bias": False,
+    "mlp_bias": False,
+}
+
+TINY_B = {
+    "architectures": ["LlamaForCausalLM"],
+    "model_type": "llama",
+    "vocab_size": 384,
+    "hidden_size": 96,
+    "intermediate_size": 256,
+    "num_hidden_layers": 3,
+    "num_attention_heads": 3,
+    "num_key_value_heads": 1,
+    "rms_norm_eps": 1e-6,
+    "rope_theta": 500000.0,
+    "max_position_embeddings": 128,
+    "tie_word_embeddings": True,
+    "hidden_act": "silu",
+    "attention_bias": False,
+    "mlp_bias": False,
+}
+
+# A third shape for long sequences: head size 48 (a multiple of 16 that is no power of two), 5 query
+# heads over 5 key/value heads, an odd vocabulary, a context of 1024.
+TINY_C = {
+    "architectures": ["LlamaForCausalLM"],
+    "model_type": "llama",
+    "vocab_size": 331,
+    "hidden_size": 240,
+    "intermediate_size": 328,
+    "num_hidden_layers": 2,
+    "num_attention_heads": 5,
+    "num_key_value_heads": 5,
+    "rms_norm_eps": 1e-5,
+    "rope_theta": 10000.0,
+    "max_position_embeddings": 1024,
+    "tie_word_embeddings": False,
+    "hidden_act": "silu",
+    "attention_bias": False,
+    "mlp_bias": False,
+}
+
+TINY = {"a": (TINY_A, 0, torch.bfloat16), "b": (TINY_B, 1, torch.float32), "c": (TINY_C, 2, torch.bfloat16)}
+
+
+def tiny_tensors(cfg: dict, seed: int, gain_dtype: torch.dtype = torch.bfloat16, matrix_std: float = 0.02):
+    """Linear and embedding weights ~ N(0, 0.02) rounded to bfloat16, norm gains 1 + U(-0.1, 0.1), drawn
+    in a fixed order from a CPU generator."""
+    g = torch.Generator(device="cpu")
+    g.manual_seed(seed)
+    d = cfg["hidden_size"]
+    h = cfg["num_attention_heads"]
+    kv = cfg["num_key_value_heads"]
+    hd = d // h
+    f = cfg["intermediate_size"]
+    v = cfg["vocab_size"]
+
+    def mat(rows, cols):
+        return (torch.randn(rows, cols, generator=g) * matrix_std).to(torch.bfloat16)
+
+    def gain(n):
+        return (1.0 + (torch.rand(n, generator=g) * 0.2 - 0.1)).to(gain_dtype)
+
+    t = {"model.embed_tokens.weight": mat(v, d)}
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        t[p + "input_layernorm.weight"] = gain(d)
+        t[p + "self_attn.q_proj.weight"] = mat(h * hd, d)
+        t[p + "self_attn.k_proj.weight"] = mat(kv * hd, d)
+        t[p + "self_attn.v_proj.weight"] = mat(kv * hd, d)
+        t[p + "self_attn.o_proj.weight"] = mat(d, h * hd)
+        t[p + "post_attention_layernorm.weight"] = gain(d)
+        t[p + "mlp.gate_proj.weight"] = mat(f, d)
+        t[p + "mlp.up_proj.weight"] = mat(f, d)
+        t[p + "mlp.down_proj.weight"] = mat(d, f)
+    t["model.norm.weight"] = gain(d)
+    if not cfg["tie_word_embeddings"]:
+        t["lm_head.weight"] = mat(v, d)
+    return t
+
+
+def write_folder(path: str, cfg: dict, tensors: dict) -> str:
+    from safetensors.torch import save_file
+
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w", encoding="utf-8") as fh:
+        json.dump(cfg, fh, indent=1)
+    save_file({k: v.contiguous() for k, v in tensors.items()}, os.path.join(path, "model.safetensors"))
+    return path
+
+
+def write_tiny(path: str, which: str) -> str:
+    cfg, seed, gain_dtype = TINY[which]
+    return write_folder(path, cfg, tiny_tensors(cfg, seed, gain_dtype))
+
+
+def tiny_prompts(which: str):
+    """Seeded prompts of unequal lengths with token ids uniform in [0, vocab)."""
+    cfg, seed, _ = TINY[which]
+    lengths = {"a": [5, 11, 17], "b": [1, 7, 30, 64], "c": [3, 70, 200]}[which]
+    g = torch.Generator(device="cpu")
+    g.manual_seed(1000 + seed)
+    return [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lengths]
