@@ -1,0 +1,186 @@
+// Memory-bound kernels of a decoder step: embedding rows, residual add + RMSNorm in one pass, gated
+// activation, and rotary position encoding fused with the write of keys and values into the block cache.
+// All arithmetic is float32; inputs and outputs are float32 or bfloat16.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------------------
+// embedding: out[t, :] = float(table[tokens[t], :])            (reference: fms/models/llama.py:332)
+// ---------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ out,
+                                  int dim, int vocab, int* __restrict__ error_flag) {
+  const int t = blockIdx.x;
+  const int tok = tokens[t];
+  const bool ok = tok >= 0 && tok < vocab;
+  if (!ok && threadIdx.x == 0 && error_flag) atomicExch(error_flag, 1);
+  const T* src = table + (size_t)(ok ? tok : 0) * dim;
+  float* dst = out + (size_t)t * dim;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = ok ? to_f32(src[d]) : 0.f;
+}
+
+FMS_API int fms_embed_rows(const void* table, int table_dtype, const int* tokens, float* out, int n_tokens, int dim,
+                           int vocab, int* error_flag, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (dim <= 0 || vocab <= 0) return fms_fail("embed_rows: dim %d, vocab %d", dim, vocab);
+  const int threads = dim >= 1024 ? 256 : 128;
+  FMS_DISPATCH_DTYPE(table_dtype, T,
+                     embed_rows_kernel<T><<<n_tokens, threads, 0, stream>>>((const T*)table, tokens, out, dim, vocab,
+                                                                            error_flag));
+  return fms_launch_status("embed_rows");
+}
+
+// ---------------------------------------------------------------------------------------------------
+// residual add + RMSNorm                                     (reference: fms/modules/layernorm.py:56-69)
+//   x = residual[src] + delta[src]       float32; written back to residual unless rows are gathered
+//   out[r] = gain * x * rsqrt(mean(x^2) + eps)
+// One thread block per output row; the row is read twice (the second time from cache).
+// ---------------------------------------------------------------------------------------------------
+template <typename T, typename TG>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                   const TG* __restrict__ gain, float eps, T* __restrict__ out,
+                                   const int* __restrict__ rows, int dim) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* res = residual + (size_t)src * dim;
+  const T* del = delta ? delta + (size_t)src * dim : nullptr;
+  float ss = 0.f;
+  if (rows == nullptr) {
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+      float x = res[d];
+      if (del) {
+        x += to_f32(del[d]);
+        res[d] = x;
+      }
+      ss += x * x;
+    }
+  } else {
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+      float x = res[d] + (del ? to_f32(del[d]) : 0.f);
+      ss += x * x;
+    }
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = rsqrtf(total / (float)dim + eps);
+  T* o = out + (size_t)r * dim;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    float x = res[d];
+    if (rows != nullptr && del) x += to_f32(del[d]);
+    o[d] = from_f32<T>(to_f32(gain[d]) * (x * inv));
+  }
+}
+
+FMS_API int fms_add_rmsnorm(float* residual, const void* delta, const void* gain, int gain_dtype, float eps, void* out,
+                            int dtype, const int* rows, int n_rows, int dim, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (dim <= 0) return fms_fail("add_rmsnorm: dim %d", dim);
+  const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
+  FMS_DISPATCH_DTYPE(dtype, T, FMS_DISPATCH_DTYPE(gain_dtype, TG,
+                     (add_rmsnorm_kernel<T, TG><<<n_rows, threads, 0, stream>>>(
+                         residual, (const T*)delta, (const TG*)gain, eps, (T*)out, rows, dim))));
+  return fms_launch_status("add_rmsnorm");
+}
+
+// ---------------------------------------------------------------------------------------------------
+// gated activation: out[n, f] = act(gu[n, f]) * gu[n, hidden + f]   (fms/modules/feedforward.py:291-292)
+// ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float activate(float g, int act) {
+  switch (act) {
+    case 0: return g / (1.f + expf(-g));                                               // silu
+    case 1: return 0.5f * g * (1.f + erff(g * 0.70710678118654752f));                  // gelu
+    case 2: return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));  // gelu-tanh
+    default: return fmaxf(g, 0.f);                                                     // relu
+  }
+}
+
+template <typename T>
+__global__ void gated_activation_kernel(const T* __restrict__ gu, T* __restrict__ out, int hidden, int act,
+                                        size_t total) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t n = i / hidden;
+    const int f = (int)(i - n * hidden);
+    const float g = to_f32(gu[n * 2 * hidden + f]);
+    const float u = to_f32(gu[n * 2 * hidden + hidden + f]);
+    out[i] = from_f32<T>(activate(g, act) * u);
+  }
+}
+
+FMS_API int fms_gated_activation(const void* gu, void* out, int dtype, int n_rows, int hidden, int act,
+                                 cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (hidden <= 0 || act < 0 || act > 3) return fms_fail("gated_activation: hidden %d, act %d", hidden, act);
+  const size_t total = (size_t)n_rows * hidden;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  FMS_DISPATCH_DTYPE(dtype, T,
+                     gated_activation_kernel<T><<<blocks, threads, 0, stream>>>((const T*)gu, (T*)out, hidden, act,
+                                                                                total));
+  return fms_launch_status("gated_activation");
+}
+
+// ---------------------------------------------------------------------------------------------------
+// rotary encoding + cache write
+//   qkv[t] = [q heads | k heads | v heads], each head `head_dim` wide     (fms/modules/attention.py:653-657)
+//   q, k: adjacent pairs (2i, 2i+1) rotated by angle = position * inv_freq[i], float32
+//                                                                    (fms/modules/positions.py:438-456)
+//   rotated q -> q_out[t]; rotated k and v -> the cache block of the token's slot and position
+// grid (token, head), one thread per pair.
+// ---------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float* __restrict__ inv_freq,
+                                  const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                  const int* __restrict__ slots, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                  const int* __restrict__ table, int table_stride, int block_tokens, int nheads,
+                                  int kvheads, int head_dim, int write_cache, int* __restrict__ error_flag) {
+  const int t = blockIdx.x;
+  const int head = blockIdx.y;  // 0..nheads-1: q; then k heads; then v heads
+  const int i = threadIdx.x;    // pair index
+  if (i >= head_dim / 2) return;
+  const int pos = positions[t];
+  const int width = (nheads + 2 * kvheads) * head_dim;
+  const T* src = qkv + (size_t)t * width + (size_t)head * head_dim;
+  float x0 = to_f32(src[2 * i]), x1 = to_f32(src[2 * i + 1]);
+  const bool is_v = head >= nheads + kvheads;
+  if (!is_v && inv_freq != nullptr) {
+    const float angle = (float)pos * inv_freq[i];
+    float s, c;
+    sincosf(angle, &s, &c);
+    const float r0 = c * x0 - s * x1;
+    const float r1 = s * x0 + c * x1;
+    x0 = r0;
+    x1 = r1;
+  }
+  if (head < nheads) {
+    T* dst = q_out + (size_t)t * nheads * head_dim + (size_t)head * head_dim;
+    dst[2 * i] = from_f32<T>(x0);
+    dst[2 * i + 1] = from_f32<T>(x1);
+    return;
+  }
+  if (!write_cache) return;
+  const int slot = slots[token_seq[t]];
+  const int blk = table[(size_t)slot * table_stride + pos / block_tokens];
+  if (blk < 0) {
+    if (i == 0 && error_flag) atomicExch(error_flag, 2);
+    return;
+  }
+  const int kvh = is_v ? head - nheads - kvheads : head - nheads;
+  T* base = is_v ? v_cache : k_cache;
+  T* dst = base + (((size_t)blk * kvheads + kvh) * block_tokens + (pos % block_tokens)) * head_dim;
+  dst[2 * i] = from_f32<T>(x0);
+  dst[2 * i + 1] = from_f32<T>(x1);
+}
+
+FMS_API int fms_rope_store(const void* qkv, int dtype, void* q_out, const float* inv_freq, const int* positions,
+                           const int* token_seq, const int* slots, void* k_cache, void* v_cache, const int* table,
+                           int table_stride, int block_tokens, int n_tokens, int nheads, int kvheads, int head_dim,
+                           int write_cache, int* error_flag, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (head_dim <= 0 || head_dim % 2 || head_dim > 2048) return fms_fail("rope_store: head_dim %d", head_dim);
+  dim3 grid(n_tokens, nheads + 2 * kvheads);
+  const int threads = ((head_dim / 2 + 31) / 32) * 32;
+  FMS_DISPATCH_DTYPE(dtype, T,
+                     rope_store_kernel<T><<<grid, threads, 0, stream>>>(
+                         (const T*)qkv, (T*)q_out, inv_freq, positions, token_seq, slots, (T*)k_cache, (T*)v_cache,
+                         table, table_stride, block_tokens, nheads, kvheads, head_dim, write_cache, error_flag));
+  return fms_launch_status("rope_store");
+}

@@ -1,0 +1,73 @@
+"""What an architecture is to the rest of the library.
+
+An architecture subclasses ``Model`` and says four things: how its ``config.json`` becomes its typed
+configuration, what layers that configuration means (a ``DecoderSpec``), which tensors its checkpoints
+hold (for random weights and for checks), and — through the adapter registry of ``fms_b200.weights`` —
+how checkpoint names map to the engine's.  Everything else (loading, cache, stepping, generation) is
+shared.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from ..config.specs import DecoderSpec
+from ..weights.loader import load_weights
+from ..weights.sources import TensorLayout
+
+
+class Model:
+    architecture = ""
+    default_source = "hf"
+
+    def __init__(self, config) -> None:
+        self.config = config
+        self.decoder = None
+        self.dtype: Optional[torch.dtype] = None
+        self.device: Optional[torch.device] = None
+        self._engine = None
+
+    # ---- what an architecture provides -------------------------------------------------------
+    @classmethod
+    def config_from_json(cls, values: dict):
+        raise NotImplementedError
+
+    def config_json(self) -> dict:
+        raise NotImplementedError
+
+    def decoder_spec(self) -> DecoderSpec:
+        raise NotImplementedError
+
+    def checkpoint_layout(self) -> List[TensorLayout]:
+        raise NotImplementedError
+
+    # ---- shared ------------------------------------------------------------------------------
+    def load(self, source, adapter_source: Optional[str], device, dtype: torch.dtype) -> "Model":
+        from ..engine.decoder import Decoder
+
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.decoder = Decoder(self.decoder_spec(), dtype)
+        load_weights(self.decoder, source, self.architecture, adapter_source or self.default_source, self.device,
+                     dtype, config=self.config)
+        return self
+
+    def state_dict(self):
+        return self.decoder.state_dict()
+
+    def new_engine(self, max_tokens: int, max_slots: Optional[int] = None):
+        from ..engine.step import Engine
+
+        return Engine(self, max_tokens=max_tokens, max_slots=max_slots)
+
+    def engine(self, min_tokens: int = 0, min_slots: int = 0):
+        """The model's own engine, made on first use and made anew when it is too small."""
+        e = self._engine
+        if e is None or e.cache.n_blocks * 64 < min_tokens or e.cache.max_slots < min_slots:
+            if e is not None and e.cache.slots.n_held:
+                raise RuntimeError("the engine is too small for this call and sequences are still live in it")
+            self._engine = None
+            del e
+            self._engine = self.new_engine(max(min_tokens, 64), max(min_slots, 1))
+        return self._engine
