@@ -1,0 +1,403 @@
+// Grouped-query causal softmax attention over the block cache, for one head size (HEAD_DIM, given at
+// compile time: the library is built once per head size a model needs), float32 and bfloat16 storage,
+// all arithmetic in float32 on the CUDA cores.  (fms/modules/attention.py:215-294 is the formula.)
+//
+//   prefill:  any number of new tokens per sequence; the query at position p sees cached positions
+//             max(0, p - window + 1)..p.  Keys and values of the new tokens are already in the cache.
+//   decode:   one query per sequence; the keys are cut into splits of 256 positions (a fixed size, so
+//             that a sequence's arithmetic depends on its own length only), one thread block per
+//             (sequence, key/value head, split), then a second kernel combines the splits.
+//
+// Cache layout: keys, values [blocks, kv_heads, 64, HEAD_DIM]; table[slot, p / 64] is the block of
+// position p.  Rows of a block beyond the sequence's length hold garbage and are never used: masked
+// scores are set to -inf by selection and their values are skipped or zeroed, not multiplied by 0.
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#error "compile with -DHEAD_DIM=<head size>"
+#endif
+static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "head size: a multiple of 16 up to 256");
+
+namespace {
+constexpr int HD = HEAD_DIM;
+constexpr int BLK = 64;           // tokens per cache block
+constexpr int SPLIT = 256;        // keys per decode split
+constexpr int GC = 8;             // query heads of one kv head handled by one decode block
+constexpr int TQ = 16;            // query rows per prefill block
+
+template <typename T> struct Vec;  // 16-byte vectors
+template <> struct Vec<float> { static constexpr int N = 4; };
+template <> struct Vec<__nv_bfloat16> { static constexpr int N = 8; };
+
+template <typename T> __device__ __forceinline__ void load_vec(const T* p, float* out);
+template <> __device__ __forceinline__ void load_vec<float>(const float* p, float* out) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+}
+template <> __device__ __forceinline__ void load_vec<__nv_bfloat16>(const __nv_bfloat16* p, float* out) {
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[2 * i] = __uint_as_float(w[i] << 16);
+    out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+struct AttnArgs {
+  const void* q;        // [tokens, nheads * HD]
+  void* out;            // [tokens, nheads * HD]
+  const void* keys;     // cache
+  const void* values;
+  const int* table;
+  int table_stride;
+  const int* slots;      // [seqs]
+  const int* first_row;  // [seqs + 1]
+  const int* len_after;  // [seqs]
+  int nheads, kvheads;
+  float scale;
+  int window;
+};
+
+// ---------------------------------------------------------------------------------------------------
+// prefill: grid (query tiles, heads), 128 threads; thread (r = tid / 8, c = tid % 8) owns row r of the
+// tile, scores of keys c, c+8, ... and output columns c, c+8, ...
+// ---------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a, const int* __restrict__ tiles) {
+  extern __shared__ float smem[];
+  float* qs = smem;                        // [TQ][HD + 1]
+  float* ks = qs + TQ * (HD + 1);          // [BLK][HD + 1]
+  float* vs = ks + BLK * (HD + 1);         // [BLK][HD]
+  float* ps = vs + BLK * HD;               // [TQ][BLK + 1]
+
+  const int tid = threadIdx.x, r = tid >> 3, c = tid & 7;
+  const int seq = tiles[2 * blockIdx.x], r0 = tiles[2 * blockIdx.x + 1];
+  const int head = blockIdx.y;
+  const int kvh = head / (a.nheads / a.kvheads);
+  const int row_begin = a.first_row[seq];
+  const int n_new = a.first_row[seq + 1] - row_begin;
+  const int len = a.len_after[seq];
+  const int len_before = len - n_new;
+  const int slot = a.slots[seq];
+  const int rows_here = min(TQ, n_new - r0);
+  const T* q = (const T*)a.q;
+  const T* kc = (const T*)a.keys;
+  const T* vc = (const T*)a.values;
+
+  for (int i = tid; i < TQ * HD; i += 128) {
+    const int rr = i / HD, d = i - rr * HD;
+    qs[rr * (HD + 1) + d] =
+        rr < rows_here ? to_f32(q[(size_t)(row_begin + r0 + rr) * a.nheads * HD + (size_t)head * HD + d]) : 0.f;
+  }
+  const int p_first = len_before + r0;
+  const int p_last = p_first + rows_here - 1;
+  const int my_pos = p_first + r;
+  const bool row_ok = r < rows_here;
+  const int kb_lo = a.window > 0 ? max(0, p_first - a.window + 1) / BLK : 0;
+  const int kb_hi = p_last / BLK;
+
+  float m = -INFINITY, l = 0.f;
+  float acc[HD / 8];
+#pragma unroll
+  for (int j = 0; j < HD / 8; ++j) acc[j] = 0.f;
+
+  for (int kb = kb_lo; kb <= kb_hi; ++kb) {
+    const int blk = a.table[(size_t)slot * a.table_stride + kb];
+    if (blk < 0) continue;  // uniform over the block: a block that left the window
+    __syncthreads();
+    const T* kbase = kc + ((size_t)blk * a.kvheads + kvh) * BLK * HD;
+    const T* vbase = vc + ((size_t)blk * a.kvheads + kvh) * BLK * HD;
+    constexpr int VN = Vec<T>::N;
+    for (int i = tid; i < BLK * HD / VN; i += 128) {
+      const int key = (i * VN) / HD, d = (i * VN) - key * HD;
+      const bool valid = kb * BLK + key < len;
+      float kv[VN], vv[VN];
+      if (valid) {
+        load_vec<T>(kbase + (size_t)key * HD + d, kv);
+        load_vec<T>(vbase + (size_t)key * HD + d, vv);
+      }
+#pragma unroll
+      for (int e = 0; e < VN; ++e) {
+        ks[key * (HD + 1) + d + e] = valid ? kv[e] : 0.f;
+        vs[key * HD + d + e] = valid ? vv[e] : 0.f;
+      }
+    }
+    __syncthreads();
+    float s[8];
+    float tile_max = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int key = c + 8 * i;
+      const int kpos = kb * BLK + key;
+      float dot = 0.f;
+      const float* qr = qs + r * (HD + 1);
+      const float* kr = ks + key * (HD + 1);
+#pragma unroll 8
+      for (int d = 0; d < HD; ++d) dot = fmaf(qr[d], kr[d], dot);
+      const bool visible = row_ok && kpos <= my_pos && (a.window <= 0 || kpos > my_pos - a.window);
+      s[i] = visible ? dot * a.scale : -INFINITY;
+      tile_max = fmaxf(tile_max, s[i]);
+    }
+    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 4));
+    const float m_new = fmaxf(m, tile_max);
+    const float m_use = m_new == -INFINITY ? 0.f : m_new;
+    const float alpha = m == -INFINITY ? 0.f : expf(m - m_use);
+    float psum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float p = s[i] == -INFINITY ? 0.f : expf(s[i] - m_use);
+      psum += p;
+      ps[r * (BLK + 1) + c + 8 * i] = p;
+    }
+    psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+    psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+    psum += __shfl_xor_sync(0xffffffffu, psum, 4);
+    l = l * alpha + psum;
+    m = m_new;
+    __syncwarp();  // the 8 threads of a row are in one warp; ps[r] is read only by them
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) acc[j] *= alpha;
+    const float* pr = ps + r * (BLK + 1);
+    for (int key = 0; key < BLK; ++key) {
+      const float p = pr[key];
+      const float* vr = vs + key * HD + c;
+#pragma unroll
+      for (int j = 0; j < HD / 8; ++j) acc[j] = fmaf(p, vr[8 * j], acc[j]);
+    }
+  }
+  if (row_ok) {
+    T* o = (T*)a.out + (size_t)(row_begin + r0 + r) * a.nheads * HD + (size_t)head * HD;
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) o[c + 8 * j] = from_f32<T>(acc[j] * inv);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// decode: grid (sequences, kv heads * head chunks, splits), 128 threads.  One block handles up to GC
+// query heads of one kv head over one split of the keys and writes an unnormalised partial result
+// (m, l, o) per head; attn_combine_kernel merges the splits.
+// ---------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, float* __restrict__ part_o,
+                                                          float* __restrict__ part_ml, int n_splits) {
+  constexpr int VN = Vec<T>::N;
+  constexpr int NCH = HD / VN;        // 16-byte chunks per row
+  constexpr int TPR = NCH;            // threads per value row
+  constexpr int RP = 128 / TPR;       // value rows in flight
+  __shared__ float qs[GC][HD];
+  __shared__ float ss[GC][BLK];
+  __shared__ float sm[GC], sl[GC], salpha[GC];
+  __shared__ float red[RP][GC][HD];
+
+  const int tid = threadIdx.x;
+  const int seq = blockIdx.x, split = blockIdx.z;
+  const int group = a.nheads / a.kvheads;
+  const int chunks = (group + GC - 1) / GC;
+  const int kvh = blockIdx.y / chunks, chunk = blockIdx.y - kvh * chunks;
+  const int g0 = chunk * GC;
+  const int ng = min(GC, group - g0);   // heads handled here
+  const int len = a.len_after[seq];
+  const int pos = len - 1;              // the query's position
+  const int kstart = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int k_lo = max(kstart, split * SPLIT), k_hi = min(len, (split + 1) * SPLIT);
+  if (k_lo >= k_hi) return;
+  const int slot = a.slots[seq];
+  const int row = a.first_row[seq];
+  const T* q = (const T*)a.q + (size_t)row * a.nheads * HD + (size_t)(kvh * group + g0) * HD;
+  const T* kc = (const T*)a.keys;
+  const T* vc = (const T*)a.values;
+
+  for (int i = tid; i < GC * HD; i += 128) {
+    const int g = i / HD, d = i - g * HD;
+    qs[g][d] = g < ng ? to_f32(q[(size_t)g * HD + d]) * a.scale : 0.f;
+  }
+  if (tid < GC) { sm[tid] = -INFINITY; sl[tid] = 0.f; salpha[tid] = 0.f; }
+  float acc[GC][VN];
+#pragma unroll
+  for (int g = 0; g < GC; ++g)
+#pragma unroll
+    for (int e = 0; e < VN; ++e) acc[g][e] = 0.f;
+  __syncthreads();
+
+  const int key_of = tid >> 1, half = tid & 1;     // phase 1: two threads per key
+  const int rg = tid / TPR, cv = tid - rg * TPR;   // phase 3: TPR threads per value row
+  const int warp = tid >> 5, lane = tid & 31;
+
+  for (int kb = k_lo / BLK; kb * BLK < k_hi; ++kb) {
+    const int blk = a.table[(size_t)slot * a.table_stride + kb];
+    if (blk < 0) continue;  // cannot happen for positions inside the window; skip rather than read
+    const T* kbase = kc + ((size_t)blk * a.kvheads + kvh) * BLK * HD;
+    const T* vbase = vc + ((size_t)blk * a.kvheads + kvh) * BLK * HD;
+    // phase 1: scores
+    {
+      const int kpos = kb * BLK + key_of;
+      const bool valid = kpos >= k_lo && kpos < k_hi;
+      float dot[GC];
+#pragma unroll
+      for (int g = 0; g < GC; ++g) dot[g] = 0.f;
+      if (valid) {
+        for (int ch = half; ch < NCH; ch += 2) {
+          float kx[VN];
+          load_vec<T>(kbase + (size_t)key_of * HD + ch * VN, kx);
+#pragma unroll
+          for (int g = 0; g < GC; ++g)
+#pragma unroll
+            for (int e = 0; e < VN; ++e) dot[g] = fmaf(kx[e], qs[g][ch * VN + e], dot[g]);
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < GC; ++g) {
+        const float other = __shfl_xor_sync(0xffffffffu, dot[g], 1);
+        if (half == 0) ss[g][key_of] = valid ? dot[g] + other : -INFINITY;
+      }
+    }
+    __syncthreads();
+    // phase 2: running softmax per head; warp w takes heads w, w + 4
+    for (int g = warp; g < ng; g += 4) {
+      const float s0 = ss[g][lane], s1 = ss[g][lane + 32];
+      const float tile_max = warp_max(fmaxf(s0, s1));
+      const float m_old = sm[g];
+      const float m_new = fmaxf(m_old, tile_max);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float p0 = s0 == -INFINITY ? 0.f : expf(s0 - m_use);
+      const float p1 = s1 == -INFINITY ? 0.f : expf(s1 - m_use);
+      const float psum = warp_sum(p0 + p1);
+      ss[g][lane] = p0;
+      ss[g][lane + 32] = p1;
+      if (lane == 0) {
+        const float alpha = m_old == -INFINITY ? 0.f : expf(m_old - m_use);
+        salpha[g] = alpha;
+        sl[g] = sl[g] * alpha + psum;
+        sm[g] = m_new;
+      }
+    }
+    __syncthreads();
+    // phase 3: values
+    if (rg < RP) {
+#pragma unroll
+      for (int g = 0; g < GC; ++g) {
+        const float alpha = g < ng ? salpha[g] : 0.f;
+#pragma unroll
+        for (int e = 0; e < VN; ++e) acc[g][e] *= alpha;
+      }
+      for (int key = rg; key < BLK; key += RP) {
+        const int kpos = kb * BLK + key;
+        if (kpos < k_lo || kpos >= k_hi) continue;
+        float vx[VN];
+        load_vec<T>(vbase + (size_t)key * HD + cv * VN, vx);
+#pragma unroll
+        for (int g = 0; g < GC; ++g) {
+          const float p = ss[g][key];
+#pragma unroll
+          for (int e = 0; e < VN; ++e) acc[g][e] = fmaf(p, vx[e], acc[g][e]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  // sum the row groups in a fixed order and write the partial result
+  if (rg < RP) {
+#pragma unroll
+    for (int g = 0; g < GC; ++g)
+#pragma unroll
+      for (int e = 0; e < VN; ++e) red[rg][g][cv * VN + e] = acc[g][e];
+  }
+  __syncthreads();
+  for (int i = tid; i < ng * HD; i += 128) {
+    const int g = i / HD, d = i - g * HD;
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < RP; ++k) sum += red[k][g][d];
+    const int head = kvh * group + g0 + g;
+    part_o[(((size_t)seq * a.nheads + head) * n_splits + split) * HD + d] = sum;
+  }
+  if (tid < ng) {
+    const int head = kvh * group + g0 + tid;
+    float* ml = part_ml + (((size_t)seq * a.nheads + head) * n_splits + split) * 2;
+    ml[0] = sm[tid];
+    ml[1] = sl[tid];
+  }
+}
+
+template <typename T>
+__global__ void attn_combine_kernel(AttnArgs a, const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    int n_splits) {
+  const int seq = blockIdx.x, head = blockIdx.y;
+  const int len = a.len_after[seq];
+  const int pos = len - 1;
+  const int kstart = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int s_lo = kstart / SPLIT, s_hi = pos / SPLIT;
+  const float* ml = part_ml + ((size_t)seq * a.nheads + head) * n_splits * 2;
+  const float* po = part_o + ((size_t)seq * a.nheads + head) * n_splits * HD;
+  float m = -INFINITY;
+  for (int s = s_lo; s <= s_hi; ++s) m = fmaxf(m, ml[2 * s]);
+  float total = 0.f;
+  for (int s = s_lo; s <= s_hi; ++s) total += ml[2 * s + 1] * expf(ml[2 * s] - m);
+  const float inv = total > 0.f ? 1.f / total : 0.f;
+  T* o = (T*)a.out + (size_t)a.first_row[seq] * a.nheads * HD + (size_t)head * HD;
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float sum = 0.f;
+    for (int s = s_lo; s <= s_hi; ++s) sum += po[(size_t)s * HD + d] * expf(ml[2 * s] - m);
+    o[d] = from_f32<T>(sum * inv);
+  }
+}
+
+int check_args(const char* what, int nheads, int kvheads, int head_dim, int block_tokens) {
+  if (head_dim != HD) return fms_fail("%s: this library is built for head size %d, not %d", what, HD, head_dim);
+  if (block_tokens != BLK) return fms_fail("%s: cache blocks of %d tokens, %d expected", what, block_tokens, BLK);
+  if (nheads <= 0 || kvheads <= 0 || nheads % kvheads) return fms_fail("%s: %d heads over %d kv heads", what, nheads, kvheads);
+  return 0;
+}
+}  // namespace
+
+FMS_API int fms_attn_head_dim() { return HD; }
+FMS_API int fms_attn_split_tokens() { return SPLIT; }
+FMS_API int fms_attn_prefill_tile_rows() { return TQ; }
+
+FMS_API int fms_attention_prefill(const void* q, void* out, int dtype, const void* keys, const void* values,
+                                  const int* table, int table_stride, int block_tokens, const int* slots,
+                                  const int* first_row, const int* len_after, const int* tiles, int n_tiles,
+                                  int nheads, int kvheads, int head_dim, float scale, int window,
+                                  cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (check_args("attention_prefill", nheads, kvheads, head_dim, block_tokens)) return 1;
+  AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window};
+  const size_t smem = (size_t)(TQ * (HD + 1) + BLK * (HD + 1) + BLK * HD + TQ * (BLK + 1)) * sizeof(float);
+  dim3 grid(n_tiles, nheads);
+  if (nheads > 65535) return fms_fail("attention_prefill: %d heads", nheads);
+  FMS_DISPATCH_DTYPE(dtype, T, {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return fms_fail("attention_prefill: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e));
+      configured = true;
+    }
+    attn_prefill_kernel<T><<<grid, 128, smem, stream>>>(a, tiles);
+  });
+  return fms_launch_status("attention_prefill");
+}
+
+// part_o: float [seqs, nheads, n_splits, HD]; part_ml: float [seqs, nheads, n_splits, 2]; both scratch.
+FMS_API int fms_attention_decode(const void* q, void* out, int dtype, const void* keys, const void* values,
+                                 const int* table, int table_stride, int block_tokens, const int* slots,
+                                 const int* first_row, const int* len_after, int n_seqs, int n_splits, float* part_o,
+                                 float* part_ml, int nheads, int kvheads, int head_dim, float scale, int window,
+                                 cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (check_args("attention_decode", nheads, kvheads, head_dim, block_tokens)) return 1;
+  if (n_splits <= 0 || n_splits > 65535) return fms_fail("attention_decode: %d splits", n_splits);
+  AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window};
+  const int group = nheads / kvheads;
+  const int chunks = (group + GC - 1) / GC;
+  if (kvheads * chunks > 65535 || nheads > 65535) return fms_fail("attention_decode: %d heads", nheads);
+  dim3 grid(n_seqs, kvheads * chunks, n_splits);
+  FMS_DISPATCH_DTYPE(dtype, T, {
+    attn_decode_kernel<T><<<grid, 128, 0, stream>>>(a, part_o, part_ml, n_splits);
+    attn_combine_kernel<T><<<dim3(n_seqs, nheads), HD >= 128 ? 128 : 64, 0, stream>>>(a, part_o, part_ml, n_splits);
+  });
+  return fms_launch_status("attention_decode");
+}

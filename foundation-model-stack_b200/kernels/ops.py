@@ -1,0 +1,236 @@
+"""The operations a decoder step is made of, each a call into a hand-written CUDA kernel.
+
+Tensors are torch tensors on a CUDA device (torch is used for memory and for the library matrix
+product only); every function launches on torch's current stream.  There is no CPU implementation and
+no fallback: a tensor on another device, a missing compiler or a failed build raises.
+
+Matrix products: float32 runs ``gemm_f32`` (FFMA, no tensor-core mode).  bfloat16 runs the library
+product (cuBLAS through ``torch.nn.functional.linear``), as the reference does for every linear layer
+(fms/modules/linear.py:119-156).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+F32, BF16 = 0, 1
+_P, _I, _F, _U64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_ulonglong
+
+_SIGNATURES = {
+    "fms_embed_rows": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
+    "fms_add_rmsnorm": [_P, _P, _P, _I, _F, _P, _I, _P, _I, _I, _P],
+    "fms_gated_activation": [_P, _P, _I, _I, _I, _I, _P],
+    "fms_rope_store": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "fms_gemm_f32": [_P, _P, _P, _P, _I, _I, _I, _P],
+    "fms_argmax": [_P, _P, _I, _I, _P],
+    "fms_sample": [_P, _P, _I, _I, _F, _I, _U64, _P, _I, _P],
+    "fms_attention_prefill": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+    "fms_attention_decode": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _F, _I, _P],
+}
+_functions = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _fn(library: str, name: str):
+    key = (library, name)
+    f = _functions.get(key)
+    if f is None:
+        lib = load_library(library)
+        f = getattr(lib, name)
+        f.argtypes = _SIGNATURES[name]
+        f.restype = ctypes.c_int
+        _functions[key] = f = (f, lib)
+    return f
+
+
+def _call(library: str, name: str, *args):
+    f, lib = _fn(library, name)
+    rc = f(*args)
+    if rc != 0:
+        raise KernelError(f"{name}: {lib.fms_last_error().decode(errors='replace')}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"dtype {dtype} has no kernel: float32 and bfloat16 have")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("a tensor on the CPU reached a CUDA kernel; this library has no CPU path")
+    if not t.is_contiguous():
+        raise KernelError("a non-contiguous tensor reached a CUDA kernel")
+    return t.data_ptr()
+
+
+_error_flags = {}
+
+
+def error_flag(device) -> torch.Tensor:
+    """An int32 on the device that kernels set when they meet what the host should have prevented (a token
+    id outside the vocabulary, a position without a cache block).  ``check_error_flag`` reads it."""
+    device = torch.device(device)
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    if key not in _error_flags:
+        _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _error_flags[key]
+
+
+def check_error_flag(device) -> None:
+    flag = error_flag(device)
+    v = int(flag.item())
+    if v:
+        flag.zero_()
+        raise KernelError({1: "a token id outside the vocabulary reached the embedding",
+                           2: "a token's position has no cache block"}.get(v, f"device error flag {v}"))
+
+
+# ---- embedding ---------------------------------------------------------------------------------------
+def embed(table: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
+    """Float32 rows of ``table`` at ``tokens``: the start of the residual stream."""
+    n, dim = tokens.shape[0], table.shape[1]
+    out = torch.empty((n, dim), dtype=torch.float32, device=table.device)
+    _call("elementwise", "fms_embed_rows", _ptr(table), _code(table.dtype), _ptr(tokens), _ptr(out), n, dim,
+          table.shape[0], _ptr(error_flag(table.device)), _stream())
+    return out
+
+
+# ---- norm --------------------------------------------------------------------------------------------
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """residual (float32, in place) += delta; returns gain * rmsnorm(residual) in ``out_dtype``.  With
+    ``rows`` only those rows are computed and the residual is not written."""
+    dim = residual.shape[1]
+    n = rows.shape[0] if rows is not None else residual.shape[0]
+    if residual.dtype != torch.float32:
+        raise KernelError("the residual stream is float32")
+    if delta is not None and delta.dtype != out_dtype:
+        raise KernelError(f"sublayer output is {delta.dtype}, compute dtype is {out_dtype}")
+    out = torch.empty((n, dim), dtype=out_dtype, device=residual.device)
+    _call("elementwise", "fms_add_rmsnorm", _ptr(residual), _ptr(delta), _ptr(gain), _code(gain.dtype), float(eps),
+          _ptr(out), _code(out_dtype), _ptr(rows), n, dim, _stream())
+    return out
+
+
+# ---- linear ------------------------------------------------------------------------------------------
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """x [rows, in] times weight [out, in] transposed (+ bias).  ``out_dtype`` defaults to x's dtype."""
+    out_dtype = out_dtype or x.dtype
+    _ptr(x), _ptr(weight)
+    if weight.dtype == torch.float32:
+        # true float32: also taken by a float32-stored matrix inside a bfloat16 model
+        x32 = x if x.dtype == torch.float32 else x.float()
+        b32 = None if bias is None else (bias if bias.dtype == torch.float32 else bias.float())
+        y = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
+        _call("gemm_f32", "fms_gemm_f32", _ptr(x32), _ptr(weight), _ptr(b32), _ptr(y), x.shape[0], weight.shape[0],
+              weight.shape[1], _stream())
+        return y if out_dtype == torch.float32 else y.to(out_dtype)
+    if weight.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
+        raise KernelError(f"linear: x {x.dtype}, weight {weight.dtype}")
+    if out_dtype == torch.float32:
+        y = torch.mm(x, weight.t(), out_dtype=torch.float32)
+        return y if bias is None else y + bias.float()
+    b = None if bias is None else bias.to(torch.bfloat16)
+    return torch.nn.functional.linear(x, weight, b)
+
+
+# ---- feed-forward ------------------------------------------------------------------------------------
+def gated_activation(gate_up: torch.Tensor, activation: int) -> torch.Tensor:
+    """act(gate) * up for rows [gate | up]."""
+    n, two_f = gate_up.shape
+    hidden = two_f // 2
+    out = torch.empty((n, hidden), dtype=gate_up.dtype, device=gate_up.device)
+    _call("elementwise", "fms_gated_activation", _ptr(gate_up), _ptr(out), _code(gate_up.dtype), n, hidden,
+          int(activation), _stream())
+    return out
+
+
+# ---- attention ---------------------------------------------------------------------------------------
+def rope_store(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], batch, view, nheads: int, kvheads: int,
+               head_dim: int, writes_cache: bool = True) -> torch.Tensor:
+    """Rotates q and k of ``qkv`` [tokens, (nheads + 2 kvheads) head_dim] by each token's position, writes k
+    and v into the cache at the token's slot and position, returns the rotated q [tokens, nheads head_dim]."""
+    n = qkv.shape[0]
+    if view.keys.dtype != qkv.dtype:
+        raise KernelError(f"cache is {view.keys.dtype}, activations are {qkv.dtype}")
+    q = torch.empty((n, nheads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    _call("elementwise", "fms_rope_store", _ptr(qkv), _code(qkv.dtype), _ptr(q), _ptr(inv_freq), _ptr(batch.positions),
+          _ptr(batch.token_seq), _ptr(batch.slots), _ptr(view.keys), _ptr(view.values), _ptr(view.table),
+          view.table.shape[1], view.block_tokens, n, nheads, kvheads, head_dim, 1 if writes_cache else 0,
+          _ptr(error_flag(qkv.device)), _stream())
+    return q
+
+
+def _attention_library(head_dim: int) -> str:
+    return f"attention_hd{head_dim}"
+
+
+_attn_constants = {}
+
+
+def attention_constants(head_dim: int):
+    """(keys per decode split, query rows per prefill tile) of the library built for this head size."""
+    if head_dim not in _attn_constants:
+        lib = load_library(_attention_library(head_dim))
+        _attn_constants[head_dim] = (int(lib.fms_attn_split_tokens()), int(lib.fms_attn_prefill_tile_rows()))
+    return _attn_constants[head_dim]
+
+
+def attention(q: torch.Tensor, batch, view, nheads: int, kvheads: int, head_dim: int, scale: float,
+              window: int) -> torch.Tensor:
+    """Causal softmax attention of the step's queries over the cache (which already holds the step's own
+    keys and values).  One query per sequence takes the split-key decode kernels, else the prefill kernel."""
+    out = torch.empty_like(q)
+    lib = _attention_library(head_dim)
+    split, tile_rows = attention_constants(head_dim)
+    common = (_ptr(q), _ptr(out), _code(q.dtype), _ptr(view.keys), _ptr(view.values), _ptr(view.table),
+              view.table.shape[1], view.block_tokens, _ptr(batch.slots), _ptr(batch.first_row), _ptr(batch.len_after))
+    if batch.decode:
+        n_splits = (batch.max_len_after + split - 1) // split
+        part_o = torch.empty((batch.n_seqs, nheads, n_splits, head_dim), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((batch.n_seqs, nheads, n_splits, 2), dtype=torch.float32, device=q.device)
+        _call(lib, "fms_attention_decode", *common, batch.n_seqs, n_splits, _ptr(part_o), _ptr(part_ml), nheads,
+              kvheads, head_dim, float(scale), int(window), _stream())
+    else:
+        tiles = batch.query_tiles(tile_rows)
+        _call(lib, "fms_attention_prefill", *common, _ptr(tiles), tiles.shape[0], nheads, kvheads, head_dim,
+              float(scale), int(window), _stream())
+    return out
+
+
+# ---- sampling ----------------------------------------------------------------------------------------
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    rows, vocab = logits.shape
+    if logits.dtype != torch.float32:
+        raise KernelError("logits are float32")
+    out = out if out is not None else torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    _call("sampling", "fms_argmax", _ptr(logits), _ptr(out), rows, vocab, _stream())
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: float, top_k: int, seed: int, requests: torch.Tensor, step: int,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    rows, vocab = logits.shape
+    if logits.dtype != torch.float32:
+        raise KernelError("logits are float32")
+    out = out if out is not None else torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    _call("sampling", "fms_sample", _ptr(logits), _ptr(out), rows, vocab, float(temperature), int(top_k),
+          int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(requests), int(step), _stream())
+    return out

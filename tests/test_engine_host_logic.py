@@ -1,0 +1,89 @@
+"""The library's host logic on the CPU: loader, adapter, cache, batching and the step function, with the
+CUDA kernels replaced by their plain restatements (tests/plain_ops.py).  Every way of cutting the work
+must give the plain implementation's logits."""
+import pytest
+import torch
+
+import plain_llama as pl
+from plain_ops import use_plain_ops
+from tiny_models import tiny_prompts
+
+
+def _model(folder, dtype="fp32"):
+    from fms_b200.models import get_model
+
+    return get_model("llama", model_path=folder, source="hf", device_type="cpu", data_type=dtype)
+
+
+@pytest.mark.parametrize("which", ["a", "b", "c"])
+def test_whole_prompts_alone(tiny_folders, which):
+    oracle = pl.PlainLlama(tiny_folders[which])
+    with use_plain_ops():
+        model = _model(tiny_folders[which])
+        engine = model.new_engine(max_tokens=512)
+        for prompt in tiny_prompts(which):
+            (slot,) = engine.begin(1)
+            got = engine.step([slot], [prompt], [list(range(len(prompt)))])
+            engine.release([slot])
+            torch.testing.assert_close(got.double(), oracle.logits(prompt), atol=2e-5, rtol=1e-4)
+        assert engine.cache.slots.n_held == 0 and all(g.pool.n_held == 0 for g in engine.cache.groups)
+
+
+@pytest.mark.parametrize("which", ["a", "b"])
+def test_unequal_batch_then_one_token_each(tiny_folders, which):
+    oracle = pl.PlainLlama(tiny_folders[which])
+    prompts = tiny_prompts(which)
+    full = [p + [(7 * i + 3) % 200 for i in range(6)] for p in prompts]
+    with use_plain_ops():
+        model = _model(tiny_folders[which])
+        engine = model.new_engine(max_tokens=64 * 2 * len(prompts))
+        slots = engine.begin(len(prompts))
+        got = {i: [] for i in range(len(prompts))}
+        lg = engine.step(slots, prompts)  # last place of every prompt
+        for i in range(len(prompts)):
+            got[i].append(lg[i])
+        for t in range(6):
+            lg = engine.step(slots, [[f[len(p) + t]] for f, p in zip(full, prompts)])
+            for i in range(len(prompts)):
+                got[i].append(lg[i])
+        engine.release(slots)
+    for i, (f, p) in enumerate(zip(full, prompts)):
+        want = oracle.logits(f)[len(p) - 1:]
+        torch.testing.assert_close(torch.stack(got[i]).double(), want, atol=2e-5, rtol=1e-4)
+
+
+def test_continuation_of_several_tokens_onto_a_cached_prefix(tiny_folders):
+    """The reference needs an explicit mask here (fms/modules/attention.py:268-271); position-based
+    causality does not."""
+    oracle = pl.PlainLlama(tiny_folders["a"])
+    prompt = tiny_prompts("a")[2]
+    with use_plain_ops():
+        engine = _model(tiny_folders["a"]).new_engine(max_tokens=128)
+        (slot,) = engine.begin(1)
+        a = engine.step([slot], [prompt[:7]], [list(range(7))])
+        b = engine.step([slot], [prompt[7:12]], [list(range(5))])
+        c = engine.step([slot], [prompt[12:]], [list(range(len(prompt) - 12))])
+        engine.release([slot])
+    torch.testing.assert_close(torch.cat([a, b, c]).double(), oracle.logits(prompt), atol=2e-5, rtol=1e-4)
+
+
+def test_step_refuses_what_does_not_fit(tiny_folders):
+    from fms_b200.cache import CacheFull
+
+    with use_plain_ops():
+        engine = _model(tiny_folders["a"]).new_engine(max_tokens=64, max_slots=2)
+        (slot,) = engine.begin(1)
+        with pytest.raises(ValueError, match="outside the vocabulary"):
+            engine.step([slot], [[1, 256]])
+        with pytest.raises(CacheFull):
+            engine.step([slot], [[1] * 65])  # the model's 64 positions
+        engine.step([slot], [[1] * 60])
+        (other,) = engine.begin(1)
+        with pytest.raises(CacheFull):
+            engine.step([other], [[1, 2]])  # the only block is held
+        assert engine.length(other) == 0
+        with pytest.raises(ValueError, match="twice"):
+            engine.step([slot, slot], [[1], [2]])
+        engine.release([slot, other])
+        with pytest.raises(ValueError, match="not held"):
+            engine.step([slot], [[1]])
