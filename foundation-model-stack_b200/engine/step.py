@@ -24,7 +24,7 @@ _REQUIRE_CUDA = True
 class Engine:
     """A model's decoder together with a cache of a given size."""
 
-    def __init__(self, model, max_tokens: int, max_slots: Optional[int] = None) -> None:
+    def __init__(self, model, max_tokens: int, max_slots: Optional[int] = None, sampling: bool = True) -> None:
         if model.decoder is None:
             raise ValueError("the model has no weights yet")
         self.model = model
@@ -33,8 +33,26 @@ class Engine:
         if _REQUIRE_CUDA and self.device.type != "cuda":
             raise RuntimeError(f"the engine runs on a CUDA device, not on {self.device}; there is no CPU path")
         self.vocab_size = self.decoder.spec.vocab_size
+        if self.device.type == "cuda":
+            self._compile_what_this_model_needs(sampling)
         self.cache = Cache(self.decoder.cache_requests(), max_tokens, self.decoder.spec.max_positions,
                            self.decoder.dtype, self.device, max_slots)
+
+    def _compile_what_this_model_needs(self, sampling: bool) -> None:
+        """Compiles, side by side, the kernel libraries this model will call and that are not built yet."""
+        from ..kernels import build
+
+        names = ["elementwise"]
+        tensors = self.decoder.state_dict().values()
+        if self.decoder.dtype == torch.float32 or any(t.dtype == torch.float32 and t.dim() == 2 for t in tensors):
+            names.append("gemm_f32")
+        for block in self.decoder.blocks:
+            hd = getattr(block.mixer, "head_dim", None)
+            if hd and getattr(block.mixer, "kvheads", None):
+                names.append(f"attention_hd{hd}")
+        if sampling:
+            names.append("sampling")
+        build.compile_many(names)
 
     # ---- sequences ---------------------------------------------------------------------------
     def begin(self, n: int) -> List[int]:

@@ -34,6 +34,7 @@ PLAIN_LIBRARIES = {
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
+_dir_lock = threading.Lock()
 
 
 class KernelBuildError(RuntimeError):
@@ -49,7 +50,18 @@ def find_nvcc() -> str:
                            "CUDA kernels cannot be compiled and there is no other path")
 
 
+_build_dir: Optional[str] = None
+
+
 def build_dir() -> str:
+    global _build_dir
+    with _dir_lock:
+        if _build_dir is None:
+            _build_dir = _pick_build_dir()
+        return _build_dir
+
+
+def _pick_build_dir() -> str:
     override = os.environ.get("FMS_B200_BUILD_DIR")
     candidates = [override] if override else []
     candidates.append(os.path.join(CSRC, "_build"))
@@ -164,5 +176,5 @@ def load_library(name: str) -> ctypes.CDLL:
         return lib
 
 
-def all_library_names(head_dims=(16, 32, 48, 64, 128)) -> List[str]:
+def all_library_names(head_dims=(16, 32, 48, 64, 128, 256)) -> List[str]:
     return list(PLAIN_LIBRARIES) + [f"attention_hd{h}" for h in head_dims]

@@ -56,10 +56,10 @@ class Model:
     def state_dict(self):
         return self.decoder.state_dict()
 
-    def new_engine(self, max_tokens: int, max_slots: Optional[int] = None):
+    def new_engine(self, max_tokens: int, max_slots: Optional[int] = None, sampling: bool = True):
         from ..engine.step import Engine
 
-        return Engine(self, max_tokens=max_tokens, max_slots=max_slots)
+        return Engine(self, max_tokens=max_tokens, max_slots=max_slots, sampling=sampling)
 
     def engine(self, min_tokens: int = 0, min_slots: int = 0):
         """The model's own engine, made on first use and made anew when it is too small."""

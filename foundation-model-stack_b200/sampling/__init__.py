@@ -1,0 +1,3 @@
+from .sampler import Sampler
+
+__all__ = ["Sampler"]

@@ -1,0 +1,5 @@
+"""``from fms_b200.utils.generation import generate`` — the reference's import path
+(fms/utils/generation.py)."""
+from ..engine.generation import generate, generate_batch, plan_batches, trim_prefix, truncate_after_eos
+
+__all__ = ["generate", "generate_batch", "plan_batches", "trim_prefix", "truncate_after_eos"]

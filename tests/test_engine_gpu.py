@@ -1,0 +1,254 @@
+"""The engine on the GPU against the plain implementation, in float32 and in bfloat16: each request alone
+and whole; with the last 32 tokens one by one; in batches of unequal lengths whose shorter requests end
+earlier, one batch after another so that slots and blocks are used again; long decoding; the first
+tokens of a sequence; generation through the entry point; the replay program."""
+import io
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_llama as pl
+from tiny_models import TINY, tiny_prompts
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DTYPES = ["fp32", "bf16"]
+
+
+def close(got, want, dtype):
+    """float32: the engine's own rounding only.  bfloat16: activations are rounded to 8 bits of mantissa
+    between kernels; 2% of the largest logit, fixed before the first run."""
+    want = want.double()
+    got = got.double().cpu()
+    if dtype == "fp32":
+        torch.testing.assert_close(got, want, atol=2e-5, rtol=1e-4)
+    else:
+        torch.testing.assert_close(got, want, atol=0.02 * want.abs().max().item(), rtol=0.02)
+
+
+@pytest.fixture(scope="module")
+def oracles(tiny_folders):
+    return {w: pl.PlainLlama(tiny_folders[w]) for w in tiny_folders}
+
+
+@pytest.fixture(scope="module")
+def models(tiny_folders):
+    from fms_b200.models import get_model
+
+    cache = {}
+
+    def get(which, dtype):
+        if (which, dtype) not in cache:
+            cache[(which, dtype)] = get_model("hf_pretrained", model_path=tiny_folders[which], device_type="cuda",
+                                              data_type=dtype)
+        return cache[(which, dtype)]
+
+    return get
+
+
+def long_requests(which, n=5, seed=0):
+    """Requests of unequal lengths, some longer than a cache block and than a decode split."""
+    cfg = TINY[which][0]
+    g = torch.Generator().manual_seed(50 + seed)
+    top = cfg["max_position_embeddings"]
+    lengths = [min(top, x) for x in ([33, 64, 65, 40, 128, 1] if top <= 128 else [33, 300, 65, 700, 129, 1])][:n]
+    return [torch.randint(0, cfg["vocab_size"], (k,), generator=g).tolist() for k in lengths]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which", ["a", "b", "c"])
+def test_each_request_alone_and_whole(models, oracles, which, dtype):
+    engine = models(which, dtype).new_engine(max_tokens=1024)
+    for req in tiny_prompts(which) + long_requests(which, 4):
+        (slot,) = engine.begin(1)
+        got = engine.step([slot], [req], [list(range(len(req)))])
+        engine.release([slot])
+        close(got, oracles[which].logits(req), dtype)
+    engine.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which", ["a", "b", "c"])
+def test_last_32_tokens_one_by_one(models, oracles, which, dtype):
+    engine = models(which, dtype).new_engine(max_tokens=1024)
+    for req in long_requests(which, 6):
+        want = oracles[which].logits(req)
+        cut = max(0, len(req) - 32)
+        (slot,) = engine.begin(1)
+        parts = []
+        if cut:
+            parts.append(engine.step([slot], [req[:cut]], [list(range(cut))]))
+        for t in range(cut, len(req)):
+            parts.append(engine.step([slot], [[req[t]]], [[0]]))
+        engine.release([slot])
+        close(torch.cat(parts), want, dtype)
+    engine.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which", ["a", "b", "c"])
+def test_unequal_batches_one_after_another_with_reuse(models, oracles, which, dtype):
+    """Three batches on a cache that holds only one of them: every slot and block is used again.  Freed
+    blocks are filled with NaN, so anything stale that is read shows."""
+    reqs = [long_requests(which, 5, seed=s) for s in range(3)]
+    need = max(sum((len(r) + 63) // 64 * 64 for r in batch) for batch in reqs)
+    engine = models(which, dtype).new_engine(max_tokens=need, max_slots=5)
+    group = engine.cache.groups[0]
+    for batch in reqs:
+        want = [oracles[which].logits(r) for r in batch]
+        prefill = [max(1, len(r) - 6 - i) for i, r in enumerate(batch)]  # unequal numbers of decoded tokens
+        slots = engine.begin(len(batch))
+        got = [[] for _ in batch]
+        lg = engine.step(slots, [r[:k] for r, k in zip(batch, prefill)], [list(range(k)) for k in prefill])
+        o = 0
+        for i, k in enumerate(prefill):
+            got[i].append(lg[o:o + k])
+            o += k
+        live = list(range(len(batch)))
+        at = list(prefill)
+        while live:
+            # requests that have no tokens left end here, earlier than the others
+            done = [i for i in live if at[i] >= len(batch[i])]
+            for i in done:
+                blocks = group.held_blocks(slots[i])
+                engine.release([slots[i]])
+                group.storage[:, :, blocks] = float("nan")
+            live = [i for i in live if i not in done]
+            if not live:
+                break
+            lg = engine.step([slots[i] for i in live], [[batch[i][at[i]]] for i in live])
+            for j, i in enumerate(live):
+                got[i].append(lg[j:j + 1])
+                at[i] += 1
+        for i in range(len(batch)):
+            close(torch.cat(got[i]), want[i], dtype)
+        assert engine.cache.slots.n_held == 0 and group.pool.n_held == 0
+    engine.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(models, oracles, dtype):
+    """A short prompt, then hundreds of tokens one by one: across block edges and decode splits."""
+    g = torch.Generator().manual_seed(60)
+    req = torch.randint(0, TINY["c"][0]["vocab_size"], (600,), generator=g).tolist()
+    want = oracles["c"].logits(req)
+    engine = models("c", dtype).new_engine(max_tokens=640)
+    (slot,) = engine.begin(1)
+    parts = [engine.step([slot], [req[:3]], [[0, 1, 2]])]
+    for t in range(3, len(req)):
+        parts.append(engine.step([slot], [[req[t]]]))
+    engine.release([slot])
+    close(torch.cat(parts), want, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which", ["a", "b"])
+def test_first_tokens_of_a_sequence(models, oracles, which, dtype):
+    """Position 0 sees one key; a one-token prompt is a prefill of one token."""
+    engine = models(which, dtype).new_engine(max_tokens=256)
+    req = tiny_prompts(which)[-1][:6]
+    want = oracles[which].logits(req)
+    (slot,) = engine.begin(1)
+    parts = [engine.step([slot], [[t]]) for t in req]
+    engine.release([slot])
+    close(torch.cat(parts), want, dtype)
+    slots = engine.begin(2)
+    lg = engine.step(slots, [req[:1], req[:2]], [[0], [0, 1]])
+    engine.release(slots)
+    close(lg, torch.cat([want[:1], want[:2]]), dtype)
+
+
+@pytest.mark.parametrize("which", ["a", "b"])
+def test_greedy_generation_through_the_entry_point(models, oracles, which):
+    from fms_b200.utils.generation import generate
+
+    prompts = tiny_prompts(which)
+    model = models(which, "fp32")
+    out = generate(model, [torch.tensor(p) for p in prompts], max_new_tokens=8, do_sample=False)
+    for o, p in zip(out, prompts):
+        assert o.tolist() == pl.plain_generate(oracles[which], p, 8)
+    # one prompt alone gives the same tokens as in the batch
+    alone = generate(model, torch.tensor(prompts[1]), max_new_tokens=8, do_sample=False)
+    assert alone.tolist() == out[1].tolist()
+
+
+def test_sampled_generation_is_the_same_alone_and_in_batches(models, oracles):
+    from fms_b200.utils.generation import generate
+
+    prompts = tiny_prompts("b")
+    model = models("b", "fp32")
+    kw = dict(max_new_tokens=16, do_sample=True, temperature=0.8, top_k=0, seed=11)
+    together = generate(model, [torch.tensor(p) for p in prompts], **kw)
+    in_twos = generate(model, [torch.tensor(p) for p in prompts], batch_size=2, **kw)
+    assert [t.tolist() for t in together] == [t.tolist() for t in in_twos]
+    plain = [pl.plain_generate(oracles["b"], p, 16, do_sample=True, temperature=0.8, top_k=0, seed=11, request=i)
+             for i, p in enumerate(prompts)]
+    same = sum(a == b for t, w in zip(together, plain) for a, b in zip(t.tolist(), w))
+    assert same >= sum(len(w) for w in plain) - 1  # float32 against float64 running sums
+
+
+def test_bfloat16_greedy_generation(models, oracles):
+    from fms_b200.utils.generation import generate
+
+    prompts = tiny_prompts("a")
+    logits = []
+    out = generate(models("a", "bf16"), [torch.tensor(p) for p in prompts], max_new_tokens=8, do_sample=False,
+                   post_iteration_hook=lambda it, lg, toks, reqs: logits.append((reqs, lg.float().cpu())))
+    # every step's logits belong to the sequence generated so far
+    for i, (o, p) in enumerate(zip(out, prompts)):
+        want = oracles["a"].logits(o.tolist()[:-1])[len(p) - 1:]
+        got = torch.stack([lg[reqs.index(i)] for reqs, lg in logits if i in reqs])
+        close(got, want, "bf16")
+
+
+def _trace_lines(reqs, prefill):
+    """Steps of one batch: prompts together, then one token each; shorter requests end earlier."""
+    lines, step = [], 0
+    at = list(prefill)
+    ids = [f"r{i}" for i in range(len(reqs))]
+    entries = [{"id": ids[i], "tokens": reqs[i][:at[i]], "want": list(range(at[i]))} for i in range(len(reqs))]
+    live = list(range(len(reqs)))
+    while True:
+        end = [ids[i] for i in live if at[i] >= len(reqs[i])]
+        lines.append({"step": step, "entries": entries, "end": end})
+        live = [i for i in live if at[i] < len(reqs[i])]
+        if not live:
+            break
+        step += 1
+        entries = [{"id": ids[i], "tokens": [reqs[i][at[i]]], "want": [0]} for i in live]
+        for i in live:
+            at[i] += 1
+    return lines
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(tiny_folders, oracles, tmp_path, dtype):
+    reqs = long_requests("b", 4)
+    prefill = [max(1, len(r) - 5) for r in reqs]
+    lines = _trace_lines(reqs, prefill)
+    out = tmp_path / f"out_{dtype}"
+    proc = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", tiny_folders["b"], "--dtype", dtype, "--out",
+         str(out), "--max-tokens", str(sum((len(r) + 63) // 64 * 64 for r in reqs))],
+        input="\n".join(json.dumps(l) for l in lines) + "\n", capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split() == [x for l in lines for x in ("done", str(l["step"]))]
+    import numpy as np
+
+    vocab = TINY["b"][0]["vocab_size"]
+    got = {i: [] for i in range(len(reqs))}
+    for l in lines:
+        data = torch.from_numpy(np.fromfile(out / f"{l['step']}.f32", dtype="<f4").reshape(-1, vocab).copy())
+        o = 0
+        for e in l["entries"]:
+            k = len(e["want"])
+            got[int(e["id"][1:])].append(data[o:o + k])
+            o += k
+        assert o == data.shape[0]
+    for i, r in enumerate(reqs):
+        close(torch.cat(got[i]), oracles["b"].logits(r), "fp32" if dtype == "float32" else "bf16")

@@ -1,0 +1,282 @@
+"""Each CUDA kernel alone against its plain restatement (tests/plain_ops.py), at sizes other than the
+models' own: odd widths and vocabularies, head sizes in steps of 16, any number of heads and groups."""
+import math
+
+import pytest
+import torch
+
+import plain_ops as P
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from fms_b200.kernels import ops as o
+
+    return o
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab,dim", [(331, 240), (17, 16), (1000, 4096 + 48)])
+def test_embed(ops, dtype, vocab, dim):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(vocab, dim, generator=g).to(dtype).cuda()
+    tokens = torch.randint(0, vocab, (37,), generator=g, dtype=torch.int32).cuda()
+    got = ops.embed(table, tokens)
+    assert got.dtype == torch.float32
+    torch.testing.assert_close(got, P.embed(table, tokens), atol=0, rtol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("gain_dtype", DTYPES)
+@pytest.mark.parametrize("rows,dim,eps", [(5, 240, 1e-5), (3, 17, 1e-6), (2, 5000, 1e-3)])
+def test_add_rmsnorm(ops, dtype, gain_dtype, rows, dim, eps):
+    g = torch.Generator().manual_seed(1)
+    res = (torch.randn(rows, dim, generator=g) * 3).cuda()
+    delta = torch.randn(rows, dim, generator=g).to(dtype).cuda()
+    gain = (1 + 0.1 * torch.randn(dim, generator=g)).to(gain_dtype).cuda()
+    res_ref = res.clone()
+    want = P.add_rmsnorm(res_ref, delta, gain, eps, torch.float32)
+    got = ops.add_rmsnorm(res, delta, gain, eps, dtype)
+    torch.testing.assert_close(res, res_ref, atol=1e-6, rtol=1e-6)  # the stream itself, in float32
+    torch.testing.assert_close(got.float(), want, **tol(dtype))
+    # without a delta the stream is untouched
+    before = res.clone()
+    got2 = ops.add_rmsnorm(res, None, gain, eps, dtype)
+    assert torch.equal(res, before)
+    torch.testing.assert_close(got2.float(), P.add_rmsnorm(before.clone(), None, gain, eps, torch.float32), **tol(dtype))
+    # gathered rows: only those rows, the stream untouched
+    idx = torch.tensor([rows - 1, 0], dtype=torch.int32).cuda()
+    got3 = ops.add_rmsnorm(res, delta, gain, eps, dtype, rows=idx)
+    assert torch.equal(res, before)
+    torch.testing.assert_close(got3.float(), P.add_rmsnorm(before.clone(), delta, gain, eps, torch.float32, rows=idx),
+                               **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("act", [0, 1, 2, 3])
+def test_gated_activation(ops, dtype, act):
+    g = torch.Generator().manual_seed(2)
+    gu = (torch.randn(7, 2 * 173, generator=g) * 2).to(dtype).cuda()
+    got = ops.gated_activation(gu, act)
+    want = P.gated_activation(gu.float(), act)
+    torch.testing.assert_close(got.float(), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 331, 240), (5, 64, 17), (70, 130, 328), (129, 257, 1000)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_linear_float32_is_true_float32(ops, m, n, k, bias):
+    g = torch.Generator().manual_seed(3)
+    # values with many mantissa bits: a tf32 or bf16 product would miss the tolerance by orders of magnitude
+    x = torch.randn(m, k, generator=g).cuda()
+    w = torch.randn(n, k, generator=g).cuda()
+    b = torch.randn(n, generator=g).cuda() if bias else None
+    got = ops.linear(x, w, b)
+    want = P.linear(x, w, b, torch.float64)
+    err = (got.double() - want).abs().max().item()
+    assert err < 2e-6 * math.sqrt(k) * 4, err
+    # a row's result does not depend on the other rows of the batch
+    alone = ops.linear(x[:1].contiguous(), w, b)
+    assert torch.equal(alone[0], got[0])
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 331, 240), (8, 512, 96), (33, 1000, 328), (200, 384, 64)])
+def test_linear_bfloat16(ops, m, n, k):
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    want = P.linear(x, w, None, torch.float64)
+    got = ops.linear(x, w)
+    assert got.dtype == torch.bfloat16
+    torch.testing.assert_close(got.double(), want, atol=2e-2, rtol=2e-2)
+    got32 = ops.linear(x, w, None, torch.float32)
+    assert got32.dtype == torch.float32
+    torch.testing.assert_close(got32.double(), want, atol=1e-3, rtol=1e-3)
+
+
+def test_linear_float32_matrix_in_a_bfloat16_model(ops):
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(4, 96, generator=g).to(torch.bfloat16).cuda()
+    w = torch.randn(50, 96, generator=g).cuda()
+    got = ops.linear(x, w)
+    assert got.dtype == torch.bfloat16
+    torch.testing.assert_close(got.double(), P.linear(x, w, None, torch.float64), atol=5e-2, rtol=2e-2)
+
+
+class FakeBatch:
+    pass
+
+
+def make_cache_case(dtype, nheads, kvheads, hd, lens_before, num_new, seed, window=0, poison=True):
+    """A cache with random contents for sequences of the given lengths, blocks handed out in a scrambled
+    order, everything that is not a live position poisoned with NaN; the batch arrays of a step."""
+    from fms_b200.cache import Cache, KVRequest
+    from fms_b200.engine.batch import Batch
+
+    g = torch.Generator().manual_seed(seed)
+    n = len(lens_before)
+    cache = Cache([KVRequest(kvheads, hd, window)], max_tokens=64 * (sum((a + b + 63) // 64 for a, b in zip(lens_before, num_new)) + 5),
+                  max_positions=4096, dtype=dtype, device="cuda")
+    # scramble the free list so that block ids are not in order
+    pool = cache.groups[0].pool
+    perm = torch.randperm(len(pool._free), generator=g).tolist()
+    pool._free = [pool._free[i] for i in perm]
+    slots = cache.begin(n + 2)[2:]  # not slot 0, 1
+    storage = cache.groups[0].storage
+    if poison:
+        storage.fill_(float("nan"))
+    if any(lens_before):
+        live = [(s, lb) for s, lb in zip(slots, lens_before) if lb]
+        cache.prepare([s for s, _ in live], [lb for _, lb in live])
+        cache.commit([s for s, _ in live], [lb for _, lb in live])
+    cache.prepare(slots, num_new)
+    view = cache.layer_view(0)
+    # fill the positions that exist before the step with random keys and values
+    table = cache.groups[0].table_host
+    for s, lb in zip(slots, lens_before):
+        lo = max(0, lb - window + 1) // 64 * 64 if window else 0
+        for p in range(lo, lb):
+            blk = int(table[s, p // 64])
+            view.keys[blk, :, p % 64] = torch.randn(kvheads, hd, generator=g).to(dtype).cuda()
+            view.values[blk, :, p % 64] = torch.randn(kvheads, hd, generator=g).to(dtype).cuda()
+    tokens = [[0] * k for k in num_new]
+    batch = Batch.from_lists(slots, lens_before, tokens, [[] for _ in tokens], "cuda")
+    return cache, view, batch
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nheads,kvheads,hd", [(4, 2, 16), (3, 1, 32), (5, 5, 48), (12, 1, 64)])
+def test_rope_store(ops, dtype, nheads, kvheads, hd):
+    lens_before, num_new = [0, 70, 5], [3, 1, 66]
+    cache, view, batch = make_cache_case(dtype, nheads, kvheads, hd, lens_before, num_new, 6)
+    g = torch.Generator().manual_seed(7)
+    n = sum(num_new)
+    qkv = torch.randn(n, (nheads + 2 * kvheads) * hd, generator=g).to(dtype).cuda()
+    inv = (1.0 / (10000.0 ** (torch.arange(0, hd, 2).float() / hd))).cuda()
+    keys0, values0 = view.keys.clone(), view.values.clone()
+
+    class V:
+        keys, values, table, block_tokens = keys0, values0, view.table, 64
+
+    want_q = P.rope_store(qkv, inv, batch, V, nheads, kvheads, hd)
+    got_q = ops.rope_store(qkv, inv, batch, view, nheads, kvheads, hd)
+    t = tol(dtype)
+    torch.testing.assert_close(got_q.float(), want_q.float(), **t)
+    torch.testing.assert_close(view.keys.float(), keys0.float(), equal_nan=True, **t)
+    torch.testing.assert_close(view.values.float(), values0.float(), equal_nan=True, **t)
+    # without frequencies nothing is rotated; without cache writes nothing is written
+    before = view.keys.clone()
+    q2 = ops.rope_store(qkv, None, batch, view, nheads, kvheads, hd, writes_cache=False)
+    assert torch.equal(q2, qkv[:, : nheads * hd].contiguous())
+    assert torch.equal(torch.nan_to_num(view.keys.float()), torch.nan_to_num(before.float()))
+
+
+ATTN_CASES = [
+    # nheads, kvheads, hd, lens_before, num_new, window
+    (4, 2, 16, [0, 0, 0], [5, 70, 17], 0),          # prompts from an empty cache
+    (3, 1, 32, [100, 3, 64], [1, 1, 1], 0),         # decode, MQA
+    (5, 5, 48, [130, 0], [40, 129], 0),             # continuation onto a cached prefix, odd head size
+    (12, 1, 64, [300], [1], 0),                     # decode with 12 query heads on one kv head (two chunks)
+    (4, 2, 16, [200, 10], [1, 1], 70),              # decode with a window
+    (4, 2, 32, [90, 0], [50, 150], 33),             # prefill with a window
+    (2, 2, 128, [513], [1], 0),                     # decode over three splits
+    (2, 1, 256, [20], [30], 0),                     # the largest head size
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nheads,kvheads,hd,lens_before,num_new,window", ATTN_CASES)
+def test_attention(ops, dtype, nheads, kvheads, hd, lens_before, num_new, window):
+    cache, view, batch = make_cache_case(dtype, nheads, kvheads, hd, lens_before, num_new, 8, window)
+    g = torch.Generator().manual_seed(9)
+    n = sum(num_new)
+    # the step's own keys and values
+    qkv = torch.randn(n, (nheads + 2 * kvheads) * hd, generator=g).to(dtype).cuda()
+    q = ops.rope_store(qkv, None, batch, view, nheads, kvheads, hd)
+    scale = 1.0 / math.sqrt(hd)
+    want = P.attention(q, batch, view, nheads, kvheads, hd, scale, window)
+    got = ops.attention(q, batch, view, nheads, kvheads, hd, scale, window)
+    assert not torch.isnan(got).any()
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key(ops, dtype):
+    """One key among hundreds is scaled so that it takes nearly all the weight: its value must come out,
+    wherever it lies (first position, a block edge, a split edge)."""
+    nheads, kvheads, hd = 2, 1, 32
+    for far in (0, 63, 64, 255, 256, 400):
+        cache, view, batch = make_cache_case(dtype, nheads, kvheads, hd, [600], [1], 10)
+        table = cache.groups[0].table_host
+        slot = int(batch.slots[0])
+        g = torch.Generator().manual_seed(11)
+        qkv = torch.randn(1, (nheads + 2 * kvheads) * hd, generator=g).to(dtype).cuda()
+        q = ops.rope_store(qkv, None, batch, view, nheads, kvheads, hd)
+        blk = int(table[slot, far // 64])
+        view.keys[blk, 0, far % 64] = (q[0, :hd].float() * 8).to(dtype)  # a large score for head 0
+        marker = torch.full((hd,), 3.0).to(dtype).cuda()
+        view.values[blk, 0, far % 64] = marker
+        got = ops.attention(q, batch, view, nheads, kvheads, hd, 1.0 / math.sqrt(hd), 0)
+        torch.testing.assert_close(got[0, :hd].float(), marker.float(), atol=5e-2, rtol=0)
+        want = P.attention(q, batch, view, nheads, kvheads, hd, 1.0 / math.sqrt(hd), 0)
+        torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+
+
+def test_attention_refuses_other_head_sizes():
+    from fms_b200.kernels.build import KernelBuildError, _spec
+
+    for hd in (8, 24, 272):
+        with pytest.raises(KernelBuildError):
+            _spec(f"attention_hd{hd}")
+
+
+@pytest.mark.parametrize("vocab", [331, 1000, 128256])
+def test_argmax(ops, vocab):
+    g = torch.Generator().manual_seed(12)
+    logits = torch.randn(5, vocab, generator=g).cuda()
+    logits[1, 7] = logits[1, vocab - 1] = 50.0  # equal maxima: the lower index
+    logits[2, vocab - 1] = 60.0
+    got = ops.argmax(logits)
+    assert got.tolist() == torch.argmax(logits.cpu(), -1).tolist()
+    assert got[1].item() == 7 and got[2].item() == vocab - 1
+
+
+@pytest.mark.parametrize("vocab,top_k,temperature", [(331, 0, 0.8), (331, 10, 1.0), (1000, 1, 0.5), (128256, 50, 1.3),
+                                                     (128256, 0, 0.7)])
+def test_sample_equals_plain_inverse_cdf(ops, vocab, top_k, temperature):
+    g = torch.Generator().manual_seed(13)
+    rows = 24
+    logits = (torch.randn(rows, vocab, generator=g) * 3).cuda()
+    requests = torch.arange(100, 100 + rows, dtype=torch.int32).cuda()
+    mismatches = 0
+    for step in (0, 1, 17):
+        got = ops.sample(logits, temperature, top_k, 77, requests, step).tolist()
+        want = P.sample(logits.cpu(), temperature, top_k, 77, requests.cpu(), step).tolist()
+        mismatches += sum(a != b for a, b in zip(got, want))
+        # a request's draw does not depend on its row or on the other rows
+        alone = ops.sample(logits[5:6].contiguous(), temperature, top_k, 77, requests[5:6].contiguous(), step)
+        assert alone.item() == got[5]
+    # float32 and float64 running sums may cross u at neighbouring tokens, rarely
+    assert mismatches <= 1
+
+
+def test_sample_distribution_and_top_k(ops):
+    vocab, rows = 50, 4000
+    g = torch.Generator().manual_seed(14)
+    row = torch.randn(vocab, generator=g) * 2
+    logits = row.repeat(rows, 1).cuda()
+    requests = torch.arange(rows, dtype=torch.int32).cuda()
+    got = ops.sample(logits, 1.0, 0, 5, requests, 0).long().cpu()
+    freq = torch.bincount(got, minlength=vocab).double() / rows
+    p = torch.softmax(row.double(), 0)
+    assert (freq - p).abs().max() < 0.03
+    got = ops.sample(logits, 1.0, 3, 5, requests, 1).long().cpu()
+    assert set(got.tolist()) <= set(torch.topk(row, 3).indices.tolist())
+    assert len(set(got.tolist())) == 3
