@@ -233,6 +233,19 @@ class Cache:
             g.sync()
         return before
 
+    def prepare_decode(self, slots: Sequence[int]) -> None:
+        """``prepare`` for a step of one token per sequence, without looking at whole table rows: a block
+        is needed only when a sequence's length is a multiple of 64, and a window only moves then."""
+        work = []
+        for s in slots:
+            n = self.length[s]
+            if n + 1 > self.max_positions:
+                raise CacheFull(f"slot {s}: {n} + 1 tokens exceed the model's {self.max_positions} positions")
+            if n % BLOCK_TOKENS == 0 or any(isinstance(g, KVGroup) and g.request.window for g in self.groups):
+                work.append(s)
+        if work:
+            self.prepare(work, [1] * len(work))
+
     def commit(self, slots: Sequence[int], num_new: Sequence[int]) -> None:
         for s, n in zip(slots, num_new):
             self.length[s] += n

@@ -184,3 +184,21 @@ FMS_API int fms_rope_store(const void* qkv, int dtype, void* q_out, const float*
                          table, table_stride, block_tokens, nheads, kvheads, head_dim, write_cache, error_flag));
   return fms_launch_status("rope_store");
 }
+
+// ---------------------------------------------------------------------------------------------------
+// start of a decode step: every sequence's new token sits at its current length, which then grows by one
+// ---------------------------------------------------------------------------------------------------
+__global__ void decode_advance_kernel(int* __restrict__ positions, int* __restrict__ lengths, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    const int len = lengths[i];
+    positions[i] = len;
+    lengths[i] = len + 1;
+  }
+}
+
+FMS_API int fms_decode_advance(int* positions, int* lengths, int n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  decode_advance_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, lengths, n);
+  return fms_launch_status("decode_advance");
+}

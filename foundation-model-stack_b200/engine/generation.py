@@ -73,7 +73,10 @@ def generate_batch(engine, sampler: Sampler, prompts: Sequence[Sequence[int]], r
         feed = [list(p) for p in prompts]
         for it in range(max_new_tokens):
             start = time.perf_counter()
-            logits = engine.step([slots[i] for i in live], feed)
+            if it > 0 and hasattr(engine, "decode"):
+                logits = engine.decode([slots[i] for i in live], [f[0] for f in feed])
+            else:
+                logits = engine.step([slots[i] for i in live], feed)
             req = torch.tensor([requests[i] for i in live], dtype=torch.int32).to(engine.device)
             tokens = sampler(logits, req, it).tolist()  # device -> host: the loop's one synchronisation
             if times is not None:

@@ -5,10 +5,14 @@ one step, then one token each.
 left, and returns float32 logits at the wanted places.  The reference's counterpart is
 ``LLaMA.forward(..., past_key_value_states, use_cache=True)`` (fms/models/llama.py:425-450) on a
 left-padded rectangle with a mask; here rows are ragged, nothing is padded and causality is by position.
+
+A step in which every sequence brings one token and wants its logits is a decode step.  It runs the same
+kernels as any other step, but from arrays that stay on the device (tokens, positions, lengths, slots)
+and, from its second occurrence on, as one CUDA graph launch instead of some hundred kernel launches.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -16,15 +20,41 @@ from ..cache.cache import Cache
 from ..kernels import ops
 from .batch import Batch
 
-
 # Tests that replace the kernels by plain restatements clear this to drive the host logic on the CPU.
 _REQUIRE_CUDA = True
+
+
+class _DecodeBuffers:
+    """Device arrays of decode steps of n sequences, and the CUDA graphs captured over them."""
+
+    def __init__(self, n: int, device) -> None:
+        self.n = n
+        ar = torch.arange(n + 1, dtype=torch.int32, device=device)
+        self.batch = Batch()
+        b = self.batch
+        b.n_seqs = b.n_tokens = b.n_wanted = n
+        b.decode, b.max_new, b.num_new = True, 1, [1] * n
+        b.tokens = torch.zeros(n, dtype=torch.int32, device=device)
+        b.positions = torch.zeros(n, dtype=torch.int32, device=device)
+        b.token_seq = ar[:n].clone()
+        b.first_row = ar
+        b.slots = torch.zeros(n, dtype=torch.int32, device=device)
+        b.len_after = torch.zeros(n, dtype=torch.int32, device=device)  # between steps: the current lengths
+        b.want_rows = ar[:n].clone()
+        self.tokens_host = torch.zeros(n, dtype=torch.int32).pin_memory() if torch.device(device).type == "cuda" \
+            else torch.zeros(n, dtype=torch.int32)
+        self.copied = None  # event after the last copy out of tokens_host
+        self.loaded: Optional[Tuple[int, ...]] = None  # slots whose state the arrays hold
+        self.lengths: List[int] = []  # their lengths, as the device arrays have them
+        self.graphs: Dict[int, object] = {}  # key-split bound -> (graph, logits)
+        self.seen: Dict[int, int] = {}
 
 
 class Engine:
     """A model's decoder together with a cache of a given size."""
 
-    def __init__(self, model, max_tokens: int, max_slots: Optional[int] = None, sampling: bool = True) -> None:
+    def __init__(self, model, max_tokens: int, max_slots: Optional[int] = None, sampling: bool = True,
+                 use_graphs: bool = True) -> None:
         if model.decoder is None:
             raise ValueError("the model has no weights yet")
         self.model = model
@@ -37,6 +67,11 @@ class Engine:
             self._compile_what_this_model_needs(sampling)
         self.cache = Cache(self.decoder.cache_requests(), max_tokens, self.decoder.spec.max_positions,
                            self.decoder.dtype, self.device, max_slots)
+        self.use_graphs = use_graphs and self.device.type == "cuda"
+        self._decode: Dict[int, _DecodeBuffers] = {}
+        self.h2d_bytes = 0  # bytes copied host -> device by steps since the engine was made
+        self.graph_launches = 0
+        self.kernels_per_graph = 0  # own kernels inside the decode graph captured last
 
     def _compile_what_this_model_needs(self, sampling: bool) -> None:
         """Compiles, side by side, the kernel libraries this model will call and that are not built yet."""
@@ -73,18 +108,90 @@ class Engine:
         device, in the order of the sequences and of ``want``."""
         if len(slots) != len(tokens) or not slots:
             raise ValueError("a step needs one token list per slot, and at least one")
-        if want is None:
-            want = [[len(t) - 1] for t in tokens]
         for t in tokens:
             for x in t:
                 if not (0 <= int(x) < self.vocab_size):
                     raise ValueError(f"token id {x} outside the vocabulary of {self.vocab_size}")
+        if all(len(t) == 1 for t in tokens) and (want is None or all(list(w) == [0] for w in want)):
+            return self.decode(slots, [int(t[0]) for t in tokens]).clone()
+        if want is None:
+            want = [[len(t) - 1] for t in tokens]
         num_new = [len(t) for t in tokens]
         before = self.cache.prepare(slots, num_new)
         batch = Batch.from_lists(slots, before, tokens, want, self.device)
+        self.h2d_bytes += 4 * (3 * batch.n_tokens + 3 * batch.n_seqs + 1 + batch.n_wanted)
         logits = self.decoder.forward(batch, self.cache)
         self.cache.commit(slots, num_new)
         return logits
+
+    def decode(self, slots: Sequence[int], tokens: Optional[Sequence[int]] = None,
+               tokens_device: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One token for each sequence; logits [n, vocab] for each.  The tokens come from the host
+        (``tokens``) or are already on the device (``tokens_device``, int32 [n], e.g. what the sampler
+        wrote).  The result is a buffer that the next decode step of as many sequences overwrites: use
+        it, or copy it, before that."""
+        n = len(slots)
+        if len(set(slots)) != n:
+            raise ValueError("a slot appears twice in one step")
+        for s in slots:
+            if not self.cache.slots.is_held(s):
+                raise ValueError(f"slot {s} is not held")
+        buf = self._decode.get(n)
+        if buf is None:
+            buf = self._decode[n] = _DecodeBuffers(n, self.device)
+        key = tuple(slots)
+        lengths = [self.cache.length[s] for s in slots]
+        self.cache.prepare_decode(slots)
+        if buf.copied is not None:
+            buf.copied.synchronize()  # the last copy out of the pinned array is over
+        if buf.loaded != key or buf.lengths != lengths:
+            state = torch.tensor([list(slots), lengths], dtype=torch.int32)
+            buf.batch.slots.copy_(state[0])
+            buf.batch.len_after.copy_(state[1])
+            buf.loaded, buf.lengths = key, lengths
+            self.h2d_bytes += 8 * n
+        if tokens_device is not None:
+            buf.batch.tokens.copy_(tokens_device)
+        else:
+            buf.tokens_host.copy_(torch.tensor(list(tokens), dtype=torch.int32))
+            buf.batch.tokens.copy_(buf.tokens_host, non_blocking=True)
+            self.h2d_bytes += 4 * n
+            if self.device.type == "cuda":
+                buf.copied = torch.cuda.Event()
+                buf.copied.record()
+        logits = self._run_decode(buf, max(lengths) + 1)
+        self.cache.commit(slots, [1] * n)
+        buf.lengths = [x + 1 for x in lengths]
+        return logits
+
+    def _decode_body(self, buf: _DecodeBuffers) -> torch.Tensor:
+        ops.decode_advance(buf.batch.positions, buf.batch.len_after)
+        return self.decoder.forward(buf.batch, self.cache)
+
+    def _run_decode(self, buf: _DecodeBuffers, longest: int) -> torch.Tensor:
+        # the bound on key splits that the launch is sized for: a power of two of 256-token splits, so
+        # that a graph serves many steps; blocks beyond a sequence's own length return at once
+        bound = 256
+        while bound < longest:
+            bound *= 2
+        bound = min(bound, max(256, (self.cache.max_positions + 255) // 256 * 256))
+        buf.batch.max_len_after = max(bound, longest)
+        if not self.use_graphs:
+            return self._decode_body(buf)
+        entry = buf.graphs.get(bound)
+        if entry is None:
+            buf.seen[bound] = buf.seen.get(bound, 0) + 1
+            if buf.seen[bound] == 1:
+                return self._decode_body(buf)  # first occurrence: plain launches (they also warm everything up)
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launches
+            with torch.cuda.graph(graph):
+                logits = self._decode_body(buf)
+            self.kernels_per_graph = ops.launches - before
+            entry = buf.graphs[bound] = (graph, logits)
+        entry[0].replay()
+        self.graph_launches += 1
+        return entry[1]
 
     def check(self) -> None:
         """Raises if a kernel met something the host should have prevented (synchronises)."""

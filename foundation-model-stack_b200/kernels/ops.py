@@ -25,6 +25,7 @@ _SIGNATURES = {
     "fms_add_rmsnorm": [_P, _P, _P, _I, _F, _P, _I, _P, _I, _I, _P],
     "fms_gated_activation": [_P, _P, _I, _I, _I, _I, _P],
     "fms_rope_store": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "fms_decode_advance": [_P, _P, _I, _P],
     "fms_gemm_f32": [_P, _P, _P, _P, _I, _I, _I, _P],
     "fms_argmax": [_P, _P, _I, _I, _P],
     "fms_sample": [_P, _P, _I, _I, _F, _I, _U64, _P, _I, _P],
@@ -32,6 +33,9 @@ _SIGNATURES = {
     "fms_attention_decode": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _F, _I, _P],
 }
 _functions = {}
+# kernels launched through this module since import (a decode-attention call launches two)
+launches = 0
+_KERNELS_PER_CALL = {"fms_attention_decode": 2}
 
 
 class KernelError(RuntimeError):
@@ -51,7 +55,9 @@ def _fn(library: str, name: str):
 
 
 def _call(library: str, name: str, *args):
+    global launches
     f, lib = _fn(library, name)
+    launches += _KERNELS_PER_CALL.get(name, 1)
     rc = f(*args)
     if rc != 0:
         raise KernelError(f"{name}: {lib.fms_last_error().decode(errors='replace')}")
@@ -213,6 +219,11 @@ def attention(q: torch.Tensor, batch, view, nheads: int, kvheads: int, head_dim:
         _call(lib, "fms_attention_prefill", *common, _ptr(tiles), tiles.shape[0], nheads, kvheads, head_dim,
               float(scale), int(window), _stream())
     return out
+
+
+def decode_advance(positions: torch.Tensor, lengths: torch.Tensor) -> None:
+    """positions[i] = lengths[i]; lengths[i] += 1 — the bookkeeping of a decode step, on the device."""
+    _call("elementwise", "fms_decode_advance", _ptr(positions), _ptr(lengths), positions.shape[0], _stream())
 
 
 # ---- sampling ----------------------------------------------------------------------------------------

@@ -99,6 +99,11 @@ def attention(q, batch, view, nheads, kvheads, head_dim, scale, window):
     return out
 
 
+def decode_advance(positions, lengths):
+    positions.copy_(lengths)
+    lengths += 1
+
+
 def argmax(logits, out=None):
     r = torch.argmax(logits, dim=-1).to(torch.int32)
     if out is not None:
@@ -128,7 +133,7 @@ def check_error_flag(device):
 
 
 PLAIN = dict(embed=embed, add_rmsnorm=add_rmsnorm, linear=linear, gated_activation=gated_activation,
-             rope_store=rope_store, attention=attention, argmax=argmax, sample=sample, error_flag=error_flag,
+             rope_store=rope_store, attention=attention, decode_advance=decode_advance, argmax=argmax, sample=sample, error_flag=error_flag,
              check_error_flag=check_error_flag)
 
 
