@@ -93,7 +93,7 @@ def _spec(name: str) -> Tuple[str, List[str]]:
 def _digest(source: str, flags: List[str]) -> str:
     h = hashlib.sha256()
     for path in [os.path.join(CSRC, source)] + sorted(
-            os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cuh")):
+            os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))):
         with open(path, "rb") as f:
             h.update(f.read())
     h.update(" ".join(ARCH_FLAGS + BASE_FLAGS + flags).encode())
