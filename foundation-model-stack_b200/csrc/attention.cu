@@ -401,3 +401,69 @@ FMS_API int fms_attention_decode(const void* q, void* out, int dtype, const void
   });
   return fms_launch_status("attention_decode");
 }
+
+// ---------------------------------------------------------------------------------------------------
+// The same decode attention for callers that cannot allocate: scratch inside the library image.
+// Declaration, limit and rules of use: attention_no_alloc.h.
+// ---------------------------------------------------------------------------------------------------
+#include "attention_no_alloc.h"
+
+#include <mutex>
+
+namespace {
+static __device__ __align__(256) unsigned char g_decode_scratch[FMS_NO_ALLOC_SCRATCH_BYTES];
+constexpr int MAX_DEVICES = 64;
+float* g_scratch_address[MAX_DEVICES] = {};  // per device, filled by the first call on that device
+std::mutex g_scratch_mutex;
+
+// The device address of g_decode_scratch on the current device; nullptr with fms_last_error() set.
+float* scratch_on_current_device() {
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess || device < 0 || device >= MAX_DEVICES) {
+    fms_fail("attention_decode_no_alloc: no usable current device (%s)", cudaGetErrorString(e));
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> guard(g_scratch_mutex);
+  if (g_scratch_address[device] == nullptr) {
+    void* address = nullptr;
+    e = cudaGetSymbolAddress(&address, g_decode_scratch);
+    if (e != cudaSuccess || address == nullptr) {
+      fms_fail("attention_decode_no_alloc: cudaGetSymbolAddress failed on device %d: %s", device, cudaGetErrorString(e));
+      return nullptr;
+    }
+    g_scratch_address[device] = static_cast<float*>(address);
+  }
+  return g_scratch_address[device];
+}
+}  // namespace
+
+FMS_API int fms_attention_decode_no_alloc(const void* q, void* out, int dtype, const void* keys, const void* values,
+                                          const int* table, int table_stride, int block_tokens, const int* slots,
+                                          const int* first_row, const int* len_after, int n_seqs, int n_splits,
+                                          int nheads, int kvheads, int head_dim, float scale, int window,
+                                          cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (check_args("attention_decode_no_alloc", nheads, kvheads, head_dim, block_tokens)) return 1;
+  if (n_splits <= 0 || n_splits > 65535) return fms_fail("attention_decode_no_alloc: %d splits", n_splits);
+  const size_t entries = (size_t)n_seqs * (size_t)nheads * (size_t)n_splits;
+  const size_t need = entries * (size_t)(HD + 2) * sizeof(float);
+  if (need > (size_t)FMS_NO_ALLOC_SCRATCH_BYTES)
+    return fms_fail("attention_decode_no_alloc: %d sequences x %d heads x %d splits need %zu bytes of scratch, the "
+                    "built-in array holds %u; use fms_attention_decode with scratch of your own",
+                    n_seqs, nheads, n_splits, need, (unsigned)FMS_NO_ALLOC_SCRATCH_BYTES);
+  float* scratch = scratch_on_current_device();
+  if (scratch == nullptr) return 1;
+  float* part_o = scratch;                  // [seqs, nheads, n_splits, HD]
+  float* part_ml = scratch + entries * HD;  // [seqs, nheads, n_splits, 2]
+  AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window};
+  const int group = nheads / kvheads;
+  const int chunks = (group + GC - 1) / GC;
+  if (kvheads * chunks > 65535 || nheads > 65535) return fms_fail("attention_decode_no_alloc: %d heads", nheads);
+  dim3 grid(n_seqs, kvheads * chunks, n_splits);
+  FMS_DISPATCH_DTYPE(dtype, T, {
+    attn_decode_kernel<T><<<grid, 128, 0, stream>>>(a, part_o, part_ml, n_splits);
+    attn_combine_kernel<T><<<dim3(n_seqs, nheads), HD >= 128 ? 128 : 64, 0, stream>>>(a, part_o, part_ml, n_splits);
+  });
+  return fms_launch_status("attention_decode_no_alloc");
+}
