@@ -171,7 +171,7 @@ def run_ours(args):
     def prefill(tokens, repeats=5):
         prompt = random_prompts([tokens], MODEL["vocab"], seed=7)
         ms = []
-        for i in range(3 + repeats):
+        for i in range(3 + repeats):  # three warm-up runs, then the timed ones
             (slot,) = engine.begin(1)
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
@@ -183,6 +183,14 @@ def run_ours(args):
                 ms.append(start.elapsed_time(end))
         return statistics.median(ms)
 
+    if args.only:  # a short run of one part, for profilers: prints that part's figures only
+        if args.only == "prefill":
+            print(json.dumps({"only": "prefill", "ms": round(prefill(PREFILL_TOKENS, repeats=args.steps), 3)}))
+        else:
+            batch = int(args.only.split("_b")[1])
+            v, ms, _, _ = device_decode(batch, args.steps, args.warmup)
+            print(json.dumps({"only": args.only, "value": round(v, 1), "ms_per_step": round(ms, 4)}))
+        return
     sampler = ClockSampler()
     sampler.start()
     value, ms_step, context, launched = device_decode(BATCH, args.steps, args.warmup)
@@ -308,6 +316,7 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--only", default="", help="decode_b<batch> or prefill: run and print that part only")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model's 32 (named in config)")
     args = ap.parse_args()
     if args.gpus != 1:

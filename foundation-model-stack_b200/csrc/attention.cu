@@ -346,11 +346,42 @@ __global__ void attn_combine_kernel(AttnArgs a, const float* __restrict__ part_o
   }
 }
 
+#include "attention_mma.cuh"
+
 int check_args(const char* what, int nheads, int kvheads, int head_dim, int block_tokens) {
   if (head_dim != HD) return fms_fail("%s: this library is built for head size %d, not %d", what, HD, head_dim);
   if (block_tokens != BLK) return fms_fail("%s: cache blocks of %d tokens, %d expected", what, block_tokens, BLK);
   if (nheads <= 0 || kvheads <= 0 || nheads % kvheads) return fms_fail("%s: %d heads over %d kv heads", what, nheads, kvheads);
   return 0;
+}
+
+// Launches the decode kernels (splits, then combine) with the given scratch.  float32: CUDA-core kernel;
+// bfloat16: tensor-core kernel.  Both entry points below go through here.
+int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, int n_splits, float* part_o,
+                  float* part_ml, cudaStream_t stream) {
+  if (n_splits <= 0 || n_splits > 65535) return fms_fail("%s: %d splits", what, n_splits);
+  const int group = a.nheads / a.kvheads;
+  if (a.nheads > 65535) return fms_fail("%s: %d heads", what, a.nheads);
+  if (dtype == FMS_F32) {
+    const int chunks = (group + GC - 1) / GC;
+    attn_decode_kernel<float><<<dim3(n_seqs, a.kvheads * chunks, n_splits), 128, 0, stream>>>(a, part_o, part_ml, n_splits);
+    attn_combine_kernel<float><<<dim3(n_seqs, a.nheads), HD >= 128 ? 128 : 64, 0, stream>>>(a, part_o, part_ml, n_splits);
+  } else if (dtype == FMS_BF16) {
+    constexpr int NW = HD <= 128 ? 4 : 2;
+    constexpr size_t smem = (size_t)NW * 2 * BLK * ROWB;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return fms_fail("%s: %zu bytes of shared memory refused: %s", what, smem, cudaGetErrorString(e));
+      configured = true;
+    }
+    const int chunks = (group + GROWS - 1) / GROWS;
+    attn_decode_mma_kernel<NW><<<dim3(n_seqs, a.kvheads * chunks, n_splits), NW * 32, smem, stream>>>(a, part_o, part_ml, n_splits);
+    attn_combine_kernel<__nv_bfloat16><<<dim3(n_seqs, a.nheads), HD >= 128 ? 128 : 64, 0, stream>>>(a, part_o, part_ml, n_splits);
+  } else {
+    return fms_fail("%s: unsupported dtype code %d", what, dtype);
+  }
+  return fms_launch_status(what);
 }
 }  // namespace
 
@@ -389,17 +420,8 @@ FMS_API int fms_attention_decode(const void* q, void* out, int dtype, const void
                                  cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (check_args("attention_decode", nheads, kvheads, head_dim, block_tokens)) return 1;
-  if (n_splits <= 0 || n_splits > 65535) return fms_fail("attention_decode: %d splits", n_splits);
   AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window};
-  const int group = nheads / kvheads;
-  const int chunks = (group + GC - 1) / GC;
-  if (kvheads * chunks > 65535 || nheads > 65535) return fms_fail("attention_decode: %d heads", nheads);
-  dim3 grid(n_seqs, kvheads * chunks, n_splits);
-  FMS_DISPATCH_DTYPE(dtype, T, {
-    attn_decode_kernel<T><<<grid, 128, 0, stream>>>(a, part_o, part_ml, n_splits);
-    attn_combine_kernel<T><<<dim3(n_seqs, nheads), HD >= 128 ? 128 : 64, 0, stream>>>(a, part_o, part_ml, n_splits);
-  });
-  return fms_launch_status("attention_decode");
+  return launch_decode("attention_decode", a, dtype, n_seqs, n_splits, part_o, part_ml, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -457,13 +479,5 @@ FMS_API int fms_attention_decode_no_alloc(const void* q, void* out, int dtype, c
   float* part_o = scratch;                  // [seqs, nheads, n_splits, HD]
   float* part_ml = scratch + entries * HD;  // [seqs, nheads, n_splits, 2]
   AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window};
-  const int group = nheads / kvheads;
-  const int chunks = (group + GC - 1) / GC;
-  if (kvheads * chunks > 65535 || nheads > 65535) return fms_fail("attention_decode_no_alloc: %d heads", nheads);
-  dim3 grid(n_seqs, kvheads * chunks, n_splits);
-  FMS_DISPATCH_DTYPE(dtype, T, {
-    attn_decode_kernel<T><<<grid, 128, 0, stream>>>(a, part_o, part_ml, n_splits);
-    attn_combine_kernel<T><<<dim3(n_seqs, nheads), HD >= 128 ? 128 : 64, 0, stream>>>(a, part_o, part_ml, n_splits);
-  });
-  return fms_launch_status("attention_decode_no_alloc");
+  return launch_decode("attention_decode_no_alloc", a, dtype, n_seqs, n_splits, part_o, part_ml, stream);
 }

@@ -1,0 +1,214 @@
+// bfloat16 attention on the tensor cores (mma.sync m16n8k16, float32 accumulation), included by attention.cu
+// inside its namespace after HD, BLK, SPLIT, AttnArgs.  Scores, softmax and the output accumulator are float32;
+// the probabilities are rounded to bfloat16 for the second product, as in every flash-attention kernel.
+#pragma once
+
+constexpr int ROWB = HD * 2 + 16;  // bytes of a key/value row in shared memory: padded, so that the eight rows
+                                   // of an 8x8 matrix (and of a fragment load) fall into different banks
+constexpr int PIECES = HD / 8;     // 16-byte pieces of a row
+
+__device__ __forceinline__ void mma16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, const void* smem_row) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;  // 0: the destination is filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait_group() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// A warp copies the 64 rows of one cache block (keys or values of one kv head) into its padded buffer.  Rows
+// outside [lo, hi) of the sequence are filled with zeros instead of being read.
+__device__ __forceinline__ void copy_block_async(unsigned char* dst, const __nv_bfloat16* src, int first_pos, int lo,
+                                                 int hi, int lane) {
+  for (int p = lane; p < BLK * PIECES; p += 32) {
+    const int row = p / PIECES, piece = p - row * PIECES;
+    const int pos = first_pos + row;
+    cp_async_16(dst + row * ROWB + piece * 16, src + (size_t)row * HD + piece * 8, pos >= lo && pos < hi);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// decode: grid (sequences, kv heads * head chunks, splits of 256 keys), NW warps.  The 16 rows of the mma tile
+// are up to 16 query heads that share the kv head.  Warp w takes the 64-key blocks w, w + NW, ... of the
+// split, each warp with a running softmax of its own; the warps' results are merged in shared memory and
+// written as one unnormalised partial result (m, l, o) per head, which attn_combine_kernel merges over splits.
+// ---------------------------------------------------------------------------------------------------
+constexpr int GROWS = 16;  // query heads per block (rows of the mma tile)
+
+template <int NW>
+__global__ void __launch_bounds__(NW * 32) attn_decode_mma_kernel(AttnArgs a, float* __restrict__ part_o,
+                                                                   float* __restrict__ part_ml, int n_splits) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+  const int seq = blockIdx.x, split = blockIdx.z;
+  const int group = a.nheads / a.kvheads;
+  const int chunks = (group + GROWS - 1) / GROWS;
+  const int kvh = blockIdx.y / chunks, chunk = blockIdx.y - kvh * chunks;
+  const int g0 = chunk * GROWS;
+  const int ng = min(GROWS, group - g0);
+  const int len = a.len_after[seq];
+  const int pos = len - 1;
+  const int kstart = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int k_lo = max(kstart, split * SPLIT), k_hi = min(len, (split + 1) * SPLIT);
+  if (k_lo >= k_hi) return;
+  const int slot = a.slots[seq];
+  const __nv_bfloat16* q = (const __nv_bfloat16*)a.q + (size_t)a.first_row[seq] * a.nheads * HD +
+                           (size_t)(kvh * group + g0) * HD;
+  const __nv_bfloat16* kc = (const __nv_bfloat16*)a.keys;
+  const __nv_bfloat16* vc = (const __nv_bfloat16*)a.values;
+  unsigned char* kbuf = smem_raw + (size_t)warp * 2 * BLK * ROWB;
+  unsigned char* vbuf = kbuf + BLK * ROWB;
+
+  // query fragments: rows g and g + 8 are heads g0 + g and g0 + g + 8 (zero beyond the group)
+  uint32_t qf[HD / 16][4];
+#pragma unroll
+  for (int s = 0; s < HD / 16; ++s) {
+    const uint32_t* r0 = reinterpret_cast<const uint32_t*>(q + (size_t)g * HD + 16 * s + 2 * c);
+    const uint32_t* r1 = reinterpret_cast<const uint32_t*>(q + (size_t)(g + 8) * HD + 16 * s + 2 * c);
+    qf[s][0] = g < ng ? r0[0] : 0u;
+    qf[s][1] = g + 8 < ng ? r1[0] : 0u;
+    qf[s][2] = g < ng ? r0[4] : 0u;
+    qf[s][3] = g + 8 < ng ? r1[4] : 0u;
+  }
+  float o[HD / 8][4];
+#pragma unroll
+  for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  for (int kb = k_lo / BLK + warp; kb * BLK < k_hi; kb += NW) {
+    const int blk = a.table[(size_t)slot * a.table_stride + kb];
+    if (blk < 0) continue;
+    __syncwarp();  // the buffers are free: every lane is past the previous block
+    copy_block_async(kbuf, kc + ((size_t)blk * a.kvheads + kvh) * BLK * HD, kb * BLK, k_lo, k_hi, lane);
+    cp_async_commit_group();
+    copy_block_async(vbuf, vc + ((size_t)blk * a.kvheads + kvh) * BLK * HD, kb * BLK, k_lo, k_hi, lane);
+    cp_async_commit_group();
+    cp_async_wait_group<1>();
+    __syncwarp();
+    // scores of 16 rows x 64 keys
+    float s[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      const unsigned char* krow = kbuf + (8 * j + g) * ROWB + 4 * c;
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + 32 * ks);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + 32 * ks + 16);
+        mma16816(s[j], qf[ks], b0, b1);
+      }
+    }
+    // element e of tile j: row g + 8 (e / 2), key 8 j + 2 c + (e % 2)
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int kpos = kb * BLK + 8 * j + 2 * c + (e & 1);
+        s[j][e] = (kpos >= k_lo && kpos < k_hi) ? s[j][e] * a.scale : -INFINITY;
+        tile_max[e >> 1] = fmaxf(tile_max[e >> 1], s[j][e]);
+      }
+    float alpha[2], psum[2] = {0.f, 0.f}, m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+      const float m_new = fmaxf(m[r], tile_max[r]);
+      m_use[r] = m_new == -INFINITY ? 0.f : m_new;
+      alpha[r] = m[r] == -INFINITY ? 0.f : expf(m[r] - m_use[r]);
+      m[r] = m_new;
+    }
+    uint32_t pf[4][4];  // probabilities as A fragments: k-step t covers keys 16 t .. 16 t + 15
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float p[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        p[e] = s[j][e] == -INFINITY ? 0.f : expf(s[j][e] - m_use[e >> 1]);
+        psum[e >> 1] += p[e];
+      }
+      pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
+      pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 1);
+      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 2);
+      l[r] = l[r] * alpha[r] + psum[r];
+    }
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) {
+      o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+    }
+    cp_async_wait_group<0>();
+    __syncwarp();
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const unsigned char* vrow = vbuf + (16 * t + (lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (lane >> 4) * 16;
+#pragma unroll
+      for (int jd = 0; jd < HD / 8; jd += 2) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, vrow + jd * 16);
+        mma16816(o[jd], pf[t], b[0], b[1]);
+        mma16816(o[jd + 1], pf[t], b[2], b[3]);
+      }
+    }
+  }
+
+  // merge the warps: each writes (m, l, o) of its 16 rows over its own key buffer
+  __syncwarp();
+  float* wo = reinterpret_cast<float*>(kbuf);          // [16][HD]
+  float* wml = reinterpret_cast<float*>(vbuf);         // [16][2]
+#pragma unroll
+  for (int j = 0; j < HD / 8; ++j) {
+    wo[g * HD + 8 * j + 2 * c] = o[j][0];
+    wo[g * HD + 8 * j + 2 * c + 1] = o[j][1];
+    wo[(g + 8) * HD + 8 * j + 2 * c] = o[j][2];
+    wo[(g + 8) * HD + 8 * j + 2 * c + 1] = o[j][3];
+  }
+  if (c == 0) {
+    wml[2 * g] = m[0]; wml[2 * g + 1] = l[0];
+    wml[2 * (g + 8)] = m[1]; wml[2 * (g + 8) + 1] = l[1];
+  }
+  __syncthreads();
+  for (int i = tid; i < ng * HD; i += NW * 32) {
+    const int r = i / HD, d = i - r * HD;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NW; ++w)
+      mm = fmaxf(mm, reinterpret_cast<const float*>(smem_raw + (size_t)w * 2 * BLK * ROWB + BLK * ROWB)[2 * r]);
+    float sum = 0.f, lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      const float* wm = reinterpret_cast<const float*>(smem_raw + (size_t)w * 2 * BLK * ROWB + BLK * ROWB);
+      const float* wv = reinterpret_cast<const float*>(smem_raw + (size_t)w * 2 * BLK * ROWB);
+      const float f = wm[2 * r] == -INFINITY ? 0.f : expf(wm[2 * r] - mm);
+      sum += wv[r * HD + d] * f;
+      lsum += wm[2 * r + 1] * f;
+    }
+    const int head = kvh * group + g0 + r;
+    const size_t at = ((size_t)seq * a.nheads + head) * n_splits + split;
+    part_o[at * HD + d] = sum;
+    if (d == 0) {
+      part_ml[at * 2] = mm;
+      part_ml[at * 2 + 1] = lsum;
+    }
+  }
+}

@@ -70,10 +70,99 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
   }
 }
 
+// The same for rows whose width is a multiple of 4 and at most 4 * NCHUNK * blockDim: each thread keeps its
+// part of the row in registers, all loads are issued before the first store, nothing is read twice.
+__device__ __forceinline__ void load4(const float* p, float* v) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float* v) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+  v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+}
+__device__ __forceinline__ void store4(float* p, const float* v) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float* v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 t;
+  t.x = *reinterpret_cast<uint32_t*>(&a);
+  t.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+
+template <typename T, typename TG, int NCHUNK>
+__global__ void add_rmsnorm_regs_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                        const TG* __restrict__ gain, float eps, T* __restrict__ out,
+                                        const int* __restrict__ rows, int dim) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* res = residual + (size_t)src * dim;
+  const T* del = delta ? delta + (size_t)src * dim : nullptr;
+  const int nvec = dim >> 2;
+  float x[NCHUNK][4], dl[NCHUNK][4], g[NCHUNK][4];
+#pragma unroll
+  for (int j = 0; j < NCHUNK; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    if (c < nvec) {
+      load4(res + 4 * c, x[j]);
+      if (del) load4(del + 4 * c, dl[j]);
+      load4(gain + 4 * c, g[j]);
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < NCHUNK; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    if (c < nvec) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (del) x[j][e] += dl[j][e];
+        ss += x[j][e] * x[j][e];
+      }
+      if (del && rows == nullptr) store4(res + 4 * c, x[j]);
+    }
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = rsqrtf(total / (float)dim + eps);
+  T* o = out + (size_t)r * dim;
+#pragma unroll
+  for (int j = 0; j < NCHUNK; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    if (c < nvec) {
+      float y[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) y[e] = g[j][e] * (x[j][e] * inv);
+      store4(o + 4 * c, y);
+    }
+  }
+}
+
 FMS_API int fms_add_rmsnorm(float* residual, const void* delta, const void* gain, int gain_dtype, float eps, void* out,
                             int dtype, const int* rows, int n_rows, int dim, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (dim <= 0) return fms_fail("add_rmsnorm: dim %d", dim);
+  if (dim % 4 == 0 && dim <= 4 * 4 * 1024) {
+    // up to 4 chunks of 4 values per thread; few rows: more threads per row, so that each has one chunk
+    const int nvec = dim / 4;
+    int threads = 128;
+    while (threads < 1024 && threads * (n_rows <= 64 ? 1 : 4) < nvec) threads *= 2;
+    const int nchunk = (nvec + threads - 1) / threads;
+    FMS_DISPATCH_DTYPE(dtype, T, FMS_DISPATCH_DTYPE(gain_dtype, TG, {
+      if (nchunk <= 1)
+        add_rmsnorm_regs_kernel<T, TG, 1><<<n_rows, threads, 0, stream>>>(residual, (const T*)delta, (const TG*)gain,
+                                                                          eps, (T*)out, rows, dim);
+      else if (nchunk <= 2)
+        add_rmsnorm_regs_kernel<T, TG, 2><<<n_rows, threads, 0, stream>>>(residual, (const T*)delta, (const TG*)gain,
+                                                                          eps, (T*)out, rows, dim);
+      else
+        add_rmsnorm_regs_kernel<T, TG, 4><<<n_rows, threads, 0, stream>>>(residual, (const T*)delta, (const TG*)gain,
+                                                                          eps, (T*)out, rows, dim);
+    }));
+    return fms_launch_status("add_rmsnorm");
+  }
   const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
   FMS_DISPATCH_DTYPE(dtype, T, FMS_DISPATCH_DTYPE(gain_dtype, TG,
                      (add_rmsnorm_kernel<T, TG><<<n_rows, threads, 0, stream>>>(

@@ -81,6 +81,8 @@ class Engine:
         tensors = self.decoder.state_dict().values()
         if self.decoder.dtype == torch.float32 or any(t.dtype == torch.float32 and t.dim() == 2 for t in tensors):
             names.append("gemm_f32")
+        if self.decoder.dtype == torch.bfloat16:
+            names.append("gemm_bf16_skinny")
         for block in self.decoder.blocks:
             hd = getattr(block.mixer, "head_dim", None)
             if hd and getattr(block.mixer, "kvheads", None):

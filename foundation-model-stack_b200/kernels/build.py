@@ -29,6 +29,7 @@ BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-shared"
 PLAIN_LIBRARIES = {
     "elementwise": ("elementwise.cu", []),
     "gemm_f32": ("gemm_f32.cu", []),
+    "gemm_bf16_skinny": ("gemm_bf16_skinny.cu", []),
     "sampling": ("sampling.cu", []),
 }
 

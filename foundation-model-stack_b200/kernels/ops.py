@@ -27,6 +27,8 @@ _SIGNATURES = {
     "fms_rope_store": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "fms_decode_advance": [_P, _P, _I, _P],
     "fms_gemm_f32": [_P, _P, _P, _P, _I, _I, _I, _P],
+    "fms_linear_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "fms_glu_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "fms_argmax": [_P, _P, _I, _I, _P],
     "fms_sample": [_P, _P, _I, _I, _F, _I, _U64, _P, _I, _P],
     "fms_attention_prefill": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
@@ -150,6 +152,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         return y if out_dtype == torch.float32 else y.to(out_dtype)
     if weight.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
         raise KernelError(f"linear: x {x.dtype}, weight {weight.dtype}")
+    if x.shape[0] <= SKINNY_ROWS and weight.shape[1] % 8 == 0 and (bias is None or bias.dtype == torch.bfloat16):
+        # few rows (decode): the weight-streaming tensor-core kernel
+        y = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
+        _call("gemm_bf16_skinny", "fms_linear_bf16_skinny", _ptr(x), _ptr(weight), _ptr(bias), _ptr(y), _code(out_dtype),
+              x.shape[0], weight.shape[0], weight.shape[1], _stream())
+        return y
     if out_dtype == torch.float32:
         y = torch.mm(x, weight.t(), out_dtype=torch.float32)
         return y if bias is None else y + bias.float()
@@ -157,7 +165,24 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return torch.nn.functional.linear(x, weight, b)
 
 
+SKINNY_ROWS = 16  # rows up to which the weight-streaming kernels are used
+
+
 # ---- feed-forward ------------------------------------------------------------------------------------
+def gated_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], activation: int) -> torch.Tensor:
+    """act(x Wg^T) * (x Wu^T) for weight = [Wg; Wu]: one kernel for few bfloat16 rows, else the product
+    followed by ``gated_activation``."""
+    hidden = weight.shape[0] // 2
+    if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_ROWS
+            and weight.shape[1] % 8 == 0 and (bias is None or bias.dtype == torch.bfloat16)):
+        _ptr(x), _ptr(weight)
+        y = torch.empty((x.shape[0], hidden), dtype=torch.bfloat16, device=x.device)
+        _call("gemm_bf16_skinny", "fms_glu_bf16_skinny", _ptr(x), _ptr(weight), _ptr(bias), _ptr(y), x.shape[0], hidden,
+              weight.shape[1], int(activation), _stream())
+        return y
+    return gated_activation(linear(x, weight, bias), activation)
+
+
 def gated_activation(gate_up: torch.Tensor, activation: int) -> torch.Tensor:
     """act(gate) * up for rows [gate | up]."""
     n, two_f = gate_up.shape

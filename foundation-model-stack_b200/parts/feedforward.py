@@ -30,8 +30,8 @@ class GatedLinearUnit(Part):
         self.down = self.add("w2", Linear(spec.hidden, spec.dim, spec.bias))
 
     def forward(self, x):
-        gu = self.gate_up.forward(x)
-        return self.down.forward(ops.gated_activation(gu, self.activation))
+        h = ops.gated_linear(x, self.gate_up.tensor("weight"), self.gate_up.tensor("bias"), self.activation)
+        return self.down.forward(h)
 
 
 register_feed_forward("glu", GatedLinearUnit)

@@ -47,6 +47,10 @@ def gated_activation(gate_up, activation):
     return (act(g) * u).to(gate_up.dtype)
 
 
+def gated_linear(x, weight, bias, activation):
+    return gated_activation(linear(x, weight, bias), activation)
+
+
 def rope_store(qkv, inv_freq, batch, view, nheads, kvheads, head_dim, writes_cache=True):
     n = qkv.shape[0]
     x = qkv.float().view(n, nheads + 2 * kvheads, head_dim)
@@ -132,7 +136,7 @@ def check_error_flag(device):
     return None
 
 
-PLAIN = dict(embed=embed, add_rmsnorm=add_rmsnorm, linear=linear, gated_activation=gated_activation,
+PLAIN = dict(embed=embed, add_rmsnorm=add_rmsnorm, linear=linear, gated_activation=gated_activation, gated_linear=gated_linear,
              rope_store=rope_store, attention=attention, decode_advance=decode_advance, argmax=argmax, sample=sample, error_flag=error_flag,
              check_error_flag=check_error_flag)
 

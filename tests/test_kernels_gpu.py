@@ -101,6 +101,44 @@ def test_linear_bfloat16(ops, m, n, k):
     torch.testing.assert_close(got32.double(), want, atol=1e-3, rtol=1e-3)
 
 
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(331, 240), (40, 8), (4096 + 16, 1000), (16400, 96)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_linear_bfloat16_few_rows(ops, m, n, k, out_dtype):
+    """The weight-streaming kernel of decode steps: odd numbers of weight rows, K that is no multiple of 32,
+    one to sixteen batch rows, with and without bias."""
+    g = torch.Generator().manual_seed(40 + m)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    b = torch.randn(n, generator=g).to(torch.bfloat16).cuda()
+    for bias in (None, b):
+        got = ops.linear(x, w, bias, out_dtype)
+        want = P.linear(x, w, bias, torch.float64)
+        assert got.dtype == out_dtype and got.shape == (m, n)
+        t = dict(atol=2e-2, rtol=2e-2) if out_dtype == torch.bfloat16 else dict(atol=1e-3, rtol=1e-3)
+        torch.testing.assert_close(got.double(), want, **t)
+    # a row's result does not depend on how many other rows there are
+    alone = ops.linear(x[:1].contiguous(), w, None, out_dtype)
+    assert torch.equal(alone[0], ops.linear(x, w, None, out_dtype)[0])
+
+
+@pytest.mark.parametrize("m", [1, 8, 13])
+@pytest.mark.parametrize("hidden,k", [(176, 64), (328, 240), (1000, 96), (14336, 128)])
+@pytest.mark.parametrize("act", [0, 2])
+def test_gated_linear_few_rows(ops, m, hidden, k, act):
+    g = torch.Generator().manual_seed(50 + m)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(2 * hidden, k, generator=g) * 0.1).to(torch.bfloat16).cuda()
+    got = ops.gated_linear(x, w, None, act)
+    want = P.gated_activation(P.linear(x, w, None, torch.float32), act)
+    assert got.dtype == torch.bfloat16 and got.shape == (m, hidden)
+    torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
+    # many rows take the product and the activation as two kernels: the same values up to rounding
+    x2 = torch.randn(40, k, generator=g).to(torch.bfloat16).cuda()
+    torch.testing.assert_close(ops.gated_linear(x2, w, None, act).float(),
+                               P.gated_activation(P.linear(x2, w, None, torch.float32), act), atol=3e-2, rtol=3e-2)
+
+
 def test_linear_float32_matrix_in_a_bfloat16_model(ops):
     g = torch.Generator().manual_seed(5)
     x = torch.randn(4, 96, generator=g).to(torch.bfloat16).cuda()
