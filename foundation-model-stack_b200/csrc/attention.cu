@@ -387,7 +387,11 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
 
 FMS_API int fms_attn_head_dim() { return HD; }
 FMS_API int fms_attn_split_tokens() { return SPLIT; }
-FMS_API int fms_attn_prefill_tile_rows() { return TQ; }
+// Positions of one sequence that a prefill block takes (the host cuts the new tokens into such tiles).
+FMS_API int fms_attn_prefill_tile_positions(int dtype, int nheads, int kvheads) {
+  if (dtype == FMS_BF16 && kvheads > 0 && nheads % kvheads == 0) return prefill_positions_per_block(nheads / kvheads);
+  return TQ;
+}
 
 FMS_API int fms_attention_prefill(const void* q, void* out, int dtype, const void* keys, const void* values,
                                   const int* table, int table_stride, int block_tokens, const int* slots,
@@ -397,18 +401,29 @@ FMS_API int fms_attention_prefill(const void* q, void* out, int dtype, const voi
   if (n_tiles <= 0) return 0;
   if (check_args("attention_prefill", nheads, kvheads, head_dim, block_tokens)) return 1;
   AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window};
-  const size_t smem = (size_t)(TQ * (HD + 1) + BLK * (HD + 1) + BLK * HD + TQ * (BLK + 1)) * sizeof(float);
-  dim3 grid(n_tiles, nheads);
   if (nheads > 65535) return fms_fail("attention_prefill: %d heads", nheads);
-  FMS_DISPATCH_DTYPE(dtype, T, {
+  if (dtype == FMS_BF16) {
+    constexpr size_t smem = (size_t)2 * 2 * BLK * ROWB;
     static bool configured = false;
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return fms_fail("attention_prefill: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e));
       configured = true;
     }
-    attn_prefill_kernel<T><<<grid, 128, smem, stream>>>(a, tiles);
-  });
+    const int group = nheads / kvheads;
+    const int gh = prefill_heads_per_block(group);
+    attn_prefill_mma_kernel<<<dim3(n_tiles, kvheads * ((group + gh - 1) / gh)), PF_WARPS * 32, smem, stream>>>(a, tiles);
+    return fms_launch_status("attention_prefill");
+  }
+  if (dtype != FMS_F32) return fms_fail("attention_prefill: unsupported dtype code %d", dtype);
+  const size_t smem = (size_t)(TQ * (HD + 1) + BLK * (HD + 1) + BLK * HD + TQ * (BLK + 1)) * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fms_fail("attention_prefill: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  attn_prefill_kernel<float><<<dim3(n_tiles, nheads), 128, smem, stream>>>(a, tiles);
   return fms_launch_status("attention_prefill");
 }
 

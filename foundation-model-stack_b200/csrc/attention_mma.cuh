@@ -212,3 +212,176 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_mma_kernel(AttnArgs a, fl
     }
   }
 }
+
+// ---------------------------------------------------------------------------------------------------
+// prefill: grid (query tiles, kv heads * head chunks), 4 warps.  The 64 rows of a block are P positions x GH
+// query heads that share the kv head (row = position * GH + head; GH = min(group, 64), P = 64 / GH), so a key
+// or value block is loaded once for all of them.  Each warp owns 16 rows; the warps share the key and value
+// blocks, which are copied into shared memory two blocks ahead of use (cp.async, two stages).
+// ---------------------------------------------------------------------------------------------------
+constexpr int PF_WARPS = 4;
+constexpr int PF_ROWS = 16 * PF_WARPS;
+
+__host__ __device__ inline int prefill_heads_per_block(int group) { return group < PF_ROWS ? group : PF_ROWS; }
+__host__ __device__ inline int prefill_positions_per_block(int group) { return PF_ROWS / prefill_heads_per_block(group); }
+
+__global__ void __launch_bounds__(PF_WARPS * 32) attn_prefill_mma_kernel(AttnArgs a, const int* __restrict__ tiles) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+  const int group = a.nheads / a.kvheads;
+  const int gh = prefill_heads_per_block(group), pp = PF_ROWS / gh;
+  const int chunks = (group + gh - 1) / gh;
+  const int kvh = blockIdx.y / chunks, g0 = (blockIdx.y - kvh * chunks) * gh;
+  const int ng = min(gh, group - g0);
+  const int seq = tiles[2 * blockIdx.x], r0 = tiles[2 * blockIdx.x + 1];
+  const int row_begin = a.first_row[seq];
+  const int n_new = a.first_row[seq + 1] - row_begin;
+  const int len = a.len_after[seq];
+  const int len_before = len - n_new;
+  const int slot = a.slots[seq];
+  const int pos_here = min(pp, n_new - r0);       // positions of this tile
+  const int p_first = len_before + r0, p_last = p_first + pos_here - 1;
+  const __nv_bfloat16* q = (const __nv_bfloat16*)a.q;
+  const __nv_bfloat16* kc = (const __nv_bfloat16*)a.keys;
+  const __nv_bfloat16* vc = (const __nv_bfloat16*)a.values;
+
+  // the two rows of this lane: tile row -> (position index, head index)
+  int row_pos[2];
+  bool row_ok[2];
+  const __nv_bfloat16* qrow[2];
+  __nv_bfloat16* orow[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = warp * 16 + g + 8 * h;
+    const int pi = r / gh, gi = r - pi * gh;
+    row_ok[h] = pi < pos_here && gi < ng;
+    row_pos[h] = p_first + pi;
+    const size_t at = ((size_t)(row_begin + r0 + (row_ok[h] ? pi : 0)) * a.nheads + kvh * group + g0 + (row_ok[h] ? gi : 0)) * HD;
+    qrow[h] = q + at;
+    orow[h] = (__nv_bfloat16*)a.out + at;
+  }
+  uint32_t qf[HD / 16][4];
+#pragma unroll
+  for (int s = 0; s < HD / 16; ++s) {
+    const uint32_t* q0 = reinterpret_cast<const uint32_t*>(qrow[0] + 16 * s + 2 * c);
+    const uint32_t* q1 = reinterpret_cast<const uint32_t*>(qrow[1] + 16 * s + 2 * c);
+    qf[s][0] = row_ok[0] ? q0[0] : 0u;
+    qf[s][1] = row_ok[1] ? q1[0] : 0u;
+    qf[s][2] = row_ok[0] ? q0[4] : 0u;
+    qf[s][3] = row_ok[1] ? q1[4] : 0u;
+  }
+  float o[HD / 8][4];
+#pragma unroll
+  for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  const int kb_lo = a.window > 0 ? max(0, p_first - a.window + 1) / BLK : 0;
+  const int kb_hi = p_last / BLK;
+  const int nblocks = kb_hi - kb_lo + 1;
+  constexpr int STAGE = 2 * BLK * ROWB;
+  auto issue = [&](int i) {  // copies block kb_lo + i into stage i % 2 (all threads take part)
+    if (i < nblocks) {
+      const int kb = kb_lo + i;
+      const int blk = a.table[(size_t)slot * a.table_stride + kb];
+      unsigned char* kbuf = smem_raw + (size_t)(i & 1) * STAGE;
+      unsigned char* vbuf = kbuf + BLK * ROWB;
+      const __nv_bfloat16* ksrc = kc + ((size_t)max(blk, 0) * a.kvheads + kvh) * BLK * HD;
+      const __nv_bfloat16* vsrc = vc + ((size_t)max(blk, 0) * a.kvheads + kvh) * BLK * HD;
+      for (int p = tid; p < BLK * PIECES; p += PF_WARPS * 32) {
+        const int row = p / PIECES, piece = p - row * PIECES;
+        const bool valid = blk >= 0 && kb * BLK + row < len;
+        cp_async_16(kbuf + row * ROWB + piece * 16, ksrc + (size_t)row * HD + piece * 8, valid);
+        cp_async_16(vbuf + row * ROWB + piece * 16, vsrc + (size_t)row * HD + piece * 8, valid);
+      }
+    }
+    cp_async_commit_group();
+  };
+  issue(0);
+  issue(1);
+  for (int i = 0; i < nblocks; ++i) {
+    const int kb = kb_lo + i;
+    cp_async_wait_group<1>();
+    __syncthreads();
+    const unsigned char* kbuf = smem_raw + (size_t)(i & 1) * STAGE;
+    const unsigned char* vbuf = kbuf + BLK * ROWB;
+    float s[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      const unsigned char* krow = kbuf + (8 * j + g) * ROWB + 4 * c;
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + 32 * ks);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + 32 * ks + 16);
+        mma16816(s[j], qf[ks], b0, b1);
+      }
+    }
+    // a block that every row of the tile sees whole needs no mask
+    const bool whole = kb * BLK + BLK - 1 <= p_first && (a.window <= 0 || kb * BLK > p_last - a.window);
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1;
+        const int kpos = kb * BLK + 8 * j + 2 * c + (e & 1);
+        const bool visible = whole || (kpos <= row_pos[h] && (a.window <= 0 || kpos > row_pos[h] - a.window));
+        s[j][e] = (visible && row_ok[h]) ? s[j][e] * a.scale : -INFINITY;
+        tile_max[h] = fmaxf(tile_max[h], s[j][e]);
+      }
+    float alpha[2], psum[2] = {0.f, 0.f}, m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+      const float m_new = fmaxf(m[r], tile_max[r]);
+      m_use[r] = m_new == -INFINITY ? 0.f : m_new;
+      alpha[r] = m[r] == -INFINITY ? 0.f : expf(m[r] - m_use[r]);
+      m[r] = m_new;
+    }
+    uint32_t pf[4][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float p[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        p[e] = s[j][e] == -INFINITY ? 0.f : expf(s[j][e] - m_use[e >> 1]);
+        psum[e >> 1] += p[e];
+      }
+      pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
+      pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 1);
+      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 2);
+      l[r] = l[r] * alpha[r] + psum[r];
+    }
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) {
+      o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const unsigned char* vrow = vbuf + (16 * t + (lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (lane >> 4) * 16;
+#pragma unroll
+      for (int jd = 0; jd < HD / 8; jd += 2) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, vrow + jd * 16);
+        mma16816(o[jd], pf[t], b[0], b[1]);
+        mma16816(o[jd + 1], pf[t], b[2], b[3]);
+      }
+    }
+    __syncthreads();  // every warp is done with this stage
+    issue(i + 2);
+  }
+  cp_async_wait_group<0>();
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (!row_ok[h]) continue;
+    const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j)
+      *reinterpret_cast<uint32_t*>(orow[h] + 8 * j + 2 * c) = pack_bf16(o[j][2 * h] * inv, o[j][2 * h + 1] * inv);
+  }
+}

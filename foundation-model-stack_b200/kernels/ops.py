@@ -216,12 +216,14 @@ def _attention_library(head_dim: int) -> str:
 _attn_constants = {}
 
 
-def attention_constants(head_dim: int):
-    """(keys per decode split, query rows per prefill tile) of the library built for this head size."""
-    if head_dim not in _attn_constants:
+def attention_constants(head_dim: int, dtype: torch.dtype, nheads: int, kvheads: int):
+    """(keys per decode split, positions per prefill tile) of the library built for this head size."""
+    key = (head_dim, dtype, nheads, kvheads)
+    if key not in _attn_constants:
         lib = load_library(_attention_library(head_dim))
-        _attn_constants[head_dim] = (int(lib.fms_attn_split_tokens()), int(lib.fms_attn_prefill_tile_rows()))
-    return _attn_constants[head_dim]
+        _attn_constants[key] = (int(lib.fms_attn_split_tokens()),
+                                int(lib.fms_attn_prefill_tile_positions(_code(dtype), nheads, kvheads)))
+    return _attn_constants[key]
 
 
 def attention(q: torch.Tensor, batch, view, nheads: int, kvheads: int, head_dim: int, scale: float,
@@ -230,7 +232,7 @@ def attention(q: torch.Tensor, batch, view, nheads: int, kvheads: int, head_dim:
     keys and values).  One query per sequence takes the split-key decode kernels, else the prefill kernel."""
     out = torch.empty_like(q)
     lib = _attention_library(head_dim)
-    split, tile_rows = attention_constants(head_dim)
+    split, tile_rows = attention_constants(head_dim, q.dtype, nheads, kvheads)
     common = (_ptr(q), _ptr(out), _code(q.dtype), _ptr(view.keys), _ptr(view.values), _ptr(view.table),
               view.table.shape[1], view.block_tokens, _ptr(batch.slots), _ptr(batch.first_row), _ptr(batch.len_after))
     if batch.decode:
