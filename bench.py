@@ -136,17 +136,18 @@ def run_ours(args):
         prompts = random_prompts(lengths, MODEL["vocab"])
         slots = engine.begin(batch)
         try:
+            horizon = max(lengths) + max(3, warmup) + steps + 1
             logits = engine.step(slots, prompts)
             tokens = ops.argmax(logits)
             for _ in range(max(3, warmup)):
-                tokens = ops.argmax(engine.decode(slots, tokens_device=tokens))
+                tokens = ops.argmax(engine.decode(slots, tokens_device=tokens, horizon=horizon))
             torch.cuda.synchronize()
             context = sum(engine.length(s) for s in slots) + batch * (steps + 1) / 2.0
             launches0, graphs0 = ops.launches, engine.graph_launches
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
             for _ in range(steps):
-                tokens = ops.argmax(engine.decode(slots, tokens_device=tokens))
+                tokens = ops.argmax(engine.decode(slots, tokens_device=tokens, horizon=horizon))
             end.record()
             torch.cuda.synchronize()
             ms = start.elapsed_time(end)

@@ -367,16 +367,22 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
     attn_decode_kernel<float><<<dim3(n_seqs, a.kvheads * chunks, n_splits), 128, 0, stream>>>(a, part_o, part_ml, n_splits);
     attn_combine_kernel<float><<<dim3(n_seqs, a.nheads), HD >= 128 ? 128 : 64, 0, stream>>>(a, part_o, part_ml, n_splits);
   } else if (dtype == FMS_BF16) {
-    constexpr int NW = HD <= 128 ? 4 : 2;
-    constexpr size_t smem = (size_t)NW * 2 * BLK * ROWB;
-    static bool configured = false;
-    if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return fms_fail("%s: %zu bytes of shared memory refused: %s", what, smem, cudaGetErrorString(e));
-      configured = true;
-    }
+    // Few (sequence, kv head) pairs: four warps share a split, each with one block of 64 keys in flight, which
+    // is quickest when the GPU is not full.  Many: one warp per block with a small footprint, so that several
+    // blocks of threads fit on a multiprocessor and one's loads overlap another's arithmetic.
     const int chunks = (group + GROWS - 1) / GROWS;
-    attn_decode_mma_kernel<NW><<<dim3(n_seqs, a.kvheads * chunks, n_splits), NW * 32, smem, stream>>>(a, part_o, part_ml, n_splits);
+    const long units = (long)n_seqs * a.kvheads * chunks;
+    const int nw = units >= 256 ? 1 : (units >= 96 || HD > 128 ? 2 : 4);
+    const size_t smem = (size_t)nw * 2 * BLK * ROWB;
+    auto kernel = nw == 1 ? attn_decode_mma_kernel<1> : (nw == 2 ? attn_decode_mma_kernel<2> : attn_decode_mma_kernel<4>);
+    static bool configured[3] = {false, false, false};
+    const int slot = nw == 1 ? 0 : (nw == 2 ? 1 : 2);
+    if (!configured[slot]) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return fms_fail("%s: %zu bytes of shared memory refused: %s", what, smem, cudaGetErrorString(e));
+      configured[slot] = true;
+    }
+    kernel<<<dim3(n_seqs, a.kvheads * chunks, n_splits), nw * 32, smem, stream>>>(a, part_o, part_ml, n_splits);
     attn_combine_kernel<__nv_bfloat16><<<dim3(n_seqs, a.nheads), HD >= 128 ? 128 : 64, 0, stream>>>(a, part_o, part_ml, n_splits);
   } else {
     return fms_fail("%s: unsupported dtype code %d", what, dtype);

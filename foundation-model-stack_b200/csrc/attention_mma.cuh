@@ -8,7 +8,7 @@ constexpr int ROWB = HD * 2 + 16;  // bytes of a key/value row in shared memory:
 constexpr int PIECES = HD / 8;     // 16-byte pieces of a row
 
 __device__ __forceinline__ void mma16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -19,6 +19,37 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, const void* smem_
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(addr));
 }
+// Four 8x8 matrices, not transposed: lane l gives the address of row (l & 7) of matrix (l >> 3).
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* smem_row) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+// Scores of a warp's 16 query rows against the 64 keys of a block in shared memory: s[j] is the 16 x 8 tile of
+// keys 8 j .. 8 j + 7.  Consecutive mma go to different tiles, so that none waits for the one before.
+__device__ __forceinline__ void scores_16x64(float (*s)[4], const uint32_t (*qf)[4], const unsigned char* kbuf, int lane) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+  const unsigned char* base = kbuf + (lane & 7) * ROWB + (lane >> 3) * 16;
+#pragma unroll
+  for (int ks = 0; ks < HD / 16; ks += 2) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      uint32_t b[4];  // keys 8 j .. 8 j + 7: (b[0], b[1]) for k-step ks, (b[2], b[3]) for k-step ks + 1
+      if (ks + 1 < HD / 16) {
+        ldmatrix_x4(b, base + 8 * j * ROWB + 32 * ks);
+        mma16816(s[j], qf[ks], b[0], b[1]);
+        mma16816(s[j], qf[ks + 1 < HD / 16 ? ks + 1 : ks], b[2], b[3]);
+      } else {  // an odd number of k-steps: the last one alone
+        const unsigned char* krow = kbuf + (8 * j + (lane >> 2)) * ROWB + 4 * (lane & 3) + 32 * ks;
+        mma16816(s[j], qf[ks], *reinterpret_cast<const uint32_t*>(krow), *reinterpret_cast<const uint32_t*>(krow + 16));
+      }
+    }
+  }
+}
+constexpr float LOG2E = 1.4426950408889634f;
+
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
   const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem);
   const int bytes = valid ? 16 : 0;  // 0: the destination is filled with zeros
@@ -90,7 +121,8 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_mma_kernel(AttnArgs a, fl
   float o[HD / 8][4];
 #pragma unroll
   for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};  // running maximum in units of log2, and sum
+  const float scale2 = a.scale * LOG2E;  // scores are kept times log2(e): exp(x) = exp2(x log2 e)
 
   for (int kb = k_lo / BLK + warp; kb * BLK < k_hi; kb += NW) {
     const int blk = a.table[(size_t)slot * a.table_stride + kb];
@@ -104,17 +136,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_mma_kernel(AttnArgs a, fl
     __syncwarp();
     // scores of 16 rows x 64 keys
     float s[8][4];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-      const unsigned char* krow = kbuf + (8 * j + g) * ROWB + 4 * c;
-#pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks) {
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + 32 * ks);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + 32 * ks + 16);
-        mma16816(s[j], qf[ks], b0, b1);
-      }
-    }
+    scores_16x64(s, qf, kbuf, lane);
     // element e of tile j: row g + 8 (e / 2), key 8 j + 2 c + (e % 2)
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -122,7 +144,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_mma_kernel(AttnArgs a, fl
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int kpos = kb * BLK + 8 * j + 2 * c + (e & 1);
-        s[j][e] = (kpos >= k_lo && kpos < k_hi) ? s[j][e] * a.scale : -INFINITY;
+        s[j][e] = (kpos >= k_lo && kpos < k_hi) ? s[j][e] * scale2 : -INFINITY;
         tile_max[e >> 1] = fmaxf(tile_max[e >> 1], s[j][e]);
       }
     float alpha[2], psum[2] = {0.f, 0.f}, m_use[2];
@@ -132,7 +154,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_mma_kernel(AttnArgs a, fl
       tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
       const float m_new = fmaxf(m[r], tile_max[r]);
       m_use[r] = m_new == -INFINITY ? 0.f : m_new;
-      alpha[r] = m[r] == -INFINITY ? 0.f : expf(m[r] - m_use[r]);
+      alpha[r] = m[r] == -INFINITY ? 0.f : exp2f(m[r] - m_use[r]);
       m[r] = m_new;
     }
     uint32_t pf[4][4];  // probabilities as A fragments: k-step t covers keys 16 t .. 16 t + 15
@@ -141,7 +163,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_mma_kernel(AttnArgs a, fl
       float p[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        p[e] = s[j][e] == -INFINITY ? 0.f : expf(s[j][e] - m_use[e >> 1]);
+        p[e] = s[j][e] == -INFINITY ? 0.f : exp2f(s[j][e] - m_use[e >> 1]);
         psum[e >> 1] += p[e];
       }
       pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
@@ -199,7 +221,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_mma_kernel(AttnArgs a, fl
     for (int w = 0; w < NW; ++w) {
       const float* wm = reinterpret_cast<const float*>(smem_raw + (size_t)w * 2 * BLK * ROWB + BLK * ROWB);
       const float* wv = reinterpret_cast<const float*>(smem_raw + (size_t)w * 2 * BLK * ROWB);
-      const float f = wm[2 * r] == -INFINITY ? 0.f : expf(wm[2 * r] - mm);
+      const float f = wm[2 * r] == -INFINITY ? 0.f : exp2f(wm[2 * r] - mm);
       sum += wv[r * HD + d] * f;
       lsum += wm[2 * r + 1] * f;
     }
@@ -207,7 +229,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_mma_kernel(AttnArgs a, fl
     const size_t at = ((size_t)seq * a.nheads + head) * n_splits + split;
     part_o[at * HD + d] = sum;
     if (d == 0) {
-      part_ml[at * 2] = mm;
+      part_ml[at * 2] = mm * (1.f / LOG2E);  // back to natural units, which attn_combine_kernel expects
       part_ml[at * 2 + 1] = lsum;
     }
   }
@@ -273,7 +295,8 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attn_prefill_mma_kernel(AttnArg
   float o[HD / 8][4];
 #pragma unroll
   for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};  // running maximum in units of log2, and sum
+  const float scale2 = a.scale * LOG2E;  // scores are kept times log2(e): exp(x) = exp2(x log2 e)
 
   const int kb_lo = a.window > 0 ? max(0, p_first - a.window + 1) / BLK : 0;
   const int kb_hi = p_last / BLK;
@@ -305,17 +328,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attn_prefill_mma_kernel(AttnArg
     const unsigned char* kbuf = smem_raw + (size_t)(i & 1) * STAGE;
     const unsigned char* vbuf = kbuf + BLK * ROWB;
     float s[8][4];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-      const unsigned char* krow = kbuf + (8 * j + g) * ROWB + 4 * c;
-#pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks) {
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + 32 * ks);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + 32 * ks + 16);
-        mma16816(s[j], qf[ks], b0, b1);
-      }
-    }
+    scores_16x64(s, qf, kbuf, lane);
     // a block that every row of the tile sees whole needs no mask
     const bool whole = kb * BLK + BLK - 1 <= p_first && (a.window <= 0 || kb * BLK > p_last - a.window);
     float tile_max[2] = {-INFINITY, -INFINITY};
@@ -326,7 +339,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attn_prefill_mma_kernel(AttnArg
         const int h = e >> 1;
         const int kpos = kb * BLK + 8 * j + 2 * c + (e & 1);
         const bool visible = whole || (kpos <= row_pos[h] && (a.window <= 0 || kpos > row_pos[h] - a.window));
-        s[j][e] = (visible && row_ok[h]) ? s[j][e] * a.scale : -INFINITY;
+        s[j][e] = (visible && row_ok[h]) ? s[j][e] * scale2 : -INFINITY;
         tile_max[h] = fmaxf(tile_max[h], s[j][e]);
       }
     float alpha[2], psum[2] = {0.f, 0.f}, m_use[2];
@@ -336,7 +349,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attn_prefill_mma_kernel(AttnArg
       tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
       const float m_new = fmaxf(m[r], tile_max[r]);
       m_use[r] = m_new == -INFINITY ? 0.f : m_new;
-      alpha[r] = m[r] == -INFINITY ? 0.f : expf(m[r] - m_use[r]);
+      alpha[r] = m[r] == -INFINITY ? 0.f : exp2f(m[r] - m_use[r]);
       m[r] = m_new;
     }
     uint32_t pf[4][4];
@@ -345,7 +358,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attn_prefill_mma_kernel(AttnArg
       float p[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        p[e] = s[j][e] == -INFINITY ? 0.f : expf(s[j][e] - m_use[e >> 1]);
+        p[e] = s[j][e] == -INFINITY ? 0.f : exp2f(s[j][e] - m_use[e >> 1]);
         psum[e >> 1] += p[e];
       }
       pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p[0], p[1]);

@@ -194,12 +194,41 @@ __global__ void gated_activation_kernel(const T* __restrict__ gu, T* __restrict_
   }
 }
 
+// bfloat16 rows whose width is a multiple of 8: 8 values (16 bytes) of gate and of up per thread
+__global__ void gated_activation_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                                            int hidden, int act, int n_rows) {
+  const int per_row = hidden >> 3;
+  const long total = (long)n_rows * per_row;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int n = (int)(i / per_row), f = (int)(i - (long)n * per_row) * 8;
+    const uint4 gv = *reinterpret_cast<const uint4*>(gu + (size_t)n * 2 * hidden + f);
+    const uint4 uv = *reinterpret_cast<const uint4*>(gu + (size_t)n * 2 * hidden + hidden + f);
+    const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float g0 = __uint_as_float(gw[k] << 16), g1 = __uint_as_float(gw[k] & 0xffff0000u);
+      const float u0 = __uint_as_float(uw[k] << 16), u1 = __uint_as_float(uw[k] & 0xffff0000u);
+      __nv_bfloat162 r = __floats2bfloat162_rn(activate(g0, act) * u0, activate(g1, act) * u1);
+      ow[k] = *reinterpret_cast<uint32_t*>(&r);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)n * hidden + f) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  }
+}
+
 FMS_API int fms_gated_activation(const void* gu, void* out, int dtype, int n_rows, int hidden, int act,
                                  cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (hidden <= 0 || act < 0 || act > 3) return fms_fail("gated_activation: hidden %d, act %d", hidden, act);
-  const size_t total = (size_t)n_rows * hidden;
   const int threads = 256;
+  if (dtype == FMS_BF16 && hidden % 8 == 0) {
+    const long total = (long)n_rows * (hidden / 8);
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 32 ? (total + threads - 1) / threads : 148 * 32);
+    gated_activation_vec_kernel<<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, hidden,
+                                                              act, n_rows);
+    return fms_launch_status("gated_activation");
+  }
+  const size_t total = (size_t)n_rows * hidden;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   FMS_DISPATCH_DTYPE(dtype, T,
                      gated_activation_kernel<T><<<blocks, threads, 0, stream>>>((const T*)gu, (T*)out, hidden, act,
@@ -259,12 +288,64 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
   dst[2 * i + 1] = from_f32<T>(x1);
 }
 
+// bfloat16, many tokens: one block per token, a thread per 16-byte piece (8 values = 4 pairs) of a head
+__global__ void rope_store_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+                                      const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                                      const int* __restrict__ token_seq, const int* __restrict__ slots,
+                                      __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                      const int* __restrict__ table, int table_stride, int block_tokens, int nheads,
+                                      int kvheads, int head_dim, int write_cache, int* __restrict__ error_flag) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int pieces = head_dim >> 3;
+  const int total = (nheads + 2 * kvheads) * pieces;
+  const size_t width = (size_t)(nheads + 2 * kvheads) * head_dim;
+  int blk = 0;
+  if (write_cache) {
+    blk = table[(size_t)slots[token_seq[t]] * table_stride + pos / block_tokens];
+    if (blk < 0 && threadIdx.x == 0 && error_flag) atomicExch(error_flag, 2);
+  }
+  for (int i = threadIdx.x; i < total; i += blockDim.x) {
+    const int head = i / pieces, piece = i - head * pieces;
+    const uint4 v = *reinterpret_cast<const uint4*>(qkv + (size_t)t * width + (size_t)head * head_dim + piece * 8);
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    const bool is_v = head >= nheads + kvheads;
+    if (!is_v && inv_freq != nullptr) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float x0 = __uint_as_float(w[k] << 16), x1 = __uint_as_float(w[k] & 0xffff0000u);
+        float sn, cs;
+        sincosf((float)pos * inv_freq[piece * 4 + k], &sn, &cs);
+        __nv_bfloat162 r = __floats2bfloat162_rn(cs * x0 - sn * x1, sn * x0 + cs * x1);
+        w[k] = *reinterpret_cast<uint32_t*>(&r);
+      }
+    }
+    const uint4 o = make_uint4(w[0], w[1], w[2], w[3]);
+    if (head < nheads) {
+      *reinterpret_cast<uint4*>(q_out + ((size_t)t * nheads + head) * head_dim + piece * 8) = o;
+    } else if (write_cache && blk >= 0) {
+      const int kvh = is_v ? head - nheads - kvheads : head - nheads;
+      __nv_bfloat16* base = is_v ? v_cache : k_cache;
+      *reinterpret_cast<uint4*>(base + (((size_t)blk * kvheads + kvh) * block_tokens + (pos % block_tokens)) * head_dim +
+                                piece * 8) = o;
+    }
+  }
+}
+
 FMS_API int fms_rope_store(const void* qkv, int dtype, void* q_out, const float* inv_freq, const int* positions,
                            const int* token_seq, const int* slots, void* k_cache, void* v_cache, const int* table,
                            int table_stride, int block_tokens, int n_tokens, int nheads, int kvheads, int head_dim,
                            int write_cache, int* error_flag, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (head_dim <= 0 || head_dim % 2 || head_dim > 2048) return fms_fail("rope_store: head_dim %d", head_dim);
+  if (dtype == FMS_BF16 && head_dim % 8 == 0 && n_tokens >= 64) {
+    const int total = (nheads + 2 * kvheads) * (head_dim / 8);
+    const int threads = total >= 256 ? 256 : ((total + 31) / 32) * 32;
+    rope_store_vec_kernel<<<n_tokens, threads, 0, stream>>>(
+        (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, inv_freq, positions, token_seq, slots, (__nv_bfloat16*)k_cache,
+        (__nv_bfloat16*)v_cache, table, table_stride, block_tokens, nheads, kvheads, head_dim, write_cache, error_flag);
+    return fms_launch_status("rope_store");
+  }
   dim3 grid(n_tokens, nheads + 2 * kvheads);
   const int threads = ((head_dim / 2 + 31) / 32) * 32;
   FMS_DISPATCH_DTYPE(dtype, T,

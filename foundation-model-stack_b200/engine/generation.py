@@ -68,13 +68,14 @@ def generate_batch(engine, sampler: Sampler, prompts: Sequence[Sequence[int]], r
     outputs = [list(p) for p in prompts]
     slots = engine.begin(n)
     held = set(slots)
+    horizon = max(len(p) for p in prompts) + max_new_tokens
     try:
         live = list(range(n))
         feed = [list(p) for p in prompts]
         for it in range(max_new_tokens):
             start = time.perf_counter()
             if it > 0 and hasattr(engine, "decode"):
-                logits = engine.decode([slots[i] for i in live], [f[0] for f in feed])
+                logits = engine.decode([slots[i] for i in live], [f[0] for f in feed], horizon=horizon)
             else:
                 logits = engine.step([slots[i] for i in live], feed)
             req = torch.tensor([requests[i] for i in live], dtype=torch.int32).to(engine.device)

@@ -127,11 +127,13 @@ class Engine:
         return logits
 
     def decode(self, slots: Sequence[int], tokens: Optional[Sequence[int]] = None,
-               tokens_device: Optional[torch.Tensor] = None) -> torch.Tensor:
+               tokens_device: Optional[torch.Tensor] = None, horizon: int = 0) -> torch.Tensor:
         """One token for each sequence; logits [n, vocab] for each.  The tokens come from the host
         (``tokens``) or are already on the device (``tokens_device``, int32 [n], e.g. what the sampler
-        wrote).  The result is a buffer that the next decode step of as many sequences overwrites: use
-        it, or copy it, before that."""
+        wrote).  ``horizon``: the longest any of these sequences will get in this run, if the caller knows
+        it; the launch is then sized for it once, instead of growing (and being captured anew) as the
+        sequences grow.  The result is a buffer that the next decode step of as many sequences
+        overwrites: use it, or copy it, before that."""
         n = len(slots)
         if len(set(slots)) != n:
             raise ValueError("a slot appears twice in one step")
@@ -161,7 +163,7 @@ class Engine:
             if self.device.type == "cuda":
                 buf.copied = torch.cuda.Event()
                 buf.copied.record()
-        logits = self._run_decode(buf, max(lengths) + 1)
+        logits = self._run_decode(buf, max(max(lengths) + 1, min(int(horizon), self.cache.max_positions)))
         self.cache.commit(slots, [1] * n)
         buf.lengths = [x + 1 for x in lengths]
         return logits

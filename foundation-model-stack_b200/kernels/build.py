@@ -138,6 +138,12 @@ def compile_library(name: str, verbose: bool = True) -> str:
             os.remove(tmp)
         raise KernelBuildError(f"nvcc failed on {source}:\n{' '.join(cmd)}\n{output}")
     os.replace(tmp, out)
+    for stale in os.listdir(os.path.dirname(out)):  # earlier builds of this library, from other sources or flags
+        if stale.startswith(f"libfms_{name}_") and stale.endswith(".so") and stale != os.path.basename(out):
+            try:
+                os.remove(os.path.join(os.path.dirname(out), stale))
+            except OSError:
+                pass
     if verbose:
         print(f"[fms_b200] compiled {os.path.basename(out)} in {time.time() - start:.0f} s", file=sys.stderr, flush=True)
     return out
