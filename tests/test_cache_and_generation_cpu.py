@@ -1,0 +1,281 @@
+"""The cache's bookkeeping (no slot or block lost, held twice or freed twice), the generation loop's
+decisions on a fake engine, the tokenizer and the command line's parser — all on the CPU."""
+import random
+
+import pytest
+import torch
+
+
+# ---- slots and blocks ---------------------------------------------------------------------------------
+def test_slot_allocator_never_loses_or_doubles():
+    from fms_b200.cache import CacheFull, SlotAllocator
+
+    a = SlotAllocator(5)
+    got = [a.alloc() for _ in range(5)]
+    assert sorted(got) == [0, 1, 2, 3, 4] and a.n_free == 0
+    with pytest.raises(CacheFull):
+        a.alloc()
+    a.free(3)
+    with pytest.raises(ValueError):
+        a.free(3)  # freed twice
+    with pytest.raises(ValueError):
+        a.free(7)  # never existed
+    assert a.alloc() == 3  # used again
+    rng = random.Random(0)
+    held = set(got)
+    for _ in range(2000):
+        if held and rng.random() < 0.5:
+            s = rng.choice(sorted(held))
+            a.free(s)
+            held.discard(s)
+        elif a.n_free:
+            s = a.alloc()
+            assert s not in held  # never held twice
+            held.add(s)
+        assert a.n_held == len(held) and a.n_free + a.n_held == 5
+
+
+def test_block_pool_never_loses_or_doubles():
+    from fms_b200.cache import BlockPool, CacheFull
+
+    p = BlockPool(10)
+    a = p.alloc(4)
+    b = p.alloc(6)
+    assert sorted(a + b) == list(range(10))
+    with pytest.raises(CacheFull):
+        p.alloc(1)
+    p.free(a)
+    with pytest.raises(ValueError):
+        p.free([a[0]])
+    assert p.n_free == 4 and p.n_held == 6
+    with pytest.raises(CacheFull):
+        p.alloc(5)  # refused whole: nothing is taken
+    assert p.n_free == 4
+    assert sorted(p.alloc(4)) == sorted(a)
+
+
+def test_cache_lengths_blocks_groups_and_reuse():
+    from fms_b200.cache import Cache, CacheFull, KVRequest, StateRequest
+
+    reqs = [KVRequest(2, 16), KVRequest(2, 16), KVRequest(2, 16, window=70), None, StateRequest((3, 4), torch.float32)]
+    c = Cache(reqs, max_tokens=64 * 6, max_positions=512, dtype=torch.float32, device="cpu", max_slots=3)
+    assert len(c.groups) == 3  # layers 0 and 1 share a group; the windowed layer and the state have their own
+    full, win, state = c.groups
+    assert full.layers == [0, 1] and win.layers == [2] and state.layers == [4]
+    assert full.storage.shape == (2, 2, 6, 2, 64, 16) and state.storage.shape == (1, 3, 3, 4)
+    assert c.layer_view(3) is None and c.layer_view(0).keys.shape == (6, 2, 64, 16)
+    s0, s1 = c.begin(2)
+    state.storage[0, s0] = 1.0
+    assert c.prepare([s0, s1], [100, 5]) == [0, 0]
+    c.commit([s0, s1], [100, 5])
+    assert (c.length[s0], c.length[s1]) == (100, 5)
+    assert full.pool.n_held == 3 and len(full.held_blocks(s0)) == 2
+    # the device table says where each position lies; unheld entries are -1
+    assert full.table[s0, :2].tolist() == full.held_blocks(s0) and full.table[s0, 2].item() == -1
+    for _ in range(100):
+        c.prepare_decode([s0, s1])
+        c.commit([s0, s1], [1, 1])
+    assert c.length[s0] == 200 and len(full.held_blocks(s0)) == 4
+    # the window of 70 keeps positions 130..199: blocks 2 and 3 only; earlier ones went back to the pool
+    assert win.table_host[s0].tolist()[:5] == [-1, -1] + win.held_blocks(s0) + [-1]
+    assert len(win.held_blocks(s0)) == 2
+    # a step that does not fit is refused before anything is taken
+    held = full.pool.n_held
+    with pytest.raises(CacheFull):
+        c.prepare([s1], [64 * 3])
+    assert full.pool.n_held == held and c.length[s1] == 105
+    with pytest.raises(CacheFull):
+        c.prepare([s0], [400])  # beyond the model's positions
+    c.release([s0])
+    with pytest.raises(ValueError):
+        c.release([s0])
+    assert full.pool.n_held == 2 and full.table_host[s0].max().item() == -1
+    (again,) = c.begin(1)
+    assert again == s0 and c.length[again] == 0
+    assert state.storage[0, again].abs().sum().item() == 0  # state starts at zero for the new sequence
+    c.release([again, s1])
+    assert c.slots.n_held == 0 and full.pool.n_held == 0 and win.pool.n_held == 0
+    with pytest.raises(CacheFull):
+        c.begin(4)
+
+
+def test_cache_random_walk_keeps_its_books():
+    from fms_b200.cache import Cache, CacheFull, KVRequest
+
+    c = Cache([KVRequest(1, 16), KVRequest(1, 16, window=100)], max_tokens=64 * 12, max_positions=640,
+              dtype=torch.float32, device="cpu", max_slots=4)
+    rng = random.Random(1)
+    live = {}
+    for _ in range(600):
+        r = rng.random()
+        try:
+            if r < 0.15 and c.slots.n_free:
+                (s,) = c.begin(1)
+                assert s not in live
+                live[s] = 0
+            elif r < 0.25 and live:
+                s = rng.choice(sorted(live))
+                c.release([s])
+                del live[s]
+            elif live:
+                s = rng.choice(sorted(live))
+                n = rng.choice([1, 1, 1, 7, 64, 130])
+                c.prepare([s], [n])
+                c.commit([s], [n])
+                live[s] += n
+        except CacheFull:
+            pass
+        for g in c.groups:
+            owned = [b for s in range(4) for b in g.held_blocks(s)]
+            assert len(owned) == len(set(owned)) == g.pool.n_held  # no block held twice, none lost
+            assert g.pool.n_held + g.pool.n_free == g.pool.n_blocks
+        for s, n in live.items():
+            assert c.length[s] == n
+            full = c.groups[0]
+            assert len(full.held_blocks(s)) == (n + 63) // 64
+        assert c.slots.n_held == len(live)
+
+
+# ---- the generation loop on a fake engine --------------------------------------------------------------
+class CountingEngine:
+    """next token = (last token + 1) % vocab, as the reference's ModelMock (tests/utils/test_generate.py:15-30);
+    keeps the books of slots so that the loop's decisions can be checked."""
+
+    def __init__(self, vocab=20, max_slots=3):
+        self.vocab, self.device = vocab, torch.device("cpu")
+        self.free = list(range(max_slots))
+        self.last = {}
+        self.steps = []  # (kind, number of sequences)
+        self.released = []
+
+    def begin(self, n):
+        assert n <= len(self.free)
+        out = [self.free.pop(0) for _ in range(n)]
+        return out
+
+    def release(self, slots):
+        for s in slots:
+            assert s not in self.free
+            self.free.append(s)
+            self.released.append(s)
+
+    def _logits(self, slots):
+        lg = torch.zeros(len(slots), self.vocab)
+        for i, s in enumerate(slots):
+            lg[i, (self.last[s] + 1) % self.vocab] = 5.0
+        return lg
+
+    def step(self, slots, tokens, want=None):
+        self.steps.append(("step", len(slots), [len(t) for t in tokens]))
+        for s, t in zip(slots, tokens):
+            self.last[s] = t[-1]
+        return self._logits(slots)
+
+    def decode(self, slots, tokens, horizon=0):
+        self.steps.append(("decode", len(slots), horizon))
+        for s, t in zip(slots, tokens):
+            self.last[s] = t
+        return self._logits(slots)
+
+
+@pytest.fixture
+def greedy_on_cpu(monkeypatch):
+    from fms_b200.kernels import ops
+
+    monkeypatch.setattr(ops, "argmax", lambda logits, out=None: torch.argmax(logits, -1).to(torch.int32))
+
+
+def test_generate_stops_each_sequence_at_its_stop_token(greedy_on_cpu):
+    from fms_b200.utils.generation import generate
+
+    e = CountingEngine()
+    out = generate(e, [[5], [1, 2], [9, 6]], max_new_tokens=8, do_sample=False, eos_token_id=7)
+    assert [o.tolist() for o in out] == [[5, 6, 7], [1, 2, 3, 4, 5, 6, 7], [9, 6, 7]]
+    # the prompts in one step, then one token each; the batch shrinks as sequences end (the reference would
+    # end everything at the first stop token, fms/utils/generation.py:338-341)
+    assert e.steps[0] == ("step", 3, [1, 2, 2])
+    assert [s[:2] for s in e.steps[1:]] == [("decode", 2), ("decode", 1), ("decode", 1), ("decode", 1)]
+    assert all(s[2] == 2 + 8 for s in e.steps[1:])  # the horizon: longest prompt + max_new_tokens
+    assert sorted(e.released) == [0, 1, 2] and sorted(e.free) == [0, 1, 2]  # every slot given back once
+
+
+def test_generate_runs_batches_one_after_another_and_keeps_the_order(greedy_on_cpu):
+    from fms_b200.utils.generation import generate
+
+    e = CountingEngine(max_slots=2)
+    prompts = [[i] for i in range(5)]
+    out = generate(e, prompts, max_new_tokens=3, do_sample=False, batch_size=2)
+    assert [o.tolist() for o in out] == [[i, i + 1, i + 2, i + 3] for i in range(5)]
+    assert [s[1] for s in e.steps if s[0] == "step"] == [2, 2, 1]  # three batches
+    assert len(e.released) == 5 and sorted(e.free) == [0, 1]  # slots were used again
+    # a 1-D prompt gives a 1-D result; a rectangle gives a rectangle, padded after early stops
+    assert generate(e, torch.tensor([3]), max_new_tokens=2, do_sample=False).tolist() == [3, 4, 5]
+    rect = generate(e, torch.tensor([[3], [5]]), max_new_tokens=4, do_sample=False, eos_token_id=7, pad_token_id=0)
+    assert rect.tolist() == [[3, 4, 5, 6, 7], [5, 6, 7, 0, 0]]
+
+
+def test_generate_argument_checks_and_release_on_error(greedy_on_cpu):
+    from fms_b200.utils.generation import generate
+
+    e = CountingEngine()
+    with pytest.raises(NotImplementedError):
+        generate(e, [[1]], num_beams=2)
+    with pytest.raises(ValueError):
+        generate(e, [[]])
+    with pytest.raises(ValueError):
+        generate(e, [[1]], timing="sometimes")
+    with pytest.raises(ValueError):
+        generate(e, [[1]], do_sample=True, temperature=0.0)
+
+    def boom(*a, **k):
+        raise RuntimeError("hook failed")
+
+    with pytest.raises(RuntimeError):
+        generate(e, [[1], [2]], max_new_tokens=3, do_sample=False, post_iteration_hook=boom)
+    assert sorted(e.free) == [0, 1, 2]  # the slots came back although the loop ended in an error
+    out, times = generate(e, [[1]], max_new_tokens=3, do_sample=False, timing="per-token")
+    assert len(times) == 3 and out[0].tolist() == [1, 2, 3, 4]
+    out, times = generate(e, [[1, 2, 3, 4]], max_new_tokens=2, do_sample=False, timing="e2e", max_seq_len=2)
+    assert len(times) == 1 and out[0].tolist() == [3, 4, 5, 6]  # the prompt was cut to its last 2 tokens
+
+
+def test_plan_batches_respects_cache_and_slots():
+    from fms_b200.utils.generation import plan_batches
+
+    # each request needs ceil((len + new) / 64) blocks of the cache
+    assert plan_batches([10, 10, 10], 10, None, 64 * 3, 8) == [[0, 1, 2]]
+    assert plan_batches([10, 60, 10], 30, None, 64 * 3, 8) == [[0, 1], [2]]
+    assert plan_batches([10] * 5, 10, 2, 64 * 100, 8) == [[0, 1], [2, 3], [4]]
+    assert plan_batches([10] * 5, 10, None, 64 * 100, 3) == [[0, 1, 2], [3, 4]]
+    with pytest.raises(ValueError):
+        plan_batches([200], 10, None, 128, 8)
+
+
+def test_helpers_and_tokenizer_and_parser():
+    from fms_b200.cli.inference import build_parser
+    from fms_b200.utils.generation import trim_prefix, truncate_after_eos
+    from fms_b200.utils.tokenizers import CharTokenizer, get_tokenizer
+
+    assert truncate_after_eos(torch.tensor([5, 6, 3, 9, 3]), 3).tolist() == [5, 6, 3]
+    assert truncate_after_eos(torch.tensor([5, 6]), 3).tolist() == [5, 6]
+    assert trim_prefix(torch.tensor([0, 0, 4, 0, 5]), 0).tolist() == [4, 0, 5]
+    t = get_tokenizer("char_tokenizer")
+    assert isinstance(t, CharTokenizer) and t.vocab_size() == 256 and (t.bos_token_id, t.eos_token_id) == (2, 3)
+    ids = t.encode("héllo", add_special_tokens=True)
+    assert ids == [2, 104, 233, 108, 108, 111] and t.decode(ids + [3]) == "héllo"
+    with pytest.raises(ValueError):
+        get_tokenizer("/no/such/tokenizer")
+    args = build_parser().parse_args(["--variant", "micro", "--prompt", "a", "--prompt", "b", "--batch_input",
+                                      "--default_dtype", "fp32", "--max_new_tokens", "7"])
+    assert args.prompt == ["a", "b"] and args.batch_input and args.default_dtype == "fp32" and args.max_new_tokens == 7
+    assert args.device_type == "cuda" and args.architecture == "llama" and args.top_k == 10
+
+
+def test_sampler_arguments():
+    from fms_b200.sampling import Sampler
+
+    with pytest.raises(ValueError):
+        Sampler(do_sample=True, temperature=0.0)
+    with pytest.raises(ValueError):
+        Sampler(do_sample=True, top_k=-1)
+    Sampler(do_sample=False, temperature=0.0)  # greedy ignores the temperature
