@@ -1,0 +1,306 @@
+"""Each part of a layer alone against the plain implementation, and the generality of the assembly: a toy
+mixer with state of its own, a toy feed-forward with routing and a decoder whose schedule names a layer
+twice are defined HERE, registered, built and stepped without a change to the library's files."""
+import math
+
+import pytest
+import torch
+
+import plain_llama as pl
+
+pytestmark = pytest.mark.gpu
+
+
+def close(got, want, dtype):
+    want = want.double().cpu()
+    got = got.double().cpu()
+    if dtype == torch.float32:
+        torch.testing.assert_close(got, want, atol=2e-5, rtol=1e-4)
+    else:
+        torch.testing.assert_close(got, want, atol=0.02 * want.abs().max().item(), rtol=0.02)
+
+
+def fill(part, dtype, seed, scale=0.05):
+    """Random tensors for everything a part declares; returns them by qualified name (float64 copies)."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, owner, local, decl in part.named_decls():
+        if decl.role == "vector":
+            t = 1 + 0.1 * torch.randn(decl.shape, generator=g)
+        else:
+            t = torch.randn(decl.shape, generator=g) * scale
+        t = t.to(dtype)
+        owner.set_tensor(local, t.cuda())
+        out[name] = t.double()
+    part.finalize(torch.device("cuda"), dtype)
+    return out
+
+
+def one_sequence_batch(n_new, len_before, cache, slot):
+    from fms_b200.engine.batch import Batch
+
+    cache.prepare([slot], [n_new])
+    b = Batch.from_lists([slot], [len_before], [[0] * n_new], [[]], "cuda")
+    return b
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_part(dtype):
+    from fms_b200.config import NormSpec
+    from fms_b200.parts import build_norm
+
+    norm = build_norm(NormSpec("rmsnorm", 240, 1e-6))
+    w = fill(norm, dtype, 0)
+    g = torch.Generator().manual_seed(1)
+    res = torch.randn(9, 240, generator=g).cuda()
+    delta = torch.randn(9, 240, generator=g).to(dtype).cuda()
+    want = pl.plain_rmsnorm(res.double().cpu() + delta.double().cpu(), w["weight"], 1e-6)
+    got = norm.apply(res, delta, dtype)
+    close(got, want, dtype)
+    with pytest.raises(KeyError):
+        build_norm(NormSpec("no_such_norm", 8, 1e-5))
+
+
+def test_rotary_part_frequencies():
+    from fms_b200.config import PositionSpec
+    from fms_b200.parts import build_position
+
+    for theta, scaling in ((10000.0, {}), (500000.0, {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                                       "high_freq_factor": 4.0, "original_max_position_embeddings": 8192})):
+        part = build_position(PositionSpec("rope", head_dim=64, theta=theta, scaling=tuple(sorted(scaling.items()))))
+        part.finalize(torch.device("cuda"), torch.float32)
+        torch.testing.assert_close(part.rotary_frequencies().cpu(), pl.plain_rope_inv_freq(64, theta, scaling), rtol=1e-6,
+                                   atol=0)
+    assert build_position(PositionSpec("none")).rotary_frequencies() is None
+    with pytest.raises(ValueError):
+        build_position(PositionSpec("rope", head_dim=64, scaling=(("rope_type", "yarn"),)))
+
+
+def plain_mixer(w, x, nheads, kvheads, hd, theta, window, positions):
+    s = x.shape[0]
+    qkv = x @ w["in_proj.qkv_fused.weight"].T
+    q, k, v = qkv.split([nheads * hd, kvheads * hd, kvheads * hd], -1)
+    inv = pl.plain_rope_inv_freq(hd, theta)
+    q = pl.plain_rope(q.view(s, nheads, hd), positions, inv)
+    k = pl.plain_rope(k.view(s, kvheads, hd), positions, inv)
+    a = pl.plain_attention(q, k, v.view(s, kvheads, hd), window=window).reshape(s, -1)
+    return a @ w["dense.weight"].T
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nheads,kvheads,hd,window", [(4, 2, 16, 0), (6, 1, 32, 0), (3, 3, 48, 40)])
+def test_attention_part_alone(dtype, nheads, kvheads, hd, window):
+    """The mixer with a cache of its own: a whole sequence, then the same sequence cut in three."""
+    from fms_b200.cache import Cache
+    from fms_b200.config import MixerSpec, PositionSpec
+    from fms_b200.parts import build_mixer
+
+    dim, theta, n = nheads * hd, 10000.0, 150
+    spec = MixerSpec("attention", dim=dim, nheads=nheads, kvheads=kvheads, head_dim=hd, window=window,
+                     position=PositionSpec("rope", head_dim=hd, theta=theta))
+    mixer = build_mixer(spec)
+    w = fill(mixer, dtype, 2, scale=0.08)
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(n, dim, generator=g).to(dtype)
+    want = plain_mixer(w, x.double(), nheads, kvheads, hd, theta, window, torch.arange(n))
+    cache = Cache([mixer.cache_request()], max_tokens=512, max_positions=512, dtype=dtype, device="cuda")
+    for cuts in ([n], [70, 1, 79]):
+        (slot,) = cache.begin(1)
+        outs, at = [], 0
+        for k in cuts:
+            batch = one_sequence_batch(k, at, cache, slot)
+            outs.append(mixer.forward(x[at:at + k].cuda().contiguous(), batch, cache.layer_view(0), True))
+            cache.commit([slot], [k])
+            at += k
+        cache.release([slot])
+        close(torch.cat(outs), want, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows", [3, 40])
+def test_feed_forward_part_alone(dtype, rows):
+    from fms_b200.config import FeedForwardSpec
+    from fms_b200.parts import build_feed_forward
+
+    ff = build_feed_forward(FeedForwardSpec("glu", dim=96, hidden=328, activation="swish"))
+    w = fill(ff, dtype, 4, scale=0.1)
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(rows, 96, generator=g).to(dtype)
+    gate, up = w["wg1_fused.weight"][:328], w["wg1_fused.weight"][328:]
+    want = pl.plain_swiglu_ffn(x.double(), gate, up, w["w2.weight"])
+    close(ff.forward(x.cuda()), want, dtype)
+    with pytest.raises(ValueError):
+        build_feed_forward(FeedForwardSpec("glu", dim=8, hidden=8, activation="mish"))
+
+
+# ---------------------------------------------------------------------------------------------------
+# toy parts, defined in this test only
+# ---------------------------------------------------------------------------------------------------
+def register_toys():
+    from fms_b200.cache import StateRequest
+    from fms_b200.parts import Linear, Part, register_feed_forward, register_mixer, registered
+
+    class DecayMixer(Part):
+        """y_t = W s_t with s_t = decay * s_{t-1} + x_t: a mixer whose only memory is a state vector per
+        sequence.  Written with torch operations: it is a test's toy, not a kernel."""
+
+        def __init__(self, spec):
+            super().__init__()
+            self.dim = spec.dim
+            self.decay = dict(spec.options)["decay"]
+            self.out = self.add("out", Linear(spec.dim, spec.dim))
+
+        def cache_request(self):
+            return StateRequest((self.dim,), torch.float32, name="decay_state")
+
+        def forward(self, x, batch, view, writes_cache=True):
+            slots = batch.slots.long()
+            if batch.decode:  # one token per sequence; no host synchronisation, so that it can be captured
+                s = view.state[slots] * self.decay + x.float()
+                if writes_cache:
+                    view.state[slots] = s
+                return self.out.forward(s.to(x.dtype))
+            rows, at = [], 0
+            for i, n in enumerate(batch.num_new):
+                s = view.state[slots[i]].clone()
+                for t in range(n):
+                    s = s * self.decay + x[at + t].float()
+                    rows.append(s)
+                at += n
+                if writes_cache:
+                    view.state[slots[i]] = s
+            return self.out.forward(torch.stack(rows).to(x.dtype))
+
+    class TopOneExperts(Part):
+        """A feed-forward with routing: each token goes to the expert with the largest router logit (router
+        logits in float32) and is scaled by the softmax weight of that expert."""
+
+        def __init__(self, spec):
+            super().__init__()
+            self.n = dict(spec.options)["experts"]
+            self.router = self.add("router", Linear(spec.dim, self.n))
+            self.experts = [self.add(f"expert{i}", Linear(spec.dim, spec.dim)) for i in range(self.n)]
+
+        def forward(self, x):
+            logits = x.float() @ self.router.tensor("weight").float().T
+            weight, choice = torch.softmax(logits, -1).max(-1)
+            out = torch.zeros_like(x)
+            for i, e in enumerate(self.experts):
+                out = out + torch.where((choice == i)[:, None], e.forward(x), torch.zeros_like(x))
+            return (out.float() * weight[:, None]).to(x.dtype)
+
+    if "toy_decay" not in registered("mixer"):
+        register_mixer("toy_decay", DecayMixer)
+        register_feed_forward("toy_experts", TopOneExperts)
+
+
+def toy_model(dtype, seed=7):
+    """A two-layer decoder: layer 0 is Llama's attention + SwiGLU, layer 1 the toy mixer + the toy experts;
+    the schedule runs layer 0, layer 1, and layer 0 again, the second time reading the cache of the first."""
+    from fms_b200.config import (BlockSpec, DecoderSpec, FeedForwardSpec, LayerCall, MixerSpec, NormSpec, PositionSpec)
+    from fms_b200.models.base import Model
+    from fms_b200.weights import RandomSource, TensorLayout
+
+    register_toys()
+    dim, vocab = 64, 97
+    norm = NormSpec("rmsnorm", dim, 1e-5)
+    attn = BlockSpec(
+        MixerSpec("attention", dim=dim, nheads=4, kvheads=2, head_dim=16, position=PositionSpec("rope", head_dim=16)),
+        FeedForwardSpec("glu", dim=dim, hidden=96), norm, norm)
+    toy = BlockSpec(MixerSpec("toy_decay", dim=dim, options=(("decay", 0.5),)),
+                    FeedForwardSpec("toy_experts", dim=dim, hidden=0, options=(("experts", 3),)), norm, norm)
+    spec = DecoderSpec(vocab_size=vocab, dim=dim, layers=(attn, toy),
+                       schedule=(LayerCall(0), LayerCall(1), LayerCall(0, cache_of=0, writes_cache=False)),
+                       final_norm=norm, tie_head=True, max_positions=256)
+
+    class Toy(Model):
+        architecture = "toy_architecture_of_a_test"
+        default_source = "native"
+
+        def decoder_spec(self):
+            return spec
+
+    from fms_b200.engine.decoder import Decoder
+
+    layout = [TensorLayout(n, d.shape, "gain" if d.role == "vector" else "matrix")
+              for n, _, _, d in Decoder(spec, dtype).named_decls()]
+    model = Toy(config=None)
+    model.load(RandomSource(layout, seed, dtype=torch.bfloat16, device="cpu", std=0.08), "native", "cuda", dtype)
+    return model, spec
+
+
+def plain_toy(model, ids):
+    """The toy decoder restated in float64 from the model's own tensors."""
+    w = {k: v.double().cpu() for k, v in model.state_dict().items()}
+    n = len(ids)
+    x = w["base_model.embedding.weight"][torch.tensor(ids)]
+    pos = torch.arange(n)
+
+    def attn_block(x, kv=None):
+        """Layer 0; with ``kv`` the keys and values of an earlier call are read instead of its own."""
+        p = "base_model.layers.0."
+        h = pl.plain_rmsnorm(x, w[p + "ln.weight"], 1e-5)
+        qkv = h @ w[p + "attn.in_proj.qkv_fused.weight"].T
+        q, k, v = qkv.split([64, 32, 32], -1)
+        inv = pl.plain_rope_inv_freq(16, 10000.0)
+        q = pl.plain_rope(q.view(n, 4, 16), pos, inv)
+        if kv is None:
+            kv = (pl.plain_rope(k.view(n, 2, 16), pos, inv), v.view(n, 2, 16))
+        a = pl.plain_attention(q, kv[0], kv[1]).reshape(n, -1) @ w[p + "attn.dense.weight"].T
+        x = x + a
+        h = pl.plain_rmsnorm(x, w[p + "ff_ln.weight"], 1e-5)
+        gu = w[p + "ff_sub_layer.wg1_fused.weight"]
+        return x + pl.plain_swiglu_ffn(h, gu[:96], gu[96:], w[p + "ff_sub_layer.w2.weight"]), kv
+
+    def toy_block(x):
+        p = "base_model.layers.1."
+        h = pl.plain_rmsnorm(x, w[p + "ln.weight"], 1e-5)
+        s, rows = torch.zeros(64, dtype=torch.float64), []
+        for t in range(n):
+            s = 0.5 * s + h[t]
+            rows.append(s)
+        x = x + torch.stack(rows) @ w[p + "attn.out.weight"].T
+        h = pl.plain_rmsnorm(x, w[p + "ff_ln.weight"], 1e-5)
+        weight, choice = torch.softmax(h @ w[p + "ff_sub_layer.router.weight"].T, -1).max(-1)
+        out = torch.stack([h[t] @ w[p + f"ff_sub_layer.expert{int(choice[t])}.weight"].T for t in range(n)])
+        return x + out * weight[:, None]
+
+    x, kv = attn_block(x)
+    x, _ = attn_block(toy_block(x), kv)  # the schedule's third call reads the first call's cache
+    x = pl.plain_rmsnorm(x, w["base_model.dec_norm.weight"], 1e-5)
+    return x @ w["base_model.embedding.weight"].T
+
+
+def test_toy_mixer_with_state_and_routed_feed_forward_are_registered_built_and_stepped():
+    """float32 only: the toy's torch products are not the point, the assembly is."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    model, spec = toy_model(torch.float32)
+    engine = model.new_engine(max_tokens=512, max_slots=3)
+    kinds = [type(g).__name__ for g in engine.cache.groups]
+    assert kinds == ["KVGroup", "StateGroup"]  # the toy's state got storage of its own
+    g = torch.Generator().manual_seed(8)
+    reqs = [torch.randint(0, 97, (k,), generator=g).tolist() for k in (40, 9, 70)]
+    want = [plain_toy(model, r) for r in reqs]
+    # whole and alone
+    for r, w in zip(reqs, want):
+        (slot,) = engine.begin(1)
+        close(engine.step([slot], [r], [list(range(len(r)))]), w, torch.float32)
+        engine.release([slot])
+    # as a batch of unequal lengths: prompts, then one token each (the decode path, captured as a graph from
+    # its second step on); slots are used again, so the state must have been zeroed
+    cut = [len(r) - 6 for r in reqs]
+    slots = engine.begin(3)
+    got = [[] for _ in reqs]
+    lg = engine.step(slots, [r[:c] for r, c in zip(reqs, cut)], [list(range(c)) for c in cut])
+    o = 0
+    for i, c in enumerate(cut):
+        got[i].append(lg[o:o + c])
+        o += c
+    for t in range(6):
+        lg = engine.step(slots, [[r[c + t]] for r, c in zip(reqs, cut)])
+        for i in range(3):
+            got[i].append(lg[i:i + 1])
+    engine.release(slots)
+    for i in range(3):
+        close(torch.cat(got[i]), want[i], torch.float32)
+    assert engine.graph_launches > 0
