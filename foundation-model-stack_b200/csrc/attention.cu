@@ -193,6 +193,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, float* __r
   __shared__ float sm[GC], sl[GC], salpha[GC];
   __shared__ float red[RP][GC][HD];
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int seq = blockIdx.x, split = blockIdx.z;
   const int group = a.nheads / a.kvheads;
@@ -326,6 +328,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, float* __r
 template <typename T>
 __global__ void attn_combine_kernel(AttnArgs a, const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     int n_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int seq = blockIdx.x, head = blockIdx.y;
   const int len = a.len_after[seq];
   const int pos = len - 1;
@@ -364,8 +368,10 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
   if (a.nheads > 65535) return fms_fail("%s: %d heads", what, a.nheads);
   if (dtype == FMS_F32) {
     const int chunks = (group + GC - 1) / GC;
-    attn_decode_kernel<float><<<dim3(n_seqs, a.kvheads * chunks, n_splits), 128, 0, stream>>>(a, part_o, part_ml, n_splits);
-    attn_combine_kernel<float><<<dim3(n_seqs, a.nheads), HD >= 128 ? 128 : 64, 0, stream>>>(a, part_o, part_ml, n_splits);
+    fms_launch(attn_decode_kernel<float>, dim3(n_seqs, a.kvheads * chunks, n_splits), dim3(128), 0, stream, a, part_o,
+               part_ml, n_splits);
+    fms_launch(attn_combine_kernel<float>, dim3(n_seqs, a.nheads), dim3(HD >= 128 ? 128 : 64), 0, stream, a,
+               (const float*)part_o, (const float*)part_ml, n_splits);
   } else if (dtype == FMS_BF16) {
     // Few (sequence, kv head) pairs: four warps share a split, each with one block of 64 keys in flight, which
     // is quickest when the GPU is not full.  Many: one warp per block with a small footprint, so that several
@@ -382,8 +388,10 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
       if (e != cudaSuccess) return fms_fail("%s: %zu bytes of shared memory refused: %s", what, smem, cudaGetErrorString(e));
       configured[slot] = true;
     }
-    kernel<<<dim3(n_seqs, a.kvheads * chunks, n_splits), nw * 32, smem, stream>>>(a, part_o, part_ml, n_splits);
-    attn_combine_kernel<__nv_bfloat16><<<dim3(n_seqs, a.nheads), HD >= 128 ? 128 : 64, 0, stream>>>(a, part_o, part_ml, n_splits);
+    fms_launch(kernel, dim3(n_seqs, a.kvheads * chunks, n_splits), dim3(nw * 32), smem, stream, a, part_o, part_ml,
+               n_splits);
+    fms_launch(attn_combine_kernel<__nv_bfloat16>, dim3(n_seqs, a.nheads), dim3(HD >= 128 ? 128 : 64), 0, stream, a,
+               (const float*)part_o, (const float*)part_ml, n_splits);
   } else {
     return fms_fail("%s: unsupported dtype code %d", what, dtype);
   }

@@ -87,6 +87,8 @@ template <int NW>
 __global__ void __launch_bounds__(NW * 32) attn_decode_mma_kernel(AttnArgs a, float* __restrict__ part_o,
                                                                    float* __restrict__ part_ml, int n_splits) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
   const int seq = blockIdx.x, split = blockIdx.z;
   const int group = a.nheads / a.kvheads;

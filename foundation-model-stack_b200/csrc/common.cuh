@@ -82,3 +82,70 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
       return fms_fail("unsupported dtype code %d", (int)(code)); \
     }                                                        \
   } while (0)
+
+// ---- programmatic dependent launch ------------------------------------------------------------------
+// Kernels of a step are launched so that a kernel may start while the one before it is still draining.
+// Every kernel calls pdl_launch_dependents() early (the next kernel may be scheduled once all blocks of this
+// one have done so) and pdl_wait() before it reads what an earlier kernel wrote or writes anything at all;
+// only loads of constant data (weights) may come before pdl_wait().
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+#include <stdlib.h>
+static inline bool fms_pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* e = getenv("FMS_B200_PDL");
+    enabled = (e && e[0] == '0') ? 0 : 1;
+  }
+  return enabled == 1;
+}
+
+// Launches `kernel` on `stream`; with programmatic stream serialization unless FMS_B200_PDL=0.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t fms_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = fms_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// ---- mbarrier and bulk copies (sm_90+) ---------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(void* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive_expect_tx(void* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Waits for the phase with the given parity to complete; gives up after a bounded number of polls and returns
+// false (the caller records the failure and goes on, so that no kernel can hang).
+__device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (int i = 0; i < (1 << 22); ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+// bytes: a multiple of 16; both addresses 16-byte aligned; completion is counted on the mbarrier
+__device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, void* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}

@@ -9,6 +9,8 @@
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ out,
                                   int dim, int vocab, int* __restrict__ error_flag) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int tok = tokens[t];
   const bool ok = tok >= 0 && tok < vocab;
@@ -24,8 +26,8 @@ FMS_API int fms_embed_rows(const void* table, int table_dtype, const int* tokens
   if (dim <= 0 || vocab <= 0) return fms_fail("embed_rows: dim %d, vocab %d", dim, vocab);
   const int threads = dim >= 1024 ? 256 : 128;
   FMS_DISPATCH_DTYPE(table_dtype, T,
-                     embed_rows_kernel<T><<<n_tokens, threads, 0, stream>>>((const T*)table, tokens, out, dim, vocab,
-                                                                            error_flag));
+                     fms_launch(embed_rows_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, (const T*)table, tokens,
+                                out, dim, vocab, error_flag));
   return fms_launch_status("embed_rows");
 }
 
@@ -40,6 +42,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
                                    const TG* __restrict__ gain, float eps, T* __restrict__ out,
                                    const int* __restrict__ rows, int dim) {
   __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float* res = residual + (size_t)src * dim;
@@ -97,19 +101,25 @@ __global__ void add_rmsnorm_regs_kernel(float* __restrict__ residual, const T* _
                                         const TG* __restrict__ gain, float eps, T* __restrict__ out,
                                         const int* __restrict__ rows, int dim) {
   __shared__ float scratch[33];
+  pdl_launch_dependents();
   const int r = blockIdx.x;
+  const int nvec = dim >> 2;
+  float x[NCHUNK][4], dl[NCHUNK][4], g[NCHUNK][4];
+#pragma unroll
+  for (int j = 0; j < NCHUNK; ++j) {  // the gain is a weight: it can be read before the kernel before this one is done
+    const int c = threadIdx.x + j * blockDim.x;
+    if (c < nvec) load4(gain + 4 * c, g[j]);
+  }
+  pdl_wait();
   const int src = rows ? rows[r] : r;
   float* res = residual + (size_t)src * dim;
   const T* del = delta ? delta + (size_t)src * dim : nullptr;
-  const int nvec = dim >> 2;
-  float x[NCHUNK][4], dl[NCHUNK][4], g[NCHUNK][4];
 #pragma unroll
   for (int j = 0; j < NCHUNK; ++j) {
     const int c = threadIdx.x + j * blockDim.x;
     if (c < nvec) {
       load4(res + 4 * c, x[j]);
       if (del) load4(del + 4 * c, dl[j]);
-      load4(gain + 4 * c, g[j]);
     }
   }
   float ss = 0.f;
@@ -152,21 +162,21 @@ FMS_API int fms_add_rmsnorm(float* residual, const void* delta, const void* gain
     const int nchunk = (nvec + threads - 1) / threads;
     FMS_DISPATCH_DTYPE(dtype, T, FMS_DISPATCH_DTYPE(gain_dtype, TG, {
       if (nchunk <= 1)
-        add_rmsnorm_regs_kernel<T, TG, 1><<<n_rows, threads, 0, stream>>>(residual, (const T*)delta, (const TG*)gain,
-                                                                          eps, (T*)out, rows, dim);
+        fms_launch(add_rmsnorm_regs_kernel<T, TG, 1>, dim3(n_rows), dim3(threads), 0, stream, residual, (const T*)delta,
+                   (const TG*)gain, eps, (T*)out, rows, dim);
       else if (nchunk <= 2)
-        add_rmsnorm_regs_kernel<T, TG, 2><<<n_rows, threads, 0, stream>>>(residual, (const T*)delta, (const TG*)gain,
-                                                                          eps, (T*)out, rows, dim);
+        fms_launch(add_rmsnorm_regs_kernel<T, TG, 2>, dim3(n_rows), dim3(threads), 0, stream, residual, (const T*)delta,
+                   (const TG*)gain, eps, (T*)out, rows, dim);
       else
-        add_rmsnorm_regs_kernel<T, TG, 4><<<n_rows, threads, 0, stream>>>(residual, (const T*)delta, (const TG*)gain,
-                                                                          eps, (T*)out, rows, dim);
+        fms_launch(add_rmsnorm_regs_kernel<T, TG, 4>, dim3(n_rows), dim3(threads), 0, stream, residual, (const T*)delta,
+                   (const TG*)gain, eps, (T*)out, rows, dim);
     }));
     return fms_launch_status("add_rmsnorm");
   }
   const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
   FMS_DISPATCH_DTYPE(dtype, T, FMS_DISPATCH_DTYPE(gain_dtype, TG,
-                     (add_rmsnorm_kernel<T, TG><<<n_rows, threads, 0, stream>>>(
-                         residual, (const T*)delta, (const TG*)gain, eps, (T*)out, rows, dim))));
+                     fms_launch(add_rmsnorm_kernel<T, TG>, dim3(n_rows), dim3(threads), 0, stream, residual,
+                                (const T*)delta, (const TG*)gain, eps, (T*)out, rows, dim)));
   return fms_launch_status("add_rmsnorm");
 }
 
@@ -250,6 +260,8 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
                                   const int* __restrict__ slots, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                   const int* __restrict__ table, int table_stride, int block_tokens, int nheads,
                                   int kvheads, int head_dim, int write_cache, int* __restrict__ error_flag) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int head = blockIdx.y;  // 0..nheads-1: q; then k heads; then v heads
   const int i = threadIdx.x;    // pair index
@@ -349,9 +361,9 @@ FMS_API int fms_rope_store(const void* qkv, int dtype, void* q_out, const float*
   dim3 grid(n_tokens, nheads + 2 * kvheads);
   const int threads = ((head_dim / 2 + 31) / 32) * 32;
   FMS_DISPATCH_DTYPE(dtype, T,
-                     rope_store_kernel<T><<<grid, threads, 0, stream>>>(
-                         (const T*)qkv, (T*)q_out, inv_freq, positions, token_seq, slots, (T*)k_cache, (T*)v_cache,
-                         table, table_stride, block_tokens, nheads, kvheads, head_dim, write_cache, error_flag));
+                     fms_launch(rope_store_kernel<T>, grid, dim3(threads), 0, stream, (const T*)qkv, (T*)q_out, inv_freq,
+                                positions, token_seq, slots, (T*)k_cache, (T*)v_cache, table, table_stride, block_tokens,
+                                nheads, kvheads, head_dim, write_cache, error_flag));
   return fms_launch_status("rope_store");
 }
 
@@ -359,6 +371,8 @@ FMS_API int fms_rope_store(const void* qkv, int dtype, void* q_out, const float*
 // start of a decode step: every sequence's new token sits at its current length, which then grows by one
 // ---------------------------------------------------------------------------------------------------
 __global__ void decode_advance_kernel(int* __restrict__ positions, int* __restrict__ lengths, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) {
     const int len = lengths[i];
@@ -369,6 +383,6 @@ __global__ void decode_advance_kernel(int* __restrict__ positions, int* __restri
 
 FMS_API int fms_decode_advance(int* positions, int* lengths, int n, cudaStream_t stream) {
   if (n <= 0) return 0;
-  decode_advance_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, lengths, n);
+  fms_launch(decode_advance_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, positions, lengths, n);
   return fms_launch_status("decode_advance");
 }

@@ -2,25 +2,31 @@
 // every weight once and are bound by memory bandwidth.  bfloat16 operands, float32 accumulation on the
 // tensor cores (mma.sync m16n8k16: 16 weight rows x 8 batch rows per instruction), float32 or bfloat16 out.
 //
-// Work split: a block of 8 warps owns RT tiles of 16 weight rows; the warps share the K dimension in
-// interleaved chunks of 32 and their partial sums are added in shared memory in a fixed order, so the result
-// does not depend on timing.  A lane copies 16 contiguous bytes (8 values) of a weight row and of an x row per
+// Work split: a block of 8 warps owns RT tiles of weight rows; the warps share the K dimension in interleaved
+// chunks of 32 and their partial sums are added in shared memory in a fixed order, so the result does not
+// depend on timing nor on M.  A lane copies 16 contiguous bytes (8 values) of a weight row and of an x row per
 // chunk with cp.async into a ring in shared memory that only it reads back, several chunks ahead of use; the
 // two mma of a chunk use these values in the order in which they lie in memory, which is a permutation of the
 // instruction's k index that is the same for both operands and so leaves the sum as it is.
 //
-// GLU variant: the block's two tiles are rows [r, r+16) and [hidden + r, hidden + r + 16) of a fused
-// [gate; up] matrix, and the epilogue writes act(gate) * up — the gated activation of
-// fms/modules/feedforward.py:291-292 without the [M, 2 hidden] round trip.
+// A tile's two halves (mma rows 0-7 and 8-15) are
+//   ROWS16: weight rows r..r+7 and r+8..r+15;
+//   GLU8:   rows r..r+7 of the gate and of the up matrix of a fused [gate; up] weight; the epilogue writes
+//           act(gate) * up (fms/modules/feedforward.py:291-292) without the [M, 2 hidden] round trip.
+//
+// The weights of the first ring stages are requested before the kernel waits for the kernel before it
+// (programmatic dependent launch): weights do not depend on it, so the stream of weights from memory does
+// not stop between the kernels of a step.
 #include "common.cuh"
 
 namespace {
 constexpr int WARPS = 8;
+constexpr int THREADS = WARPS * 32;
+enum Mode { ROWS16 = 0, GLU8 = 2 };
 
 __device__ __forceinline__ void mma_bf16(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -48,27 +54,30 @@ __device__ __forceinline__ float activate(float g, int act) {
   }
 }
 
-// NT: tiles of 8 batch rows (M <= 8 NT).  RT: tiles of 16 weight rows per block.  GLU: see above (RT == 2).
-template <int NT, int RT, bool GLU, int D, typename TOut>
-__global__ void __launch_bounds__(WARPS * 32) linear_skinny_kernel(const __nv_bfloat16* __restrict__ x,
-                                                                   const __nv_bfloat16* __restrict__ w,
-                                                                   const __nv_bfloat16* __restrict__ bias,
-                                                                   TOut* __restrict__ y, int M, int N, int K,
-                                                                   int hidden, int act) {
+// NT: tiles of 8 batch rows (M <= 8 NT).  RT: tiles per block.  D: ring stages.
+template <int NT, int RT, int MODE, int D, typename TOut>
+__global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                const __nv_bfloat16* __restrict__ w,
+                                                                const __nv_bfloat16* __restrict__ bias,
+                                                                TOut* __restrict__ y, int M, int N, int K, int hidden,
+                                                                int act) {
+  constexpr int HALVES = 2;                           // weight rows a lane reads per tile
+  constexpr int TILE_ROWS = MODE == ROWS16 ? 16 : 8;  // output rows (or gate/up pairs) per tile
+  constexpr int WL = RT * HALVES;                     // weight pieces per stage
+  constexpr int LOADS = WL + NT;
   __shared__ float red[WARPS][RT][NT][32][4];
+  extern __shared__ uint4 ring[];
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, c = lane & 3;
-  const int n_rows = GLU ? 2 * hidden : N;  // rows of w
+  const int n_rows = MODE == GLU8 ? 2 * hidden : N;  // rows of w
 
-  // weight rows of this lane: tile t holds rows row0[t] + g and row0[t] + g + 8
-  int row0[RT];
-#pragma unroll
-  for (int t = 0; t < RT; ++t) row0[t] = GLU ? (blockIdx.x * 16 + t * hidden) : (blockIdx.x * RT + t) * 16;
   const __nv_bfloat16* wp[RT][2];
 #pragma unroll
   for (int t = 0; t < RT; ++t) {
-    wp[t][0] = w + (size_t)min(row0[t] + g, n_rows - 1) * K + 8 * c;
-    wp[t][1] = w + (size_t)min(row0[t] + g + 8, n_rows - 1) * K + 8 * c;
+    const int r0 = (blockIdx.x * RT + t) * TILE_ROWS + g;
+    wp[t][0] = w + (size_t)min(r0, n_rows - 1) * K + 8 * c;
+    wp[t][1] = w + (size_t)min(MODE == GLU8 ? hidden + r0 : r0 + 8, n_rows - 1) * K + 8 * c;
   }
   const __nv_bfloat16* xp[NT];
   bool xok[NT];
@@ -77,7 +86,6 @@ __global__ void __launch_bounds__(WARPS * 32) linear_skinny_kernel(const __nv_bf
     xok[j] = j * 8 + g < M;
     xp[j] = x + (size_t)(xok[j] ? j * 8 + g : 0) * K + 8 * c;
   }
-
   float acc[RT][NT][4];
 #pragma unroll
   for (int t = 0; t < RT; ++t)
@@ -86,43 +94,50 @@ __global__ void __launch_bounds__(WARPS * 32) linear_skinny_kernel(const __nv_bf
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[t][j][e] = 0.f;
 
-  // Each thread streams its own 16-byte pieces through a private ring of D stages in shared memory
-  // (cp.async): a stage holds, for one chunk of 32 k, the thread's 2 RT pieces of weight rows and NT pieces
-  // of x rows.  A thread reads back only what it copied itself, so no barrier is needed; the ring keeps
-  // D - 1 stages of loads in flight while one is consumed.
-  extern __shared__ uint4 ring[];
-  constexpr int LOADS = 2 * RT + NT;
-  constexpr int THREADS = WARPS * 32;
+  // Each thread streams its own 16-byte pieces through a private ring of D stages in shared memory: a stage
+  // holds, for one chunk of 32 k, the thread's WL pieces of weight rows and NT pieces of x rows.  A thread
+  // reads back only what it copied itself, so no barrier is needed.
   const int chunks = (K + 31) / 32;
   const int my_chunks = chunks > warp ? (chunks - warp + WARPS - 1) / WARPS : 0;
-  auto issue = [&](int i) {
+  auto issue_w = [&](int i) {
     if (i < my_chunks) {
       const int k0 = (warp + i * WARPS) * 32;
       const bool kok = k0 + 8 * c + 8 <= K;  // K is a multiple of 8: a lane's 8 values are all inside or all outside
       uint4* st = ring + (size_t)(i % D) * LOADS * THREADS + threadIdx.x;
 #pragma unroll
-      for (int t = 0; t < RT; ++t) {
-        cp_async16(st + (2 * t) * THREADS, wp[t][0] + (kok ? k0 : 0), kok, false);
-        cp_async16(st + (2 * t + 1) * THREADS, wp[t][1] + (kok ? k0 : 0), kok, false);
-      }
+      for (int t = 0; t < RT; ++t)
 #pragma unroll
-      for (int j = 0; j < NT; ++j) cp_async16(st + (2 * RT + j) * THREADS, xp[j] + (kok ? k0 : 0), kok && xok[j], true);
+        for (int h = 0; h < HALVES; ++h) cp_async16(st + (t * HALVES + h) * THREADS, wp[t][h] + (kok ? k0 : 0), kok, false);
     }
-    cp_async_commit();
+  };
+  auto issue_x = [&](int i) {
+    if (i < my_chunks) {
+      const int k0 = (warp + i * WARPS) * 32;
+      const bool kok = k0 + 8 * c + 8 <= K;
+      uint4* st = ring + (size_t)(i % D) * LOADS * THREADS + threadIdx.x;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) cp_async16(st + (WL + j) * THREADS, xp[j] + (kok ? k0 : 0), kok && xok[j], true);
+    }
   };
 #pragma unroll
-  for (int i = 0; i < D; ++i) issue(i);
+  for (int i = 0; i < D; ++i) issue_w(i);  // weights: before the wait for the kernel that produces x
+  cp_async_commit();
+  pdl_wait();
+#pragma unroll
+  for (int i = 0; i < D; ++i) issue_x(i);
+  cp_async_commit();
+  cp_async_wait<0>();
   for (int i = 0; i < my_chunks; ++i) {
     cp_async_wait<D - 1>();
     const uint4* st = ring + (size_t)(i % D) * LOADS * THREADS + threadIdx.x;
     uint4 a[RT][2], b[NT];
 #pragma unroll
     for (int t = 0; t < RT; ++t) {
-      a[t][0] = st[(2 * t) * THREADS];
-      a[t][1] = st[(2 * t + 1) * THREADS];
+      a[t][0] = st[(t * HALVES) * THREADS];
+      a[t][1] = st[(t * HALVES + 1) * THREADS];
     }
 #pragma unroll
-    for (int j = 0; j < NT; ++j) b[j] = st[(2 * RT + j) * THREADS];
+    for (int j = 0; j < NT; ++j) b[j] = st[(WL + j) * THREADS];
 #pragma unroll
     for (int t = 0; t < RT; ++t)
 #pragma unroll
@@ -130,7 +145,9 @@ __global__ void __launch_bounds__(WARPS * 32) linear_skinny_kernel(const __nv_bf
         mma_bf16(acc[t][j], a[t][0].x, a[t][1].x, a[t][0].y, a[t][1].y, b[j].x, b[j].y);
         mma_bf16(acc[t][j], a[t][0].z, a[t][1].z, a[t][0].w, a[t][1].w, b[j].z, b[j].w);
       }
-    issue(i + D);  // into the stage just consumed
+    issue_w(i + D);  // into the stage just consumed
+    issue_x(i + D);
+    cp_async_commit();
   }
   cp_async_wait<0>();
 
@@ -153,14 +170,14 @@ __global__ void __launch_bounds__(WARPS * 32) linear_skinny_kernel(const __nv_bf
     for (int e = 0; e < 4; ++e) red[0][t][j][lane][e] = s[e];
   }
   __syncthreads();
-  // epilogue: element e of a lane is (weight row g + 8 (e / 2), batch row 2 c + (e % 2)) of its tile
-  if (GLU) {
-    for (int i = threadIdx.x; i < NT * 32 * 4; i += WARPS * 32) {
-      const int j = i / 128, l = (i / 4) % 32, e = i % 4;
-      const int row = blockIdx.x * 16 + (l >> 2) + 8 * (e >> 1);
-      const int m = j * 8 + 2 * (l & 3) + (e & 1);
+  // epilogue: element e of a lane is (mma row g + 8 (e / 2), batch row 2 c + (e % 2)) of its tile
+  if (MODE == GLU8) {
+    for (int i = threadIdx.x; i < RT * NT * 32 * 2; i += THREADS) {
+      const int t = i / (NT * 64), j = (i / 64) % NT, l = (i / 2) % 32, e = i % 2;
+      const int row = (blockIdx.x * RT + t) * 8 + (l >> 2);
+      const int m = j * 8 + 2 * (l & 3) + e;
       if (row < hidden && m < M) {
-        float gate = red[0][0][j][l][e], up = red[0][1][j][l][e];
+        float gate = red[0][t][j][l][e], up = red[0][t][j][l][e + 2];
         if (bias) {
           gate += __bfloat162float(bias[row]);
           up += __bfloat162float(bias[hidden + row]);
@@ -169,9 +186,10 @@ __global__ void __launch_bounds__(WARPS * 32) linear_skinny_kernel(const __nv_bf
       }
     }
   } else {
-    for (int i = threadIdx.x; i < RT * NT * 32 * 4; i += WARPS * 32) {
-      const int t = i / (NT * 128), j = (i / 128) % NT, l = (i / 4) % 32, e = i % 4;
-      const int row = (blockIdx.x * RT + t) * 16 + (l >> 2) + 8 * (e >> 1);
+    constexpr int EL = 4;
+    for (int i = threadIdx.x; i < RT * NT * 32 * EL; i += THREADS) {
+      const int t = i / (NT * 32 * EL), j = (i / (32 * EL)) % NT, l = (i / EL) % 32, e = i % EL;
+      const int row = (blockIdx.x * RT + t) * TILE_ROWS + (l >> 2) + 8 * (e >> 1);
       const int m = j * 8 + 2 * (l & 3) + (e & 1);
       if (row < N && m < M) {
         float v = red[0][t][j][l][e];
@@ -182,30 +200,33 @@ __global__ void __launch_bounds__(WARPS * 32) linear_skinny_kernel(const __nv_bf
   }
 }
 
-template <int NT, int RT, bool GLU, typename TOut>
+template <int NT, int RT, int MODE, typename TOut>
 int launch_typed(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int hidden, int act,
                  cudaStream_t stream) {
-  constexpr int LOADS = 2 * RT + NT;
-  constexpr int D = LOADS <= 3 ? 5 : (LOADS == 4 ? 4 : 3);  // 60 to 72 KB of ring per block
-  constexpr size_t smem = (size_t)D * LOADS * WARPS * 32 * sizeof(uint4);
-  auto kernel = linear_skinny_kernel<NT, RT, GLU, D, TOut>;
+  constexpr int LOADS = RT * 2 + NT;
+  constexpr int D = LOADS <= 2 ? 7 : (LOADS == 3 ? 5 : (LOADS == 4 ? 4 : 3));  // 56 to 72 KB of ring per block
+  constexpr size_t smem = (size_t)D * LOADS * THREADS * sizeof(uint4);
+  auto kernel = linear_skinny_kernel<NT, RT, MODE, D, TOut>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fms_fail("linear_bf16_skinny: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  const int tiles = GLU ? (hidden + 15) / 16 : (N + 16 * RT - 1) / (16 * RT);
-  kernel<<<tiles, WARPS * 32, smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
-                                              (const __nv_bfloat16*)bias, (TOut*)y, M, N, K, hidden, act);
-  return fms_launch_status("linear_bf16_skinny");
+  constexpr int TILE_ROWS = MODE == ROWS16 ? 16 : 8;
+  const int rows = MODE == GLU8 ? hidden : N;
+  const int blocks = (rows + TILE_ROWS * RT - 1) / (TILE_ROWS * RT);
+  cudaError_t e = fms_launch(kernel, dim3(blocks), dim3(THREADS), smem, stream, (const __nv_bfloat16*)x,
+                             (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, (TOut*)y, M, N, K, hidden, act);
+  if (e != cudaSuccess) return fms_fail("linear_bf16_skinny: launch failed: %s", cudaGetErrorString(e));
+  return 0;
 }
 
-template <int NT, int RT, bool GLU>
+template <int NT, int RT, int MODE>
 int launch(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M, int N, int K, int hidden,
            int act, cudaStream_t stream) {
-  if (out_dtype == FMS_F32) return launch_typed<NT, RT, GLU, float>(x, w, bias, y, M, N, K, hidden, act, stream);
-  return launch_typed<NT, RT, GLU, __nv_bfloat16>(x, w, bias, y, M, N, K, hidden, act, stream);
+  if (out_dtype == FMS_F32) return launch_typed<NT, RT, MODE, float>(x, w, bias, y, M, N, K, hidden, act, stream);
+  return launch_typed<NT, RT, MODE, __nv_bfloat16>(x, w, bias, y, M, N, K, hidden, act, stream);
 }
 }  // namespace
 
@@ -218,13 +239,13 @@ FMS_API int fms_linear_bf16_skinny(const void* x, const void* w, const void* bia
   if (M > 16) return fms_fail("linear_bf16_skinny: %d rows, at most 16", M);
   if (K <= 0 || K % 8) return fms_fail("linear_bf16_skinny: K %d must be a positive multiple of 8", K);
   if (out_dtype != FMS_F32 && out_dtype != FMS_BF16) return fms_fail("linear_bf16_skinny: out dtype %d", out_dtype);
-  const bool wide = N >= 16384;  // many rows: two tiles per block halve the re-reading of x
+  // very many weight rows: 32 rows a block, which halves the re-reading of x
   if (M <= 8) {
-    return wide ? launch<1, 2, false>(x, w, bias, y, out_dtype, M, N, K, 0, 0, stream)
-                : launch<1, 1, false>(x, w, bias, y, out_dtype, M, N, K, 0, 0, stream);
+    if (N < 16384) return launch<1, 1, ROWS16>(x, w, bias, y, out_dtype, M, N, K, 0, 0, stream);
+    return launch<1, 2, ROWS16>(x, w, bias, y, out_dtype, M, N, K, 0, 0, stream);
   }
-  return wide ? launch<2, 2, false>(x, w, bias, y, out_dtype, M, N, K, 0, 0, stream)
-              : launch<2, 1, false>(x, w, bias, y, out_dtype, M, N, K, 0, 0, stream);
+  if (N < 16384) return launch<2, 1, ROWS16>(x, w, bias, y, out_dtype, M, N, K, 0, 0, stream);
+  return launch<2, 2, ROWS16>(x, w, bias, y, out_dtype, M, N, K, 0, 0, stream);
 }
 
 // y [M, hidden] = act(x w_gate^T + b_gate) * (x w_up^T + b_up) with w = [gate; up] of 2 hidden rows.
@@ -234,6 +255,6 @@ FMS_API int fms_glu_bf16_skinny(const void* x, const void* w, const void* bias, 
   if (M > 16) return fms_fail("glu_bf16_skinny: %d rows, at most 16", M);
   if (K <= 0 || K % 8) return fms_fail("glu_bf16_skinny: K %d must be a positive multiple of 8", K);
   if (act < 0 || act > 3) return fms_fail("glu_bf16_skinny: activation %d", act);
-  if (M <= 8) return launch<1, 2, true>(x, w, bias, y, FMS_BF16, M, 2 * hidden, K, hidden, act, stream);
-  return launch<2, 2, true>(x, w, bias, y, FMS_BF16, M, 2 * hidden, K, hidden, act, stream);
+  if (M <= 8) return launch<1, 2, GLU8>(x, w, bias, y, FMS_BF16, M, 2 * hidden, K, hidden, act, stream);
+  return launch<2, 2, GLU8>(x, w, bias, y, FMS_BF16, M, 2 * hidden, K, hidden, act, stream);
 }

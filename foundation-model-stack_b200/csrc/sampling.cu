@@ -28,6 +28,8 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict
                                                          int vocab) {
   __shared__ float best_v[WARPS];
   __shared__ int best_i[WARPS];
+  pdl_launch_dependents();
+  pdl_wait();
   const float* x = logits + (size_t)blockIdx.x * vocab;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
@@ -184,7 +186,7 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
 FMS_API int fms_argmax(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return fms_fail("argmax: vocab %d", vocab);
-  argmax_kernel<<<rows, THREADS, 0, stream>>>(logits, out, vocab);
+  fms_launch(argmax_kernel, dim3(rows), dim3(THREADS), 0, stream, logits, out, vocab);
   return fms_launch_status("argmax");
 }
 

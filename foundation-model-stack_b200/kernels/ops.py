@@ -106,7 +106,8 @@ def check_error_flag(device) -> None:
     if v:
         flag.zero_()
         raise KernelError({1: "a token id outside the vocabulary reached the embedding",
-                           2: "a token's position has no cache block"}.get(v, f"device error flag {v}"))
+                           2: "a token's position has no cache block",
+                           3: "a bulk copy into shared memory did not complete in time"}.get(v, f"device error flag {v}"))
 
 
 # ---- embedding ---------------------------------------------------------------------------------------

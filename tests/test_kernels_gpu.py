@@ -102,7 +102,7 @@ def test_linear_bfloat16(ops, m, n, k):
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("n,k", [(331, 240), (40, 8), (4096 + 16, 1000), (16400, 96)])
+@pytest.mark.parametrize("n,k", [(331, 240), (40, 8), (4096 + 16, 1000), (16400, 96), (331, 256), (4099, 1152), (7, 128)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_linear_bfloat16_few_rows(ops, m, n, k, out_dtype):
     """The weight-streaming kernel of decode steps: odd numbers of weight rows, K that is no multiple of 32,
@@ -123,7 +123,7 @@ def test_linear_bfloat16_few_rows(ops, m, n, k, out_dtype):
 
 
 @pytest.mark.parametrize("m", [1, 8, 13])
-@pytest.mark.parametrize("hidden,k", [(176, 64), (328, 240), (1000, 96), (14336, 128)])
+@pytest.mark.parametrize("hidden,k", [(176, 64), (328, 240), (1000, 96), (14336, 128), (331, 384), (5, 1024)])
 @pytest.mark.parametrize("act", [0, 2])
 def test_gated_linear_few_rows(ops, m, hidden, k, act):
     g = torch.Generator().manual_seed(50 + m)
