@@ -1,0 +1,321 @@
+// y[M, N] = x[M, K] . w[N, K]^T for many rows (prefill): bfloat16 operands, float32 accumulation in tensor
+// memory, on the fifth-generation tensor cores of sm_100a (tcgen05.mma issued by one thread, operands brought
+// into shared memory by TMA, the accumulator read back with tcgen05.ld for the epilogue).
+//
+// One thread block computes one 128 x 256 tile of y (128 rows of x against 256 rows of w) — or, in the GLU
+// variant, a 128 x 128 tile of act(x w_gate^T) * (x w_up^T), whose 256 accumulator columns are 128 gate and
+// the 128 matching up rows of a fused [gate; up] weight (fms/modules/feedforward.py:288-297).
+//
+//   warp 0   one lane issues the TMA loads: per step of 64 k, a 128 x 64 box of x and two 128 x 64 boxes of w
+//            (128-byte swizzle) into one of 4 stages, completion counted on the stage's "full" mbarrier
+//   warp 1   allocates 256 columns of tensor memory; one lane waits for "full", issues 4 tcgen05.mma
+//            (128 x 256 x 16 each) on the stage and commits them to the stage's "empty" mbarrier; after the last
+//            step it commits to the "accumulator ready" mbarrier
+//   warps 2-5  wait for the accumulator, read their 32 rows of it 32 columns at a time, convert and store
+//
+// Every wait on an mbarrier is bounded: on a time-out the block records error 4 in the error flag, skips the
+// rest of its work and still frees its tensor memory.  Rows and columns beyond M, N and K are filled with zeros
+// by TMA on the way in and are not stored on the way out.  K must be a multiple of 8 (16-byte row pitch).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+constexpr int TILE_M = 128, TILE_N = 256, TILE_K = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_BYTES = TILE_M * TILE_K * 2, B_BYTES = TILE_N * TILE_K * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;
+constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, void* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(void* smem_result, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(smem_result)), "r"(columns)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+// arrives on the mbarrier once all tcgen05.mma issued so far by this thread are done
+__device__ __forceinline__ void tc_commit(void* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// shared-memory matrix descriptor: K-major rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+// instruction descriptor: float32 accumulator, bfloat16 a and b, both K-major, M = 128, N = 256
+constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TILE_N >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u, zero = 0u;
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(IDESC), "r"(acc), "r"(zero)
+      : "memory");
+}
+// 32 consecutive float32 columns of this thread's row (lane) of tensor memory
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+      "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
+        "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
+        "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ float activate(float g, int act) {
+  switch (act) {
+    case 0: return g / (1.f + expf(-g));
+    case 1: return 0.5f * g * (1.f + erff(g * 0.70710678118654752f));
+    case 2: return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    default: return fmaxf(g, 0.f);
+  }
+}
+
+struct Epilogue {
+  void* out;          // [M, N] bfloat16 or float32; GLU: [M, hidden] bfloat16
+  const void* bias;   // bfloat16 [N] (GLU: [2 hidden]) or null
+  int out_f32;        // plain only
+  int glu;            // 1: columns 0-127 of the accumulator are gate rows, 128-255 the matching up rows
+  int hidden;         // GLU: rows of the gate matrix
+  int act;
+};
+
+__global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                             const __grid_constant__ CUtensorMap map_b, Epilogue ep, int M,
+                                                             int N, int K, int* __restrict__ error_flag) {
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* accum = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  __shared__ int failed;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * TILE_M;
+  const int n0 = blockIdx.x * (ep.glu ? TILE_N / 2 : TILE_N);  // first output column of this tile
+  const int k_steps = (K + TILE_K - 1) / TILE_K;
+
+  if (threadIdx.x == 0) {
+    failed = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(accum, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TILE_N);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      for (int i = 0; i < k_steps; ++i) {
+        const int s = i % STAGES;
+        if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1)) {
+          atomicExch(&failed, 1);
+          break;
+        }
+        unsigned char* a = smem + (size_t)s * STAGE_BYTES;
+        unsigned char* b = a + A_BYTES;
+        mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+        tma_load_2d(a, &map_a, i * TILE_K, m0, &full[s]);
+        // the tile's 256 rows of w: a whole range, or 128 gate rows and the 128 up rows that belong to them
+        tma_load_2d(b, &map_b, i * TILE_K, n0, &full[s]);
+        tma_load_2d(b + B_BYTES / 2, &map_b, i * TILE_K, ep.glu ? ep.hidden + n0 : n0 + TILE_N / 2, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      bool ok = true;
+      for (int i = 0; i < k_steps && ok; ++i) {
+        const int s = i % STAGES;
+        if (!mbar_wait(&full[s], (i / STAGES) & 1)) {
+          atomicExch(&failed, 1);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a = smem_u32(smem + (size_t)s * STAGE_BYTES), b = a + A_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < TILE_K / UMMA_K; ++kk)
+          umma(tmem, umma_desc(a + kk * UMMA_K * 2), umma_desc(b + kk * UMMA_K * 2), i > 0 || kk > 0);
+        tc_commit(&empty[s]);  // the stage may be filled again once these mma have read it
+      }
+      tc_commit(accum);  // arrives when everything issued above is done (at once if nothing was issued)
+    }
+  } else {
+    // epilogue warps 2..5 own the accumulator rows 32 (warp % 4) .. + 31
+    const bool ready = mbar_wait(accum, 0);
+    if (!ready) atomicExch(&failed, 1);
+    tc_fence_after();
+    const int quarter = warp & 3;
+    const int row = m0 + quarter * 32 + lane;
+    if (ready && failed == 0) {
+      const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16);
+      if (ep.glu) {
+        __nv_bfloat16* out = (__nv_bfloat16*)ep.out;
+        const __nv_bfloat16* bias = (const __nv_bfloat16*)ep.bias;
+        for (int c0 = 0; c0 < TILE_N / 2; c0 += 32) {
+          float g[32], u[32];
+          tmem_load_32(taddr + c0, g);
+          tmem_load_32(taddr + TILE_N / 2 + c0, u);
+          if (row < M) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = n0 + c0 + j;
+              if (col < ep.hidden) {
+                float gv = g[j], uv = u[j];
+                if (bias) {
+                  gv += __bfloat162float(bias[col]);
+                  uv += __bfloat162float(bias[ep.hidden + col]);
+                }
+                out[(size_t)row * ep.hidden + col] = __float2bfloat16_rn(activate(gv, ep.act) * uv);
+              }
+            }
+          }
+        }
+      } else {
+        const __nv_bfloat16* bias = (const __nv_bfloat16*)ep.bias;
+        for (int c0 = 0; c0 < TILE_N; c0 += 32) {
+          float v[32];
+          tmem_load_32(taddr + c0, v);
+          if (row < M) {
+            if (bias) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n0 + c0 + j < N) v[j] += __bfloat162float(bias[n0 + c0 + j]);
+            }
+            if (ep.out_f32) {
+              float* o = (float*)ep.out + (size_t)row * N + n0 + c0;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n0 + c0 + j < N) o[j] = v[j];
+            } else {
+              __nv_bfloat16* o = (__nv_bfloat16*)ep.out + (size_t)row * N + n0 + c0;
+              if (n0 + c0 + 32 <= N && (N % 8) == 0) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  uint4 p;
+                  __nv_bfloat162 t0 = __floats2bfloat162_rn(v[j], v[j + 1]), t1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                  __nv_bfloat162 t2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), t3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                  p.x = *reinterpret_cast<uint32_t*>(&t0);
+                  p.y = *reinterpret_cast<uint32_t*>(&t1);
+                  p.z = *reinterpret_cast<uint32_t*>(&t2);
+                  p.w = *reinterpret_cast<uint32_t*>(&t3);
+                  *reinterpret_cast<uint4*>(o + j) = p;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (n0 + c0 + j < N) o[j] = __float2bfloat16_rn(v[j]);
+              }
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && failed && error_flag) atomicExch(error_flag, 4);
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TILE_N);
+  }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+  static EncodeTiled fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiled)p;
+  }
+  return fn;
+}
+
+// a [rows, K] bfloat16 matrix, K contiguous, loaded in boxes of 128 rows x 64 k with the 128-byte swizzle
+int make_map(CUtensorMap* map, const void* base, int rows, int K) {
+  EncodeTiled enc = encode_tiled();
+  if (enc == nullptr) return fms_fail("gemm_tc: the driver does not export cuTensorMapEncodeTiled");
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {TILE_K, 128};
+  const cuuint32_t elem[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fms_fail("gemm_tc: cuTensorMapEncodeTiled failed with %d (rows %d, K %d)", (int)r, rows, K);
+  return 0;
+}
+
+int launch(const void* x, const void* w, int w_rows, const Epilogue& ep, int M, int N, int K, int* error_flag,
+           cudaStream_t stream) {
+  if (K <= 0 || K % 8) return fms_fail("gemm_tc: K %d must be a positive multiple of 8", K);
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return fms_fail("gemm_tc: operands must be 16-byte aligned");
+  CUtensorMap map_a, map_b;
+  if (make_map(&map_a, x, M, K) || make_map(&map_b, w, w_rows, K)) return 1;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (e != cudaSuccess) return fms_fail("gemm_tc: %zu bytes of shared memory refused: %s", SMEM_BYTES, cudaGetErrorString(e));
+    configured = true;
+  }
+  const int tile_n = ep.glu ? TILE_N / 2 : TILE_N;
+  dim3 grid((N + tile_n - 1) / tile_n, (M + TILE_M - 1) / TILE_M);
+  if (grid.y > 65535) return fms_fail("gemm_tc: %d rows are more than one launch takes", M);
+  gemm_tc_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, ep, M, N, K, error_flag);
+  return fms_launch_status("gemm_tc");
+}
+}  // namespace
+
+// y [M, N] (bfloat16 or float32) = x [M, K] w[N, K]^T + bias; x, w, bias bfloat16.
+FMS_API int fms_gemm_bf16_tc(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M, int N, int K,
+                             int* error_flag, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (out_dtype != FMS_F32 && out_dtype != FMS_BF16) return fms_fail("gemm_tc: out dtype %d", out_dtype);
+  Epilogue ep{y, bias, out_dtype == FMS_F32 ? 1 : 0, 0, 0, 0};
+  return launch(x, w, N, ep, M, N, K, error_flag, stream);
+}
+
+// y [M, hidden] bfloat16 = act(x w_gate^T + b_gate) * (x w_up^T + b_up), w = [gate; up] of 2 hidden rows.
+FMS_API int fms_glu_bf16_tc(const void* x, const void* w, const void* bias, void* y, int M, int hidden, int K, int act,
+                            int* error_flag, cudaStream_t stream) {
+  if (M <= 0 || hidden <= 0) return 0;
+  if (act < 0 || act > 3) return fms_fail("glu_tc: activation %d", act);
+  Epilogue ep{y, bias, 0, 1, hidden, act};
+  return launch(x, w, 2 * hidden, ep, M, hidden, K, error_flag, stream);
+}

@@ -82,7 +82,7 @@ class Engine:
         if self.decoder.dtype == torch.float32 or any(t.dtype == torch.float32 and t.dim() == 2 for t in tensors):
             names.append("gemm_f32")
         if self.decoder.dtype == torch.bfloat16:
-            names.append("gemm_bf16_skinny")
+            names += ["gemm_bf16_skinny", "gemm_bf16_tc"]
         for block in self.decoder.blocks:
             hd = getattr(block.mixer, "head_dim", None)
             if hd and getattr(block.mixer, "kvheads", None):

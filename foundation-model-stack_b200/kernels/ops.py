@@ -11,6 +11,7 @@ product (cuBLAS through ``torch.nn.functional.linear``), as the reference does f
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -29,6 +30,8 @@ _SIGNATURES = {
     "fms_gemm_f32": [_P, _P, _P, _P, _I, _I, _I, _P],
     "fms_linear_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "fms_glu_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "fms_gemm_bf16_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
+    "fms_glu_bf16_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "fms_argmax": [_P, _P, _I, _I, _P],
     "fms_sample": [_P, _P, _I, _I, _F, _I, _U64, _P, _I, _P],
     "fms_attention_prefill": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
@@ -107,7 +110,7 @@ def check_error_flag(device) -> None:
         flag.zero_()
         raise KernelError({1: "a token id outside the vocabulary reached the embedding",
                            2: "a token's position has no cache block",
-                           3: "a bulk copy into shared memory did not complete in time"}.get(v, f"device error flag {v}"))
+                           4: "the tensor-core product gave up waiting for a copy or for the tensor cores"}.get(v, f"device error flag {v}"))
 
 
 # ---- embedding ---------------------------------------------------------------------------------------
@@ -159,11 +162,44 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         _call("gemm_bf16_skinny", "fms_linear_bf16_skinny", _ptr(x), _ptr(weight), _ptr(bias), _ptr(y), _code(out_dtype),
               x.shape[0], weight.shape[0], weight.shape[1], _stream())
         return y
+    if _tensor_core_fits(x, weight, bias):
+        return linear_tensor_core(x, weight, bias, out_dtype)
     if out_dtype == torch.float32:
         y = torch.mm(x, weight.t(), out_dtype=torch.float32)
         return y if bias is None else y + bias.float()
     b = None if bias is None else bias.to(torch.bfloat16)
     return torch.nn.functional.linear(x, weight, b)
+
+
+TENSOR_CORE_ROWS = 256  # rows from which the tcgen05 kernel is used instead of the library product
+USE_TENSOR_CORE_GEMM = os.environ.get("FMS_B200_TC_GEMM", "1") != "0"
+
+
+def _tensor_core_fits(x, weight, bias) -> bool:
+    return (USE_TENSOR_CORE_GEMM and x.shape[0] >= TENSOR_CORE_ROWS and weight.shape[1] % 8 == 0
+            and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and (bias is None or bias.dtype == torch.bfloat16))
+
+
+def linear_tensor_core(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                       out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """The product on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory): bfloat16 in, bfloat16 or
+    float32 out.  K must be a multiple of 8."""
+    out_dtype = out_dtype or x.dtype
+    y = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
+    _call("gemm_bf16_tc", "fms_gemm_bf16_tc", _ptr(x), _ptr(weight), _ptr(bias), _ptr(y), _code(out_dtype), x.shape[0],
+          weight.shape[0], weight.shape[1], _ptr(error_flag(x.device)), _stream())
+    return y
+
+
+def gated_linear_tensor_core(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                             activation: int) -> torch.Tensor:
+    """act(x Wg^T) * (x Wu^T) in one tcgen05 kernel: gate and up rows share a tile, the epilogue multiplies."""
+    hidden = weight.shape[0] // 2
+    y = torch.empty((x.shape[0], hidden), dtype=torch.bfloat16, device=x.device)
+    _call("gemm_bf16_tc", "fms_glu_bf16_tc", _ptr(x), _ptr(weight), _ptr(bias), _ptr(y), x.shape[0], hidden,
+          weight.shape[1], int(activation), _ptr(error_flag(x.device)), _stream())
+    return y
 
 
 SKINNY_ROWS = 16  # rows up to which the weight-streaming kernels are used
@@ -181,6 +217,8 @@ def gated_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
         _call("gemm_bf16_skinny", "fms_glu_bf16_skinny", _ptr(x), _ptr(weight), _ptr(bias), _ptr(y), x.shape[0], hidden,
               weight.shape[1], int(activation), _stream())
         return y
+    if _tensor_core_fits(x, weight, bias):
+        return gated_linear_tensor_core(x, weight, bias, activation)
     return gated_activation(linear(x, weight, bias), activation)
 
 
