@@ -2,16 +2,18 @@
 // memory, on the fifth-generation tensor cores of sm_100a (tcgen05.mma issued by one thread, operands brought
 // into shared memory by TMA, the accumulator read back with tcgen05.ld for the epilogue).
 //
-// One thread block computes one 128 x 256 tile of y (128 rows of x against 256 rows of w) — or, in the GLU
-// variant, a 128 x 128 tile of act(x w_gate^T) * (x w_up^T), whose 256 accumulator columns are 128 gate and
-// the 128 matching up rows of a fused [gate; up] weight (fms/modules/feedforward.py:288-297).
+// A tile of y is 128 x 256 (128 rows of x against 256 rows of w) — or, in the GLU variant, a 128 x 128 tile of
+// act(x w_gate^T) * (x w_up^T), whose 256 accumulator columns are 128 gate and the 128 matching up rows of a
+// fused [gate; up] weight (fms/modules/feedforward.py:288-297).  One persistent thread block per
+// multiprocessor walks over the tiles.
 //
 //   warp 0   one lane issues the TMA loads: per step of 64 k, a 128 x 64 box of x and two 128 x 64 boxes of w
 //            (128-byte swizzle) into one of 4 stages, completion counted on the stage's "full" mbarrier
-//   warp 1   allocates 256 columns of tensor memory; one lane waits for "full", issues 4 tcgen05.mma
-//            (128 x 256 x 16 each) on the stage and commits them to the stage's "empty" mbarrier; after the last
-//            step it commits to the "accumulator ready" mbarrier
-//   warps 2-5  wait for the accumulator, read their 32 rows of it 32 columns at a time, convert and store
+//   warp 1   allocates all 512 columns of tensor memory (two accumulators); one lane waits for "full", issues 4
+//            tcgen05.mma (128 x 256 x 16 each) on the stage and commits them to the stage's "empty" mbarrier;
+//            after a tile's last step it commits to that accumulator's "ready" mbarrier
+//   warps 2-5  wait for an accumulator, read their 32 rows of it 32 columns at a time, convert, store, and
+//            give the accumulator back, while the mma warp already works on the next tile in the other one
 //
 // Every wait on an mbarrier is bounded: on a time-out the block records error 4 in the error flag, skips the
 // rest of its work and still frees its tensor memory.  Rows and columns beyond M, N and K are filled with zeros
@@ -103,6 +105,31 @@ struct Epilogue {
   int act;
 };
 
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// mbar_wait that also gives up as soon as another role of the block has recorded a failure
+__device__ __forceinline__ bool wait_or_abort(void* bar, uint32_t parity, volatile int* failed) {
+  const uint32_t addr = smem_u32(bar);
+  for (int i = 0; i < (1 << 22); ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((i & 255) == 255 && *failed) return false;
+  }
+  *failed = 1;
+  return false;
+}
+
+// Persistent: block b computes tiles b, b + gridDim.x, ...; tiles are numbered with the row index fastest, so
+// that the blocks running at the same time share few tiles of w.  The accumulator is double-buffered in tensor
+// memory (2 x 256 columns): the epilogue of a tile runs while the mma of the block's next tile are issued.
+// Barriers that a consumer gives back ("empty") are waited for with the opposite parity, which a freshly
+// initialised mbarrier satisfies at once.
 __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                              const __grid_constant__ CUtensorMap map_b, Epilogue ep, int M,
                                                              int N, int K, int* __restrict__ error_flag) {
@@ -110,25 +137,31 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)STAGES * STAGE_BYTES);
   uint64_t* empty = full + STAGES;
-  uint64_t* accum = empty + STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
-  __shared__ int failed;
+  uint64_t* acc_full = empty + STAGES;   // [2]
+  uint64_t* acc_empty = acc_full + 2;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  __shared__ int failed_flag;
+  volatile int* failed = &failed_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * TILE_M;
-  const int n0 = blockIdx.x * (ep.glu ? TILE_N / 2 : TILE_N);  // first output column of this tile
+  const int tile_n = ep.glu ? TILE_N / 2 : TILE_N;  // output columns of a tile
+  const int tiles_m = (M + TILE_M - 1) / TILE_M, tiles_n = (N + tile_n - 1) / tile_n;
+  const int n_tiles = tiles_m * tiles_n;
   const int k_steps = (K + TILE_K - 1) / TILE_K;
 
   if (threadIdx.x == 0) {
-    failed = 0;
+    failed_flag = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(accum, 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
+    }
     mbar_fence_init();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, TILE_N);
+  if (warp == 1) tmem_alloc(tmem_slot, 2 * TILE_N);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -136,49 +169,54 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
 
   if (warp == 0) {
     if (elect_one()) {
-      for (int i = 0; i < k_steps; ++i) {
-        const int s = i % STAGES;
-        if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1)) {
-          atomicExch(&failed, 1);
-          break;
+      int it = 0;  // steps issued so far, over all tiles
+      for (int tile = blockIdx.x; tile < n_tiles && !*failed; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * TILE_M, n0 = (tile / tiles_m) * tile_n;
+        for (int i = 0; i < k_steps; ++i, ++it) {
+          const int s = it % STAGES;
+          if (!wait_or_abort(&empty[s], ((it / STAGES) & 1) ^ 1, failed)) break;
+          unsigned char* a = smem + (size_t)s * STAGE_BYTES;
+          unsigned char* b = a + A_BYTES;
+          mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+          tma_load_2d(a, &map_a, i * TILE_K, m0, &full[s]);
+          // the tile's 256 rows of w: a whole range, or 128 gate rows and the 128 up rows that belong to them
+          tma_load_2d(b, &map_b, i * TILE_K, n0, &full[s]);
+          tma_load_2d(b + B_BYTES / 2, &map_b, i * TILE_K, ep.glu ? ep.hidden + n0 : n0 + TILE_N / 2, &full[s]);
         }
-        unsigned char* a = smem + (size_t)s * STAGE_BYTES;
-        unsigned char* b = a + A_BYTES;
-        mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
-        tma_load_2d(a, &map_a, i * TILE_K, m0, &full[s]);
-        // the tile's 256 rows of w: a whole range, or 128 gate rows and the 128 up rows that belong to them
-        tma_load_2d(b, &map_b, i * TILE_K, n0, &full[s]);
-        tma_load_2d(b + B_BYTES / 2, &map_b, i * TILE_K, ep.glu ? ep.hidden + n0 : n0 + TILE_N / 2, &full[s]);
       }
     }
   } else if (warp == 1) {
     if (elect_one()) {
-      bool ok = true;
-      for (int i = 0; i < k_steps && ok; ++i) {
-        const int s = i % STAGES;
-        if (!mbar_wait(&full[s], (i / STAGES) & 1)) {
-          atomicExch(&failed, 1);
-          ok = false;
-          break;
-        }
+      int it = 0, j = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && !*failed; tile += gridDim.x, ++j) {
+        const int acc = j & 1;
+        if (!wait_or_abort(&acc_empty[acc], ((j >> 1) & 1) ^ 1, failed)) break;  // the epilogue has read this buffer
         tc_fence_after();
-        const uint32_t a = smem_u32(smem + (size_t)s * STAGE_BYTES), b = a + A_BYTES;
+        const uint32_t d = tmem + acc * TILE_N;
+        for (int i = 0; i < k_steps; ++i, ++it) {
+          const int s = it % STAGES;
+          if (!wait_or_abort(&full[s], (it / STAGES) & 1, failed)) break;
+          tc_fence_after();
+          const uint32_t a = smem_u32(smem + (size_t)s * STAGE_BYTES), b = a + A_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < TILE_K / UMMA_K; ++kk)
-          umma(tmem, umma_desc(a + kk * UMMA_K * 2), umma_desc(b + kk * UMMA_K * 2), i > 0 || kk > 0);
-        tc_commit(&empty[s]);  // the stage may be filled again once these mma have read it
+          for (int kk = 0; kk < TILE_K / UMMA_K; ++kk)
+            umma(d, umma_desc(a + kk * UMMA_K * 2), umma_desc(b + kk * UMMA_K * 2), i > 0 || kk > 0);
+          tc_commit(&empty[s]);  // the stage may be filled again once these mma have read it
+        }
+        tc_commit(&acc_full[acc]);  // arrives when everything issued so far is done
       }
-      tc_commit(accum);  // arrives when everything issued above is done (at once if nothing was issued)
     }
   } else {
     // epilogue warps 2..5 own the accumulator rows 32 (warp % 4) .. + 31
-    const bool ready = mbar_wait(accum, 0);
-    if (!ready) atomicExch(&failed, 1);
-    tc_fence_after();
     const int quarter = warp & 3;
-    const int row = m0 + quarter * 32 + lane;
-    if (ready && failed == 0) {
-      const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16);
+    int j = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++j) {
+      const int acc = j & 1;
+      const int m0 = (tile % tiles_m) * TILE_M, n0 = (tile / tiles_m) * tile_n;
+      if (!wait_or_abort(&acc_full[acc], (j >> 1) & 1, failed)) break;
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t taddr = tmem + acc * TILE_N + ((uint32_t)(quarter * 32) << 16);
       if (ep.glu) {
         __nv_bfloat16* out = (__nv_bfloat16*)ep.out;
         const __nv_bfloat16* bias = (const __nv_bfloat16*)ep.bias;
@@ -187,16 +225,31 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
           tmem_load_32(taddr + c0, g);
           tmem_load_32(taddr + TILE_N / 2 + c0, u);
           if (row < M) {
+            __nv_bfloat16* o = out + (size_t)row * ep.hidden + n0 + c0;
+            if (n0 + c0 + 32 <= ep.hidden && (ep.hidden % 8) == 0 && bias == nullptr) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int col = n0 + c0 + j;
-              if (col < ep.hidden) {
-                float gv = g[j], uv = u[j];
-                if (bias) {
-                  gv += __bfloat162float(bias[col]);
-                  uv += __bfloat162float(bias[ep.hidden + col]);
+              for (int jj = 0; jj < 32; jj += 8) {
+                uint32_t p[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  __nv_bfloat162 t = __floats2bfloat162_rn(activate(g[jj + 2 * q], ep.act) * u[jj + 2 * q],
+                                                           activate(g[jj + 2 * q + 1], ep.act) * u[jj + 2 * q + 1]);
+                  p[q] = *reinterpret_cast<uint32_t*>(&t);
                 }
-                out[(size_t)row * ep.hidden + col] = __float2bfloat16_rn(activate(gv, ep.act) * uv);
+                *reinterpret_cast<uint4*>(o + jj) = make_uint4(p[0], p[1], p[2], p[3]);
+              }
+            } else {
+#pragma unroll
+              for (int jj = 0; jj < 32; ++jj) {
+                const int col = n0 + c0 + jj;
+                if (col < ep.hidden) {
+                  float gv = g[jj], uv = u[jj];
+                  if (bias) {
+                    gv += __bfloat162float(bias[col]);
+                    uv += __bfloat162float(bias[ep.hidden + col]);
+                  }
+                  o[jj] = __float2bfloat16_rn(activate(gv, ep.act) * uv);
+                }
               }
             }
           }
@@ -209,45 +262,48 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
           if (row < M) {
             if (bias) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (n0 + c0 + j < N) v[j] += __bfloat162float(bias[n0 + c0 + j]);
+              for (int jj = 0; jj < 32; ++jj)
+                if (n0 + c0 + jj < N) v[jj] += __bfloat162float(bias[n0 + c0 + jj]);
             }
             if (ep.out_f32) {
               float* o = (float*)ep.out + (size_t)row * N + n0 + c0;
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (n0 + c0 + j < N) o[j] = v[j];
+              for (int jj = 0; jj < 32; ++jj)
+                if (n0 + c0 + jj < N) o[jj] = v[jj];
             } else {
               __nv_bfloat16* o = (__nv_bfloat16*)ep.out + (size_t)row * N + n0 + c0;
               if (n0 + c0 + 32 <= N && (N % 8) == 0) {
 #pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                  uint4 p;
-                  __nv_bfloat162 t0 = __floats2bfloat162_rn(v[j], v[j + 1]), t1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                  __nv_bfloat162 t2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), t3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                  p.x = *reinterpret_cast<uint32_t*>(&t0);
-                  p.y = *reinterpret_cast<uint32_t*>(&t1);
-                  p.z = *reinterpret_cast<uint32_t*>(&t2);
-                  p.w = *reinterpret_cast<uint32_t*>(&t3);
-                  *reinterpret_cast<uint4*>(o + j) = p;
+                for (int jj = 0; jj < 32; jj += 8) {
+                  uint32_t p[4];
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) {
+                    __nv_bfloat162 t = __floats2bfloat162_rn(v[jj + 2 * q], v[jj + 2 * q + 1]);
+                    p[q] = *reinterpret_cast<uint32_t*>(&t);
+                  }
+                  *reinterpret_cast<uint4*>(o + jj) = make_uint4(p[0], p[1], p[2], p[3]);
                 }
               } else {
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (n0 + c0 + j < N) o[j] = __float2bfloat16_rn(v[j]);
+                for (int jj = 0; jj < 32; ++jj)
+                  if (n0 + c0 + jj < N) o[jj] = __float2bfloat16_rn(v[jj]);
               }
             }
           }
         }
       }
+      // this warp has read its part of the buffer: give it back to the mma warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
     }
     tc_fence_before();
   }
   __syncthreads();
-  if (threadIdx.x == 0 && failed && error_flag) atomicExch(error_flag, 4);
+  if (threadIdx.x == 0 && *failed && error_flag) atomicExch(error_flag, 4);
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem, TILE_N);
+    tmem_dealloc(tmem, 2 * TILE_N);
   }
 }
 
@@ -295,9 +351,15 @@ int launch(const void* x, const void* w, int w_rows, const Epilogue& ep, int M, 
     configured = true;
   }
   const int tile_n = ep.glu ? TILE_N / 2 : TILE_N;
-  dim3 grid((N + tile_n - 1) / tile_n, (M + TILE_M - 1) / TILE_M);
-  if (grid.y > 65535) return fms_fail("gemm_tc: %d rows are more than one launch takes", M);
-  gemm_tc_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, ep, M, N, K, error_flag);
+  const long tiles = (long)((N + tile_n - 1) / tile_n) * ((M + TILE_M - 1) / TILE_M);
+  static int sms = 0;
+  if (sms == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  const int blocks = (int)(tiles < sms ? tiles : sms);  // one persistent block per multiprocessor
+  gemm_tc_kernel<<<blocks, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, ep, M, N, K, error_flag);
   return fms_launch_status("gemm_tc");
 }
 }  // namespace
