@@ -249,7 +249,7 @@ constexpr int PF_ROWS = 16 * PF_WARPS;
 __host__ __device__ inline int prefill_heads_per_block(int group) { return group < PF_ROWS ? group : PF_ROWS; }
 __host__ __device__ inline int prefill_positions_per_block(int group) { return PF_ROWS / prefill_heads_per_block(group); }
 
-__global__ void __launch_bounds__(PF_WARPS * 32) attn_prefill_mma_kernel(AttnArgs a, const int* __restrict__ tiles) {
+__global__ void __launch_bounds__(PF_WARPS * 32, HD <= 128 ? 3 : 1) attn_prefill_mma_kernel(AttnArgs a, const int* __restrict__ tiles) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
   const int group = a.nheads / a.kvheads;
