@@ -378,8 +378,8 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
     // blocks of threads fit on a multiprocessor and one's loads overlap another's arithmetic.
     const int chunks = (group + GROWS - 1) / GROWS;
     const long units = (long)n_seqs * a.kvheads * chunks;
-    const int nw = units >= 256 ? 1 : (units >= 96 || HD > 128 ? 2 : 4);
-    const size_t smem = (size_t)nw * 2 * BLK * ROWB;
+    const int nw = units >= 512 ? 1 : (units >= 192 ? 2 : 4);
+    const size_t smem = (size_t)nw * BLK * ROWB;
     auto kernel = nw == 1 ? attn_decode_mma_kernel<1> : (nw == 2 ? attn_decode_mma_kernel<2> : attn_decode_mma_kernel<4>);
     static bool configured[3] = {false, false, false};
     const int slot = nw == 1 ? 0 : (nw == 2 ? 1 : 2);

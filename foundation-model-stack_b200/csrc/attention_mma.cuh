@@ -64,6 +64,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// asks for `bytes` (a multiple of 16) of global memory to be brought into L2
+__device__ __forceinline__ void prefetch_l2(const void* gmem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(gmem), "r"(bytes) : "memory");
+}
+
 // A warp copies the 64 rows of one cache block (keys or values of one kv head) into its padded buffer.  Rows
 // outside [lo, hi) of the sequence are filled with zeros instead of being read.
 __device__ __forceinline__ void copy_block_async(unsigned char* dst, const __nv_bfloat16* src, int first_pos, int lo,
@@ -106,8 +111,10 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_mma_kernel(AttnArgs a, fl
                            (size_t)(kvh * group + g0) * HD;
   const __nv_bfloat16* kc = (const __nv_bfloat16*)a.keys;
   const __nv_bfloat16* vc = (const __nv_bfloat16*)a.values;
-  unsigned char* kbuf = smem_raw + (size_t)warp * 2 * BLK * ROWB;
-  unsigned char* vbuf = kbuf + BLK * ROWB;
+  // one buffer per warp: first the block's keys, then, once the scores are taken, its values (which were
+  // meanwhile brought into L2), so that a block of threads is small and several fit on a multiprocessor
+  unsigned char* kbuf = smem_raw + (size_t)warp * BLK * ROWB;
+  unsigned char* vbuf = kbuf;
 
   // query fragments: rows g and g + 8 are heads g0 + g and g0 + g + 8 (zero beyond the group)
   uint32_t qf[HD / 16][4];
@@ -129,12 +136,12 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_mma_kernel(AttnArgs a, fl
   for (int kb = k_lo / BLK + warp; kb * BLK < k_hi; kb += NW) {
     const int blk = a.table[(size_t)slot * a.table_stride + kb];
     if (blk < 0) continue;
-    __syncwarp();  // the buffers are free: every lane is past the previous block
+    __syncwarp();  // the buffer is free: every lane is past the previous block
+    const __nv_bfloat16* vsrc = vc + ((size_t)blk * a.kvheads + kvh) * BLK * HD;
     copy_block_async(kbuf, kc + ((size_t)blk * a.kvheads + kvh) * BLK * HD, kb * BLK, k_lo, k_hi, lane);
     cp_async_commit_group();
-    copy_block_async(vbuf, vc + ((size_t)blk * a.kvheads + kvh) * BLK * HD, kb * BLK, k_lo, k_hi, lane);
-    cp_async_commit_group();
-    cp_async_wait_group<1>();
+    if (lane == 0) prefetch_l2(vsrc, BLK * HD * 2);
+    cp_async_wait_group<0>();
     __syncwarp();
     // scores of 16 rows x 64 keys
     float s[8][4];
@@ -181,6 +188,9 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_mma_kernel(AttnArgs a, fl
     for (int j = 0; j < HD / 8; ++j) {
       o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
     }
+    __syncwarp();  // every lane has taken its scores: the keys may be overwritten by the values
+    copy_block_async(vbuf, vsrc, kb * BLK, k_lo, k_hi, lane);
+    cp_async_commit_group();
     cp_async_wait_group<0>();
     __syncwarp();
 #pragma unroll
@@ -199,7 +209,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_mma_kernel(AttnArgs a, fl
   // merge the warps: each writes (m, l, o) of its 16 rows over its own key buffer
   __syncwarp();
   float* wo = reinterpret_cast<float*>(kbuf);          // [16][HD]
-  float* wml = reinterpret_cast<float*>(vbuf);         // [16][2]
+  float* wml = wo + 16 * HD;                           // [16][2]
 #pragma unroll
   for (int j = 0; j < HD / 8; ++j) {
     wo[g * HD + 8 * j + 2 * c] = o[j][0];
@@ -217,12 +227,12 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_mma_kernel(AttnArgs a, fl
     float mm = -INFINITY;
 #pragma unroll
     for (int w = 0; w < NW; ++w)
-      mm = fmaxf(mm, reinterpret_cast<const float*>(smem_raw + (size_t)w * 2 * BLK * ROWB + BLK * ROWB)[2 * r]);
+      mm = fmaxf(mm, (reinterpret_cast<const float*>(smem_raw + (size_t)w * BLK * ROWB) + 16 * HD)[2 * r]);
     float sum = 0.f, lsum = 0.f;
 #pragma unroll
     for (int w = 0; w < NW; ++w) {
-      const float* wm = reinterpret_cast<const float*>(smem_raw + (size_t)w * 2 * BLK * ROWB + BLK * ROWB);
-      const float* wv = reinterpret_cast<const float*>(smem_raw + (size_t)w * 2 * BLK * ROWB);
+      const float* wv = reinterpret_cast<const float*>(smem_raw + (size_t)w * BLK * ROWB);
+      const float* wm = wv + 16 * HD;
       const float f = wm[2 * r] == -INFINITY ? 0.f : exp2f(wm[2 * r] - mm);
       sum += wv[r * HD + d] * f;
       lsum += wm[2 * r + 1] * f;
