@@ -71,6 +71,7 @@ def generate_batch(engine, sampler: Sampler, prompts: Sequence[Sequence[int]], r
     horizon = max(len(p) for p in prompts) + max_new_tokens
     try:
         live = list(range(n))
+        req_of, req = None, None
         feed = [list(p) for p in prompts]
         for it in range(max_new_tokens):
             start = time.perf_counter()
@@ -78,7 +79,9 @@ def generate_batch(engine, sampler: Sampler, prompts: Sequence[Sequence[int]], r
                 logits = engine.decode([slots[i] for i in live], [f[0] for f in feed], horizon=horizon)
             else:
                 logits = engine.step([slots[i] for i in live], feed)
-            req = torch.tensor([requests[i] for i in live], dtype=torch.int32).to(engine.device)
+            if req_of != live:  # the request numbers of the live sequences, on the device (sampling draws by them)
+                req = torch.tensor([requests[i] for i in live], dtype=torch.int32).to(engine.device)
+                req_of = list(live)
             tokens = sampler(logits, req, it).tolist()  # device -> host: the loop's one synchronisation
             if times is not None:
                 times.append(time.perf_counter() - start)

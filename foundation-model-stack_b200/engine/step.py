@@ -43,6 +43,7 @@ class _DecodeBuffers:
         b.want_rows = ar[:n].clone()
         self.tokens_host = torch.zeros(n, dtype=torch.int32).pin_memory() if torch.device(device).type == "cuda" \
             else torch.zeros(n, dtype=torch.int32)
+        self.tokens_np = self.tokens_host.numpy()  # the same memory, for cheap writes from lists
         self.copied = None  # event after the last copy out of tokens_host
         self.loaded: Optional[Tuple[int, ...]] = None  # slots whose state the arrays hold
         self.lengths: List[int] = []  # their lengths, as the device arrays have them
@@ -157,11 +158,12 @@ class Engine:
         if tokens_device is not None:
             buf.batch.tokens.copy_(tokens_device)
         else:
-            buf.tokens_host.copy_(torch.tensor(list(tokens), dtype=torch.int32))
+            buf.tokens_np[:] = tokens
             buf.batch.tokens.copy_(buf.tokens_host, non_blocking=True)
             self.h2d_bytes += 4 * n
             if self.device.type == "cuda":
-                buf.copied = torch.cuda.Event()
+                if buf.copied is None:
+                    buf.copied = torch.cuda.Event()
                 buf.copied.record()
         logits = self._run_decode(buf, max(max(lengths) + 1, min(int(horizon), self.cache.max_positions)))
         self.cache.commit(slots, [1] * n)

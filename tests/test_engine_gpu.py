@@ -252,3 +252,90 @@ def test_trace_run_program(tiny_folders, oracles, tmp_path, dtype):
         assert o == data.shape[0]
     for i, r in enumerate(reqs):
         close(torch.cat(got[i]), oracles["b"].logits(r), "fp32" if dtype == "float32" else "bf16")
+
+
+def test_head_size_128_model_bfloat16_against_float32(tmp_path):
+    """A model with the head size, group size and widths (in small) of the benchmark's: prompts long enough for
+    the tcgen05 product (256 rows and more), decode through the weight-streaming product and the CUDA graph.
+    The float32 path — itself checked against the plain implementation on the tiny models — is the yardstick."""
+    from fms_b200.models import get_model
+    from fms_b200.models.llama import LLaMA, LLaMAConfig
+    from fms_b200.weights import write_random_model
+
+    arch = LLaMA(LLaMAConfig(src_vocab_size=4099, emb_dim=1024, nheads=8, kvheads=2, nlayers=2, hidden_dim=2816,
+                             max_expected_seq_len=2048, rope_theta=500000.0))
+    folder = write_random_model(str(tmp_path / "m"), arch.config_json(), arch.checkpoint_layout(), seed=5)
+    g = torch.Generator().manual_seed(70)
+    reqs = [torch.randint(0, 4099, (k,), generator=g).tolist() for k in (700, 300, 41)]
+    out = {}
+    for dtype in ("fp32", "bf16"):
+        engine = get_model("hf_pretrained", model_path=folder, device_type="cuda", data_type=dtype).new_engine(2048)
+        slots = engine.begin(3)
+        cut = [len(r) - 5 for r in reqs]
+        rows = [engine.step(slots, [r[:c] for r, c in zip(reqs, cut)], [[0, c // 2, c - 1] for c in cut]).float().cpu()]
+        for t in range(5):
+            rows.append(engine.step(slots, [[r[c + t]] for r, c in zip(reqs, cut)]).float().cpu())
+        engine.release(slots)
+        engine.check()
+        out[dtype] = torch.cat(rows)
+    close(out["bf16"], out["fp32"], "bf16")
+    assert (out["bf16"].argmax(-1) == out["fp32"].argmax(-1)).float().mean() > 0.9
+
+
+def test_window_attention_through_the_engine(tmp_path):
+    """A decoder whose mixers keep a window of 40 keys: the cache gives blocks back as they leave the window, and
+    the logits equal the plain implementation's with the same window, whole and token by token."""
+    import dataclasses
+
+    from fms_b200.models import get_model
+    from fms_b200.models.llama import LLaMA
+    from tiny_models import TINY, write_tiny
+
+    class WindowedLLaMA(LLaMA):  # Llama's layers with a window on every mixer: a test's variation, not a model
+        def decoder_spec(self):
+            spec = super().decoder_spec()
+            layers = tuple(dataclasses.replace(b, mixer=dataclasses.replace(b.mixer, window=40)) for b in spec.layers)
+            return dataclasses.replace(spec, layers=layers)
+
+    folder = write_tiny(str(tmp_path / "c"), "c")
+    plain = pl.PlainLlama(folder)
+    g = torch.Generator().manual_seed(80)
+    req = torch.randint(0, TINY["c"][0]["vocab_size"], (300,), generator=g).tolist()
+
+    def plain_logits(ids):
+        ids_t = torch.as_tensor(ids)
+        x = pl.plain_embedding(ids_t, plain.w["model.embed_tokens.weight"])
+        for i in range(plain.c["nlayers"]):
+            x = plain.block(i, x, torch.arange(len(ids)), window=40)
+        x = pl.plain_rmsnorm(x, plain.w["model.norm.weight"], plain.c["eps"])
+        return x @ plain.w["lm_head.weight"].T
+
+    want = plain_logits(req)
+    for dtype in ("fp32", "bf16"):
+        base = get_model("hf_pretrained", model_path=folder, device_type="cuda", data_type=dtype)
+        model = WindowedLLaMA(base.config)
+        from fms_b200.weights import FileSource
+
+        model.load(FileSource(folder), "hf", "cuda", base.dtype)
+        engine = model.new_engine(max_tokens=64 * 4, max_slots=1)  # 4 blocks: the sequence of 300 needs 5 without a window
+        (slot,) = engine.begin(1)
+        parts = [engine.step([slot], [req[:130]], [list(range(130))])]
+        parts.append(engine.step([slot], [req[130:200]], [list(range(70))]))
+        for t in range(200, 300):
+            parts.append(engine.step([slot], [[req[t]]]))
+        assert len(engine.cache.groups[0].held_blocks(slot)) <= 2
+        engine.release([slot])
+        engine.check()
+        close(torch.cat(parts), want, dtype)
+
+
+def test_command_line(tiny_folders):
+    proc = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "fms_inference"), "--model_path", tiny_folders["a"], "--model_source", "hf",
+         "--default_dtype", "fp32", "--prompt_ids", "5,17,3", "--prompt_ids", "9,8,7,6,5,4", "--batch_input",
+         "--max_new_tokens", "6", "--deterministic"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [l for l in proc.stdout.splitlines() if l.strip()]
+    oracle = pl.PlainLlama(tiny_folders["a"])
+    assert [[int(x) for x in l.split(",")] for l in lines] == [pl.plain_generate(oracle, p, 6)
+                                                              for p in ([5, 17, 3], [9, 8, 7, 6, 5, 4])]

@@ -188,7 +188,7 @@ def make_cache_case(dtype, nheads, kvheads, hd, lens_before, num_new, seed, wind
     g = torch.Generator().manual_seed(seed)
     n = len(lens_before)
     cache = Cache([KVRequest(kvheads, hd, window)], max_tokens=64 * (sum((a + b + 63) // 64 for a, b in zip(lens_before, num_new)) + 5),
-                  max_positions=4096, dtype=dtype, device="cuda")
+                  max_positions=8192, dtype=dtype, device="cuda")
     # scramble the free list so that block ids are not in order
     pool = cache.groups[0].pool
     perm = torch.randperm(len(pool._free), generator=g).tolist()
@@ -345,3 +345,18 @@ def test_sample_distribution_and_top_k(ops):
     got = ops.sample(logits, 1.0, 3, 5, requests, 1).long().cpu()
     assert set(got.tolist()) <= set(torch.topk(row, 3).indices.tolist())
     assert len(set(got.tolist())) == 3
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_long_context(ops, dtype):
+    """Thousands of cached positions: many blocks, many decode splits, a prefill tile deep inside a sequence."""
+    nheads, kvheads, hd = 8, 2, 64
+    for lens_before, num_new in (([5000, 37], [1, 1]), ([4090], [20])):
+        cache, view, batch = make_cache_case(dtype, nheads, kvheads, hd, lens_before, num_new, 90, poison=True)
+        g = torch.Generator().manual_seed(91)
+        qkv = torch.randn(sum(num_new), (nheads + 2 * kvheads) * hd, generator=g).to(dtype).cuda()
+        q = ops.rope_store(qkv, None, batch, view, nheads, kvheads, hd)
+        got = ops.attention(q, batch, view, nheads, kvheads, hd, 1.0 / math.sqrt(hd), 0)
+        want = P.attention(q, batch, view, nheads, kvheads, hd, 1.0 / math.sqrt(hd), 0)
+        assert not torch.isnan(got).any()
+        torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
