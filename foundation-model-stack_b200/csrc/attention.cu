@@ -426,7 +426,8 @@ FMS_API int fms_attention_prefill(const void* q, void* out, int dtype, const voi
     }
     const int group = nheads / kvheads;
     const int gh = prefill_heads_per_block(group);
-    attn_prefill_mma_kernel<<<dim3(n_tiles, kvheads * ((group + gh - 1) / gh)), PF_WARPS * 32, smem, stream>>>(a, tiles);
+    fms_launch(attn_prefill_mma_kernel, dim3(n_tiles, kvheads * ((group + gh - 1) / gh)), dim3(PF_WARPS * 32), smem,
+               stream, a, tiles);
     return fms_launch_status("attention_prefill");
   }
   if (dtype != FMS_F32) return fms_fail("attention_prefill: unsupported dtype code %d", dtype);

@@ -261,6 +261,8 @@ __host__ __device__ inline int prefill_positions_per_block(int group) { return P
 
 __global__ void __launch_bounds__(PF_WARPS * 32, HD <= 128 ? 3 : 1) attn_prefill_mma_kernel(AttnArgs a, const int* __restrict__ tiles) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
   const int group = a.nheads / a.kvheads;
   const int gh = prefill_heads_per_block(group), pp = PF_ROWS / gh;

@@ -207,6 +207,8 @@ __global__ void gated_activation_kernel(const T* __restrict__ gu, T* __restrict_
 // bfloat16 rows whose width is a multiple of 8: 8 values (16 bytes) of gate and of up per thread
 __global__ void gated_activation_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
                                             int hidden, int act, int n_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int per_row = hidden >> 3;
   const long total = (long)n_rows * per_row;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
@@ -234,8 +236,8 @@ FMS_API int fms_gated_activation(const void* gu, void* out, int dtype, int n_row
   if (dtype == FMS_BF16 && hidden % 8 == 0) {
     const long total = (long)n_rows * (hidden / 8);
     const int blocks = (int)((total + threads - 1) / threads < 148 * 32 ? (total + threads - 1) / threads : 148 * 32);
-    gated_activation_vec_kernel<<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, hidden,
-                                                              act, n_rows);
+    fms_launch(gated_activation_vec_kernel, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)gu,
+               (__nv_bfloat16*)out, hidden, act, n_rows);
     return fms_launch_status("gated_activation");
   }
   const size_t total = (size_t)n_rows * hidden;
@@ -307,6 +309,8 @@ __global__ void rope_store_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __n
                                       __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
                                       const int* __restrict__ table, int table_stride, int block_tokens, int nheads,
                                       int kvheads, int head_dim, int write_cache, int* __restrict__ error_flag) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int pieces = head_dim >> 3;
@@ -353,9 +357,10 @@ FMS_API int fms_rope_store(const void* qkv, int dtype, void* q_out, const float*
   if (dtype == FMS_BF16 && head_dim % 8 == 0 && n_tokens >= 64) {
     const int total = (nheads + 2 * kvheads) * (head_dim / 8);
     const int threads = total >= 256 ? 256 : ((total + 31) / 32) * 32;
-    rope_store_vec_kernel<<<n_tokens, threads, 0, stream>>>(
-        (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, inv_freq, positions, token_seq, slots, (__nv_bfloat16*)k_cache,
-        (__nv_bfloat16*)v_cache, table, table_stride, block_tokens, nheads, kvheads, head_dim, write_cache, error_flag);
+    fms_launch(rope_store_vec_kernel, dim3(n_tokens), dim3(threads), 0, stream, (const __nv_bfloat16*)qkv,
+               (__nv_bfloat16*)q_out, inv_freq, positions, token_seq, slots, (__nv_bfloat16*)k_cache,
+               (__nv_bfloat16*)v_cache, table, table_stride, block_tokens, nheads, kvheads, head_dim, write_cache,
+               error_flag);
     return fms_launch_status("rope_store");
   }
   dim3 grid(n_tokens, nheads + 2 * kvheads);

@@ -143,6 +143,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
   __shared__ int failed_flag;
   volatile int* failed = &failed_flag;
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_n = ep.glu ? TILE_N / 2 : TILE_N;  // output columns of a tile
   const int tiles_m = (M + TILE_M - 1) / TILE_M, tiles_n = (N + tile_n - 1) / tile_n;
@@ -166,6 +167,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  // everything above (barriers, tensor memory) overlaps the end of the kernel before; x may be read only now
+  pdl_wait();
 
   if (warp == 0) {
     if (elect_one()) {
@@ -359,7 +362,7 @@ int launch(const void* x, const void* w, int w_rows, const Epilogue& ep, int M, 
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
   }
   const int blocks = (int)(tiles < sms ? tiles : sms);  // one persistent block per multiprocessor
-  gemm_tc_kernel<<<blocks, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, ep, M, N, K, error_flag);
+  fms_launch(gemm_tc_kernel, dim3(blocks), dim3(THREADS), SMEM_BYTES, stream, map_a, map_b, ep, M, N, K, error_flag);
   return fms_launch_status("gemm_tc");
 }
 }  // namespace
