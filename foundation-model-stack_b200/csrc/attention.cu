@@ -11,6 +11,8 @@
 // Cache layout: keys, values [blocks, kv_heads, 64, HEAD_DIM]; table[slot, p / 64] is the block of
 // position p.  Rows of a block beyond the sequence's length hold garbage and are never used: masked
 // scores are set to -inf by selection and their values are skipped or zeroed, not multiplied by 0.
+#include <cuda.h>
+
 #include "common.cuh"
 
 #ifndef HEAD_DIM
@@ -352,6 +354,23 @@ __global__ void attn_combine_kernel(AttnArgs a, const float* __restrict__ part_o
 
 #include "attention_mma.cuh"
 
+#if HEAD_DIM == 64 || HEAD_DIM == 128
+#define FMS_ATTENTION_TC 1
+#include "attention_tc.cuh"
+#else
+#define FMS_ATTENTION_TC 0
+#endif
+
+// whether bfloat16 prefill takes the tcgen05 kernel (head sizes 64 and 128; FMS_B200_ATTN_TC=0 turns it off)
+static bool prefill_on_tcgen05() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("FMS_B200_ATTN_TC");
+    on = (FMS_ATTENTION_TC && !(e && e[0] == '0')) ? 1 : 0;
+  }
+  return on == 1;
+}
+
 int check_args(const char* what, int nheads, int kvheads, int head_dim, int block_tokens) {
   if (head_dim != HD) return fms_fail("%s: this library is built for head size %d, not %d", what, HD, head_dim);
   if (block_tokens != BLK) return fms_fail("%s: cache blocks of %d tokens, %d expected", what, block_tokens, BLK);
@@ -403,19 +422,43 @@ FMS_API int fms_attn_head_dim() { return HD; }
 FMS_API int fms_attn_split_tokens() { return SPLIT; }
 // Positions of one sequence that a prefill block takes (the host cuts the new tokens into such tiles).
 FMS_API int fms_attn_prefill_tile_positions(int dtype, int nheads, int kvheads) {
-  if (dtype == FMS_BF16 && kvheads > 0 && nheads % kvheads == 0) return prefill_positions_per_block(nheads / kvheads);
+  if (dtype == FMS_BF16 && kvheads > 0 && nheads % kvheads == 0) {
+#if FMS_ATTENTION_TC
+    if (prefill_on_tcgen05()) return tc_positions_per_block(nheads / kvheads);
+#endif
+    return prefill_positions_per_block(nheads / kvheads);
+  }
   return TQ;
 }
 
 FMS_API int fms_attention_prefill(const void* q, void* out, int dtype, const void* keys, const void* values,
                                   const int* table, int table_stride, int block_tokens, const int* slots,
                                   const int* first_row, const int* len_after, const int* tiles, int n_tiles,
-                                  int nheads, int kvheads, int head_dim, float scale, int window,
-                                  cudaStream_t stream) {
+                                  int nheads, int kvheads, int head_dim, float scale, int window, int pool_blocks,
+                                  int* error_flag, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (check_args("attention_prefill", nheads, kvheads, head_dim, block_tokens)) return 1;
   AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window};
   if (nheads > 65535) return fms_fail("attention_prefill: %d heads", nheads);
+#if FMS_ATTENTION_TC
+  if (dtype == FMS_BF16 && prefill_on_tcgen05()) {
+    // the cache as a matrix [blocks * kv heads * 64 positions, head size], loaded in boxes of 64 x 64
+    CUtensorMap map_k, map_v;
+    const long rows = (long)pool_blocks * kvheads * BLK;
+    if (make_map(&map_k, keys, rows, HD, BLK) || make_map(&map_v, values, rows, HD, BLK)) return 1;
+    static bool configured_tc = false;
+    if (!configured_tc) {
+      cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
+      if (e != cudaSuccess) return fms_fail("attention_prefill: shared memory of %zu bytes refused: %s", TC_SMEM, cudaGetErrorString(e));
+      configured_tc = true;
+    }
+    const int group = nheads / kvheads;
+    const int gh = tc_heads_per_block(group);
+    fms_launch(attn_prefill_tc_kernel, dim3(n_tiles, kvheads * ((group + gh - 1) / gh)), dim3(192), TC_SMEM, stream, map_k,
+               map_v, a, tiles, error_flag);
+    return fms_launch_status("attention_prefill");
+  }
+#endif
   if (dtype == FMS_BF16) {
     constexpr size_t smem = (size_t)2 * 2 * BLK * ROWB;
     static bool configured = false;

@@ -1,0 +1,255 @@
+// bfloat16 prefill attention on the tcgen05 tensor cores, for head sizes 64 and 128; included by attention.cu
+// inside its namespace after attention_mma.cuh.  One block of 6 warps owns 128 query rows of one kv head — P
+// positions x GH query heads (row = position * GH + head), so that a key/value block serves all of them — and
+// walks over the sequence's key blocks of 64 positions:
+//
+//   warp 0    one lane loads the keys and values of a block by TMA (boxes of 64 positions x 64 values of a head,
+//             128-byte swizzle) into one of two stages
+//   warp 1    one lane issues S = Q K^T (128 x 64, accumulator in tensor memory), waits for the probabilities
+//             and issues O += P V (128 x head size, accumulator in tensor memory; V is read as it lies in the
+//             cache, as an MN-major operand)
+//   warps 2-5 a thread per query row: read its row of S from tensor memory, mask by position, running maximum
+//             and sum in float32 (base 2), write the probabilities as bfloat16 into shared memory in the layout
+//             the tensor cores read, rescale its row of O when the maximum has grown; at the end divide by
+//             the sum and store
+//
+// Rows of a cache block beyond the sequence's length may hold anything; before the tensor cores read the values of
+// the last block, those rows are overwritten with zeros in shared memory (a masked probability is an exact zero,
+// but zero times NaN is not).  Every wait is bounded; a time-out is reported as error 4.
+#pragma once
+
+#include "tcgen05.cuh"
+
+constexpr int TC_ROWS = 128;                 // query rows of a block
+constexpr int TC_STAGES = 2;
+constexpr int TC_KV_TILE = BLK * HD * 2;     // bytes of a block's keys (or values) of one kv head
+constexpr int TC_Q_BYTES = TC_ROWS * HD * 2;
+constexpr int TC_P_BYTES = TC_ROWS * BLK * 2;
+constexpr size_t TC_SMEM = 1024 + TC_Q_BYTES + TC_P_BYTES + (size_t)TC_STAGES * 2 * TC_KV_TILE + 256;
+constexpr int TC_TMEM_COLS = HD + BLK <= 128 ? 128 : 256;  // O: HD columns, S: 64 columns
+
+__host__ __device__ inline int tc_heads_per_block(int group) { return group < TC_ROWS ? group : TC_ROWS; }
+__host__ __device__ inline int tc_positions_per_block(int group) { return TC_ROWS / tc_heads_per_block(group); }
+
+__global__ void __launch_bounds__(192, 1) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                 const __grid_constant__ CUtensorMap map_v, AttnArgs a,
+                                                                 const int* __restrict__ tiles, int* __restrict__ error_flag) {
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
+  unsigned char* q_tile = smem;                            // HD / 64 tiles of [128 rows][128 bytes], swizzled
+  unsigned char* p_tile = q_tile + TC_Q_BYTES;             // [128 rows][128 bytes], swizzled
+  unsigned char* kv = p_tile + TC_P_BYTES;                 // per stage: keys (HD / 64 tiles of [64][128 B]), then values
+  uint64_t* kv_full = reinterpret_cast<uint64_t*>(kv + (size_t)TC_STAGES * 2 * TC_KV_TILE);
+  uint64_t* kv_empty = kv_full + TC_STAGES;
+  uint64_t* s_full = kv_empty + TC_STAGES;
+  uint64_t* p_ready = s_full + 1;
+  uint64_t* o_done = p_ready + 1;
+  uint64_t* q_ready = o_done + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_ready + 1);
+  __shared__ int failed_flag;
+  volatile int* failed = &failed_flag;
+  pdl_launch_dependents();
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = a.nheads / a.kvheads;
+  const int gh = tc_heads_per_block(group), pp = TC_ROWS / gh;
+  const int chunks = (group + gh - 1) / gh;
+  const int kvh = blockIdx.y / chunks, g0 = (blockIdx.y - kvh * chunks) * gh;
+  const int ng = min(gh, group - g0);
+  const int seq = tiles[2 * blockIdx.x], r0 = tiles[2 * blockIdx.x + 1];
+  const int row_begin = a.first_row[seq];
+  const int n_new = a.first_row[seq + 1] - row_begin;
+  const int len = a.len_after[seq];
+  const int len_before = len - n_new;
+  const int slot = a.slots[seq];
+  const int pos_here = min(pp, n_new - r0);
+  const int p_first = len_before + r0, p_last = p_first + pos_here - 1;
+  const int kb_lo = a.window > 0 ? max(0, p_first - a.window + 1) / BLK : 0;
+  const int kb_hi = p_last / BLK;
+  const int nblocks = kb_hi - kb_lo + 1;
+
+  if (threadIdx.x == 0) {
+    failed_flag = 0;
+    for (int s = 0; s < TC_STAGES; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_ready, 128);
+    mbar_init(o_done, 1);
+    mbar_init(q_ready, 128);
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TC_TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_o = tmem, tmem_s = tmem + HD;
+  pdl_wait();
+
+  if (warp == 0) {
+    if (elect_one()) {
+      for (int i = 0; i < nblocks && !*failed; ++i) {
+        const int s = i % TC_STAGES;
+        if (!wait_or_abort(&kv_empty[s], ((i / TC_STAGES) & 1) ^ 1, failed)) break;
+        const int blk = a.table[(size_t)slot * a.table_stride + kb_lo + i];
+        unsigned char* kdst = kv + (size_t)s * 2 * TC_KV_TILE;
+        unsigned char* vdst = kdst + TC_KV_TILE;
+        const int row = (max(blk, 0) * a.kvheads + kvh) * BLK;  // first row of the block in the [positions, HD] view
+        mbar_arrive_expect_tx(&kv_full[s], 2 * TC_KV_TILE);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c) {
+          tma_load_2d(kdst + c * (BLK * 128), &map_k, c * 64, row, &kv_full[s]);
+          tma_load_2d(vdst + c * (BLK * 128), &map_v, c * 64, row, &kv_full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t IDESC_S = umma_idesc(TC_ROWS, BLK);
+      constexpr uint32_t IDESC_O = umma_idesc(TC_ROWS, HD, true);
+      bool q_there = wait_or_abort(q_ready, 0, failed);  // the query tile is in shared memory
+      for (int i = 0; i < nblocks && q_there && !*failed; ++i) {
+        const int s = i % TC_STAGES;
+        if (!wait_or_abort(&kv_full[s], (i / TC_STAGES) & 1, failed)) break;
+        tc_fence_after();
+        const uint32_t kaddr = smem_u32(kv + (size_t)s * 2 * TC_KV_TILE), vaddr = kaddr + TC_KV_TILE;
+        const uint32_t qaddr = smem_u32(q_tile), paddr = smem_u32(p_tile);
+        // S = Q K^T: both operands K-major; k-step kk lies in tile kk / 4 at byte 32 (kk % 4) of its rows
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          umma(tmem_s, umma_desc(qaddr + (kk / 4) * (TC_ROWS * 128) + (kk % 4) * 32),
+               umma_desc(kaddr + (kk / 4) * (BLK * 128) + (kk % 4) * 32), IDESC_S, kk > 0);
+        tc_commit(s_full);
+        if (!wait_or_abort(p_ready, i & 1, failed)) break;  // probabilities written, O rescaled, S read
+        tc_fence_after();
+        // O += P V: P K-major (64 keys = one 128-byte row); V MN-major: 16 keys of a step are 16 rows of 128 bytes,
+        // the head's second 64 values lie one tile (BLK * 128 bytes) further
+#pragma unroll
+        for (int kk = 0; kk < BLK / 16; ++kk)
+          umma(tmem_o, umma_desc(paddr + kk * 32), umma_desc_offsets(vaddr + kk * 16 * 128, BLK * 128, 1024), IDESC_O,
+               i > 0 || kk > 0);
+        tc_commit(&kv_empty[s]);
+        tc_commit(o_done);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;       // this thread's query row
+    const int pi = r / gh, gi = r - pi * gh;
+    const bool row_ok = pi < pos_here && gi < ng;
+    const int my_pos = p_first + pi;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    // the query tile: row r, 16-byte piece c of 64-value chunk t at t * 16 KB + r * 128 + ((c ^ (r & 7)) << 4)
+    {
+      const __nv_bfloat16* q = (const __nv_bfloat16*)a.q +
+                               ((size_t)(row_begin + r0 + (row_ok ? pi : 0)) * a.nheads + kvh * group + g0 + (row_ok ? gi : 0)) * HD;
+#pragma unroll
+      for (int c = 0; c < HD / 8; ++c) {
+        const uint4 v = row_ok ? *reinterpret_cast<const uint4*>(q + 8 * c) : make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(q_tile + (c / 8) * (TC_ROWS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+      }
+      fence_proxy_async();
+      mbar_arrive(q_ready);
+    }
+    const float scale2 = a.scale * LOG2E;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int i = 0; i < nblocks && ok; ++i) {
+      const int kb = kb_lo + i, s = i % TC_STAGES;
+      ok = __all_sync(0xffffffffu, wait_or_abort(s_full, i & 1, failed));  // the same decision in every lane:
+      if (!ok) break;                                                        // the tensor-memory loads are warp-wide
+      tc_fence_after();
+      float sc[BLK];
+      tmem_load_32(tmem_s + lane_base, sc);
+      tmem_load_32(tmem_s + lane_base + 32, sc + 32);
+      const bool whole = kb * BLK + BLK - 1 <= p_first && (a.window <= 0 || kb * BLK > p_last - a.window);
+      float tile_max = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < BLK; ++j) {
+        const int kpos = kb * BLK + j;
+        const bool visible = row_ok && (whole || (kpos <= my_pos && (a.window <= 0 || kpos > my_pos - a.window)));
+        sc[j] = visible ? sc[j] * scale2 : -INFINITY;
+        tile_max = fmaxf(tile_max, sc[j]);
+      }
+      const float m_new = fmaxf(m, tile_max);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = m == -INFINITY ? 0.f : exp2f(m - m_use);
+      float psum = 0.f;
+      // probabilities as bfloat16 into the row of the P tile (8 pieces of 8 keys, swizzled)
+#pragma unroll
+      for (int c = 0; c < BLK / 8; ++c) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = sc[8 * c + 2 * e] == -INFINITY ? 0.f : exp2f(sc[8 * c + 2 * e] - m_use);
+          const float p1 = sc[8 * c + 2 * e + 1] == -INFINITY ? 0.f : exp2f(sc[8 * c + 2 * e + 1] - m_use);
+          psum += p0 + p1;
+          w[e] = pack_bf16(p0, p1);
+        }
+        *reinterpret_cast<uint4*>(p_tile + r * 128 + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      l = l * alpha + psum;
+      m = m_new;
+      // the values of a block that the sequence fills only partly: rows beyond its length become zeros
+      const int blk = a.table[(size_t)slot * a.table_stride + kb];
+      if (kb * BLK + BLK > len || blk < 0) {
+        ok = __all_sync(0xffffffffu, wait_or_abort(&kv_full[s], (i / TC_STAGES) & 1, failed));
+        if (!ok) break;
+        unsigned char* vdst = kv + (size_t)s * 2 * TC_KV_TILE + TC_KV_TILE;
+        const int first_bad = blk < 0 ? 0 : len - kb * BLK;  // a block that has left the window holds nothing
+        for (int idx = r; idx < (BLK - first_bad) * (HD / 8); idx += 128) {
+          const int row = first_bad + idx / (HD / 8), c = idx % (HD / 8);
+          *reinterpret_cast<uint4*>(vdst + (c / 8) * (BLK * 128) + row * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      // O of the blocks before: rescale this row when its maximum has grown
+      if (i > 0) {
+        ok = __all_sync(0xffffffffu, wait_or_abort(o_done, (i - 1) & 1, failed));
+        if (!ok) break;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {  // warp-wide loads and stores: all lanes or none
+#pragma unroll
+          for (int c0 = 0; c0 < HD; c0 += 32) {
+            float o[32];
+            tmem_load_32(tmem_o + lane_base + c0, o);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] *= alpha;
+            tmem_store_32(tmem_o + lane_base + c0, o);
+          }
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(p_ready);
+    }
+    if (ok && __all_sync(0xffffffffu, wait_or_abort(o_done, (nblocks - 1) & 1, failed))) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* o_row = (__nv_bfloat16*)a.out +
+                             ((size_t)(row_begin + r0 + (row_ok ? pi : 0)) * a.nheads + kvh * group + g0 + (row_ok ? gi : 0)) * HD;
+#pragma unroll
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        float o[32];
+        tmem_load_32(tmem_o + lane_base + c0, o);  // warp-wide: every lane loads, only valid rows store
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) w[e] = pack_bf16(o[j + 2 * e] * inv, o[j + 2 * e + 1] * inv);
+            *reinterpret_cast<uint4*>(o_row + c0 + j) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && *failed && error_flag) atomicExch(error_flag, 4);
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TC_TMEM_COLS);
+  }
+}

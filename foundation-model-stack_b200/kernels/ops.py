@@ -34,7 +34,7 @@ _SIGNATURES = {
     "fms_glu_bf16_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "fms_argmax": [_P, _P, _I, _I, _P],
     "fms_sample": [_P, _P, _I, _I, _F, _I, _U64, _P, _I, _P],
-    "fms_attention_prefill": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+    "fms_attention_prefill": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "fms_attention_decode": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _F, _I, _P],
 }
 _functions = {}
@@ -283,7 +283,7 @@ def attention(q: torch.Tensor, batch, view, nheads: int, kvheads: int, head_dim:
     else:
         tiles = batch.query_tiles(tile_rows)
         _call(lib, "fms_attention_prefill", *common, _ptr(tiles), tiles.shape[0], nheads, kvheads, head_dim,
-              float(scale), int(window), _stream())
+              float(scale), int(window), view.keys.shape[0], _ptr(error_flag(q.device)), _stream())
     return out
 
 

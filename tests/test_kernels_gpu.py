@@ -253,6 +253,10 @@ ATTN_CASES = [
     (4, 2, 32, [90, 0], [50, 150], 33),             # prefill with a window
     (2, 2, 128, [513], [1], 0),                     # decode over three splits
     (2, 1, 256, [20], [30], 0),                     # the largest head size
+    (8, 2, 128, [0, 100], [200, 77], 0),            # prefill, head size 128, four query heads a kv head
+    (4, 4, 64, [64, 0], [130, 1], 0),               # prefill, head size 64, one query head a kv head
+    (6, 2, 64, [10], [300], 50),                    # prefill, head size 64, window
+    (3, 1, 128, [129], [64], 0),                    # three query heads a kv head: 42 positions a block, two rows idle
 ]
 
 
