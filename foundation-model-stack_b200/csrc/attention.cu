@@ -440,6 +440,7 @@ FMS_API int fms_attention_prefill(const void* q, void* out, int dtype, const voi
   if (check_args("attention_prefill", nheads, kvheads, head_dim, block_tokens)) return 1;
   AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window};
   if (nheads > 65535) return fms_fail("attention_prefill: %d heads", nheads);
+  if (!(scale > 0.f)) return fms_fail("attention_prefill: the scale of the scores is %g; it must be positive", (double)scale);
 #if FMS_ATTENTION_TC
   if (dtype == FMS_BF16 && prefill_on_tcgen05()) {
     // the cache as a matrix [blocks * kv heads * 64 positions, head size], loaded in boxes of 64 x 64

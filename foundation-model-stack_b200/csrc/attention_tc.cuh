@@ -5,13 +5,15 @@
 //
 //   warp 0    one lane loads the keys and values of a block by TMA (boxes of 64 positions x 64 values of a head,
 //             128-byte swizzle) into one of two stages
-//   warp 1    one lane issues S = Q K^T (128 x 64, accumulator in tensor memory), waits for the probabilities
+//   warp 1    one lane issues S = Q K^T (128 x 64, accumulator in tensor memory, two buffers: the scores of the
+//             next block are computed while the rows of this one are exponentiated), waits for the probabilities
 //             and issues O += P V (128 x head size, accumulator in tensor memory; V is read as it lies in the
 //             cache, as an MN-major operand)
 //   warps 2-5 a thread per query row: read its row of S from tensor memory, mask by position, running maximum
 //             and sum in float32 (base 2), write the probabilities as bfloat16 into shared memory in the layout
-//             the tensor cores read, rescale its row of O when the maximum has grown; at the end divide by
-//             the sum and store
+//             the tensor cores read (two buffers), rescale its row of O only when the maximum has grown by more
+//             than 2^8 over the reference the exponents are taken against (the quotient O / l does not depend on
+//             that reference); at the end divide by the sum and store
 //
 // Rows of a cache block beyond the sequence's length may hold anything; before the tensor cores read the values of
 // the last block, those rows are overwritten with zeros in shared memory (a masked probability is an exact zero,
@@ -25,8 +27,15 @@ constexpr int TC_STAGES = 2;
 constexpr int TC_KV_TILE = BLK * HD * 2;     // bytes of a block's keys (or values) of one kv head
 constexpr int TC_Q_BYTES = TC_ROWS * HD * 2;
 constexpr int TC_P_BYTES = TC_ROWS * BLK * 2;
-constexpr size_t TC_SMEM = 1024 + TC_Q_BYTES + TC_P_BYTES + (size_t)TC_STAGES * 2 * TC_KV_TILE + 256;
-constexpr int TC_TMEM_COLS = HD + BLK <= 128 ? 128 : 256;  // O: HD columns, S: 64 columns
+constexpr size_t TC_SMEM = 1024 + TC_Q_BYTES + 2 * TC_P_BYTES + (size_t)TC_STAGES * 2 * TC_KV_TILE + 256;
+constexpr int TC_TMEM_COLS = HD + 2 * BLK <= 128 ? 128 : 256;  // O: HD columns, S: two buffers of 64 columns
+
+// 2^x in one special-function instruction (relative error about 2^-22; 0 for -inf)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __host__ __device__ inline int tc_heads_per_block(int group) { return group < TC_ROWS ? group : TC_ROWS; }
 __host__ __device__ inline int tc_positions_per_block(int group) { return TC_ROWS / tc_heads_per_block(group); }
@@ -37,14 +46,14 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc_kernel(const __grid_co
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
   unsigned char* q_tile = smem;                            // HD / 64 tiles of [128 rows][128 bytes], swizzled
-  unsigned char* p_tile = q_tile + TC_Q_BYTES;             // [128 rows][128 bytes], swizzled
-  unsigned char* kv = p_tile + TC_P_BYTES;                 // per stage: keys (HD / 64 tiles of [64][128 B]), then values
+  unsigned char* p_tile = q_tile + TC_Q_BYTES;             // two buffers of [128 rows][128 bytes], swizzled
+  unsigned char* kv = p_tile + 2 * TC_P_BYTES;             // per stage: keys (HD / 64 tiles of [64][128 B]), then values
   uint64_t* kv_full = reinterpret_cast<uint64_t*>(kv + (size_t)TC_STAGES * 2 * TC_KV_TILE);
   uint64_t* kv_empty = kv_full + TC_STAGES;
-  uint64_t* s_full = kv_empty + TC_STAGES;
-  uint64_t* p_ready = s_full + 1;
-  uint64_t* o_done = p_ready + 1;
-  uint64_t* q_ready = o_done + 1;
+  uint64_t* s_full = kv_empty + TC_STAGES;  // [2], as p_ready and o_done: block i uses entry i & 1, phase (i / 2) & 1
+  uint64_t* p_ready = s_full + 2;
+  uint64_t* o_done = p_ready + 2;
+  uint64_t* q_ready = o_done + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_ready + 1);
   __shared__ int failed_flag;
   volatile int* failed = &failed_flag;
@@ -56,7 +65,8 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc_kernel(const __grid_co
   const int chunks = (group + gh - 1) / gh;
   const int kvh = blockIdx.y / chunks, g0 = (blockIdx.y - kvh * chunks) * gh;
   const int ng = min(gh, group - g0);
-  const int seq = tiles[2 * blockIdx.x], r0 = tiles[2 * blockIdx.x + 1];
+  const int tile = gridDim.x - 1 - blockIdx.x;  // later positions have more keys: the long tiles start first
+  const int seq = tiles[2 * tile], r0 = tiles[2 * tile + 1];
   const int row_begin = a.first_row[seq];
   const int n_new = a.first_row[seq + 1] - row_begin;
   const int len = a.len_after[seq];
@@ -74,9 +84,11 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc_kernel(const __grid_co
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(p_ready, 128);
-    mbar_init(o_done, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&s_full[b], 1);
+      mbar_init(&p_ready[b], 128);
+      mbar_init(&o_done[b], 1);
+    }
     mbar_init(q_ready, 128);
     mbar_fence_init();
   }
@@ -85,7 +97,7 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc_kernel(const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tmem_o = tmem, tmem_s = tmem + HD;
+  const uint32_t tmem_o = tmem, tmem_s = tmem + HD;  // S buffer b at tmem_s + 64 b
   pdl_wait();
 
   if (warp == 0) {
@@ -109,21 +121,30 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc_kernel(const __grid_co
     if (elect_one()) {
       constexpr uint32_t IDESC_S = umma_idesc(TC_ROWS, BLK);
       constexpr uint32_t IDESC_O = umma_idesc(TC_ROWS, HD, true);
-      bool q_there = wait_or_abort(q_ready, 0, failed);  // the query tile is in shared memory
-      for (int i = 0; i < nblocks && q_there && !*failed; ++i) {
+      const uint32_t qaddr = smem_u32(q_tile);
+      // S(i) = Q K(i)^T into buffer i & 1: both operands K-major; k-step kk lies in tile kk / 4 at byte 32 (kk % 4)
+      auto issue_scores = [&](int i) -> bool {
         const int s = i % TC_STAGES;
-        if (!wait_or_abort(&kv_full[s], (i / TC_STAGES) & 1, failed)) break;
+        if (!wait_or_abort(&kv_full[s], (i / TC_STAGES) & 1, failed)) return false;
         tc_fence_after();
-        const uint32_t kaddr = smem_u32(kv + (size_t)s * 2 * TC_KV_TILE), vaddr = kaddr + TC_KV_TILE;
-        const uint32_t qaddr = smem_u32(q_tile), paddr = smem_u32(p_tile);
-        // S = Q K^T: both operands K-major; k-step kk lies in tile kk / 4 at byte 32 (kk % 4) of its rows
+        const uint32_t kaddr = smem_u32(kv + (size_t)s * 2 * TC_KV_TILE);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          umma(tmem_s, umma_desc(qaddr + (kk / 4) * (TC_ROWS * 128) + (kk % 4) * 32),
+          umma(tmem_s + (i & 1) * BLK, umma_desc(qaddr + (kk / 4) * (TC_ROWS * 128) + (kk % 4) * 32),
                umma_desc(kaddr + (kk / 4) * (BLK * 128) + (kk % 4) * 32), IDESC_S, kk > 0);
-        tc_commit(s_full);
-        if (!wait_or_abort(p_ready, i & 1, failed)) break;  // probabilities written, O rescaled, S read
+        tc_commit(&s_full[i & 1]);
+        return true;
+      };
+      bool go = wait_or_abort(q_ready, 0, failed) && issue_scores(0);  // the query tile is in shared memory
+      for (int i = 0; i < nblocks && go && !*failed; ++i) {
+        // the scores of the next block, while the rows of this one are exponentiated (its buffer was read two
+        // blocks ago: p_ready of that block has been seen)
+        if (i + 1 < nblocks && !issue_scores(i + 1)) break;
+        if (!wait_or_abort(&p_ready[i & 1], (i >> 1) & 1, failed)) break;  // probabilities written, O rescaled
         tc_fence_after();
+        const int s = i % TC_STAGES;
+        const uint32_t vaddr = smem_u32(kv + (size_t)s * 2 * TC_KV_TILE) + TC_KV_TILE;
+        const uint32_t paddr = smem_u32(p_tile + (i & 1) * TC_P_BYTES);
         // O += P V: P K-major (64 keys = one 128-byte row); V MN-major: 16 keys of a step are 16 rows of 128 bytes,
         // the head's second 64 values lie one tile (BLK * 128 bytes) further
 #pragma unroll
@@ -131,7 +152,7 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc_kernel(const __grid_co
           umma(tmem_o, umma_desc(paddr + kk * 32), umma_desc_offsets(vaddr + kk * 16 * 128, BLK * 128, 1024), IDESC_O,
                i > 0 || kk > 0);
         tc_commit(&kv_empty[s]);
-        tc_commit(o_done);
+        tc_commit(&o_done[i & 1]);
       }
     }
   } else {
@@ -154,44 +175,76 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc_kernel(const __grid_co
       mbar_arrive(q_ready);
     }
     const float scale2 = a.scale * LOG2E;
-    float m = -INFINITY, l = 0.f;
+    float m_ref = -INFINITY, l = 0.f;  // the exponents are taken against m_ref (base 2); l is the sum of them
     bool ok = true;
     for (int i = 0; i < nblocks && ok; ++i) {
       const int kb = kb_lo + i, s = i % TC_STAGES;
-      ok = __all_sync(0xffffffffu, wait_or_abort(s_full, i & 1, failed));  // the same decision in every lane:
-      if (!ok) break;                                                        // the tensor-memory loads are warp-wide
+      ok = __all_sync(0xffffffffu, wait_or_abort(&s_full[i & 1], (i >> 1) & 1, failed));  // the same decision in
+      if (!ok) break;                                                    // every lane: tensor-memory loads are warp-wide
       tc_fence_after();
       float sc[BLK];
-      tmem_load_32(tmem_s + lane_base, sc);
-      tmem_load_32(tmem_s + lane_base + 32, sc + 32);
+      tmem_load_32(tmem_s + (i & 1) * BLK + lane_base, sc);
+      tmem_load_32(tmem_s + (i & 1) * BLK + lane_base + 32, sc + 32);
+      // raw scores; the scale (positive) goes into the exponent's multiply-add.  A block that every row of the tile
+      // sees whole needs no mask; rows without a query hold zeros there and are never stored.
       const bool whole = kb * BLK + BLK - 1 <= p_first && (a.window <= 0 || kb * BLK > p_last - a.window);
-      float tile_max = -INFINITY;
+      if (!whole) {
 #pragma unroll
-      for (int j = 0; j < BLK; ++j) {
-        const int kpos = kb * BLK + j;
-        const bool visible = row_ok && (whole || (kpos <= my_pos && (a.window <= 0 || kpos > my_pos - a.window)));
-        sc[j] = visible ? sc[j] * scale2 : -INFINITY;
-        tile_max = fmaxf(tile_max, sc[j]);
+        for (int j = 0; j < BLK; ++j) {
+          const int kpos = kb * BLK + j;
+          const bool visible = row_ok && kpos <= my_pos && (a.window <= 0 || kpos > my_pos - a.window);
+          sc[j] = visible ? sc[j] : -INFINITY;
+        }
       }
-      const float m_new = fmaxf(m, tile_max);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = m == -INFINITY ? 0.f : exp2f(m - m_use);
-      float psum = 0.f;
-      // probabilities as bfloat16 into the row of the P tile (8 pieces of 8 keys, swizzled)
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < BLK / 8; ++c) {
+      for (int j = 0; j < BLK; j += 4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) mx[e] = fmaxf(mx[e], sc[j + e]);
+      }
+      const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale2;
+      // a new reference only when the maximum has outgrown the old one by more than 2^8
+      float alpha = 1.f;
+      if (tile_max > m_ref + 8.f) {
+        alpha = m_ref == -INFINITY ? 0.f : exp2f(m_ref - tile_max);
+        m_ref = tile_max;
+        l *= alpha;
+      }
+      if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {  // warp-wide loads and stores: all lanes or none
+        ok = __all_sync(0xffffffffu, wait_or_abort(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1, failed));
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+          float o[32];
+          tmem_load_32(tmem_o + lane_base + c0, o);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] *= alpha;
+          tmem_store_32(tmem_o + lane_base + c0, o);
+        }
+      }
+      // the P buffer of this block was read by the product of the block two before
+      if (i >= 2) {
+        ok = __all_sync(0xffffffffu, wait_or_abort(&o_done[i & 1], ((i - 2) >> 1) & 1, failed));
+        if (!ok) break;
+      }
+      const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+      float ps[4] = {0.f, 0.f, 0.f, 0.f};
+      unsigned char* p_row = p_tile + (i & 1) * TC_P_BYTES + r * 128;
+#pragma unroll
+      for (int c = 0; c < BLK / 8; ++c) {  // probabilities as bfloat16: 8 pieces of 8 keys, swizzled
         uint32_t w[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float p0 = sc[8 * c + 2 * e] == -INFINITY ? 0.f : exp2f(sc[8 * c + 2 * e] - m_use);
-          const float p1 = sc[8 * c + 2 * e + 1] == -INFINITY ? 0.f : exp2f(sc[8 * c + 2 * e + 1] - m_use);
-          psum += p0 + p1;
+          const float p0 = fast_exp2(fmaf(sc[8 * c + 2 * e], scale2, neg_m));  // 2^-inf = 0 for a masked key
+          const float p1 = fast_exp2(fmaf(sc[8 * c + 2 * e + 1], scale2, neg_m));
+          ps[e] += p0 + p1;
           w[e] = pack_bf16(p0, p1);
         }
-        *reinterpret_cast<uint4*>(p_tile + r * 128 + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      l = l * alpha + psum;
-      m = m_new;
+      const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
+      l += psum;
       // the values of a block that the sequence fills only partly: rows beyond its length become zeros
       const int blk = a.table[(size_t)slot * a.table_stride + kb];
       if (kb * BLK + BLK > len || blk < 0) {
@@ -204,27 +257,11 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc_kernel(const __grid_co
           *reinterpret_cast<uint4*>(vdst + (c / 8) * (BLK * 128) + row * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
       }
-      // O of the blocks before: rescale this row when its maximum has grown
-      if (i > 0) {
-        ok = __all_sync(0xffffffffu, wait_or_abort(o_done, (i - 1) & 1, failed));
-        if (!ok) break;
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {  // warp-wide loads and stores: all lanes or none
-#pragma unroll
-          for (int c0 = 0; c0 < HD; c0 += 32) {
-            float o[32];
-            tmem_load_32(tmem_o + lane_base + c0, o);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) o[j] *= alpha;
-            tmem_store_32(tmem_o + lane_base + c0, o);
-          }
-        }
-      }
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(p_ready);
+      mbar_arrive(&p_ready[i & 1]);
     }
-    if (ok && __all_sync(0xffffffffu, wait_or_abort(o_done, (nblocks - 1) & 1, failed))) {
+    if (ok && __all_sync(0xffffffffu, wait_or_abort(&o_done[(nblocks - 1) & 1], ((nblocks - 1) >> 1) & 1, failed))) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* o_row = (__nv_bfloat16*)a.out +
