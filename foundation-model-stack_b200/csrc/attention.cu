@@ -455,8 +455,10 @@ FMS_API int fms_attention_prefill(const void* q, void* out, int dtype, const voi
     }
     const int group = nheads / kvheads;
     const int gh = tc_heads_per_block(group);
-    fms_launch(attn_prefill_tc_kernel, dim3(n_tiles, kvheads * ((group + gh - 1) / gh)), dim3(192), TC_SMEM, stream, map_k,
-               map_v, a, tiles, error_flag);
+    const long blocks = (long)n_tiles * kvheads * ((group + gh - 1) / gh);
+    if (blocks > 0x7fffffffL) return fms_fail("attention_prefill: %ld thread blocks", blocks);
+    fms_launch(attn_prefill_tc_kernel, dim3((unsigned)blocks), dim3(192), TC_SMEM, stream, map_k, map_v, a, tiles, n_tiles,
+               error_flag);
     return fms_launch_status("attention_prefill");
   }
 #endif

@@ -7,11 +7,11 @@
 //             128-byte swizzle) into one of two stages
 //   warp 1    one lane issues S = Q K^T (128 x 64, accumulator in tensor memory, two buffers: the scores of the
 //             next block are computed while the rows of this one are exponentiated), waits for the probabilities
-//             and issues O += P V (128 x head size, accumulator in tensor memory; V is read as it lies in the
-//             cache, as an MN-major operand)
+//             and issues O += P V (128 x head size, accumulator in tensor memory; P is read from tensor memory,
+//             V as it lies in the cache, as an MN-major operand)
 //   warps 2-5 a thread per query row: read its row of S from tensor memory, mask by position, running maximum
-//             and sum in float32 (base 2), write the probabilities as bfloat16 into shared memory in the layout
-//             the tensor cores read (two buffers), rescale its row of O only when the maximum has grown by more
+//             and sum in float32 (base 2), write the probabilities as bfloat16 back into tensor memory, over the
+//             scores they came from, rescale its row of O only when the maximum has grown by more
 //             than 2^8 over the reference the exponents are taken against (the quotient O / l does not depend on
 //             that reference); at the end divide by the sum and store
 //
@@ -26,8 +26,7 @@ constexpr int TC_ROWS = 128;                 // query rows of a block
 constexpr int TC_STAGES = 2;
 constexpr int TC_KV_TILE = BLK * HD * 2;     // bytes of a block's keys (or values) of one kv head
 constexpr int TC_Q_BYTES = TC_ROWS * HD * 2;
-constexpr int TC_P_BYTES = TC_ROWS * BLK * 2;
-constexpr size_t TC_SMEM = 1024 + TC_Q_BYTES + 2 * TC_P_BYTES + (size_t)TC_STAGES * 2 * TC_KV_TILE + 256;
+constexpr size_t TC_SMEM = 1024 + TC_Q_BYTES + (size_t)TC_STAGES * 2 * TC_KV_TILE + 256;  // two blocks fit an SM
 constexpr int TC_TMEM_COLS = HD + 2 * BLK <= 128 ? 128 : 256;  // O: HD columns, S: two buffers of 64 columns
 
 // 2^x in one special-function instruction (relative error about 2^-22; 0 for -inf)
@@ -40,14 +39,14 @@ __device__ __forceinline__ float fast_exp2(float x) {
 __host__ __device__ inline int tc_heads_per_block(int group) { return group < TC_ROWS ? group : TC_ROWS; }
 __host__ __device__ inline int tc_positions_per_block(int group) { return TC_ROWS / tc_heads_per_block(group); }
 
-__global__ void __launch_bounds__(192, 1) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
+__global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                  const __grid_constant__ CUtensorMap map_v, AttnArgs a,
-                                                                 const int* __restrict__ tiles, int* __restrict__ error_flag) {
+                                                                 const int* __restrict__ tiles, int n_tiles,
+                                                                 int* __restrict__ error_flag) {
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
   unsigned char* q_tile = smem;                            // HD / 64 tiles of [128 rows][128 bytes], swizzled
-  unsigned char* p_tile = q_tile + TC_Q_BYTES;             // two buffers of [128 rows][128 bytes], swizzled
-  unsigned char* kv = p_tile + 2 * TC_P_BYTES;             // per stage: keys (HD / 64 tiles of [64][128 B]), then values
+  unsigned char* kv = q_tile + TC_Q_BYTES;                 // per stage: keys (HD / 64 tiles of [64][128 B]), then values
   uint64_t* kv_full = reinterpret_cast<uint64_t*>(kv + (size_t)TC_STAGES * 2 * TC_KV_TILE);
   uint64_t* kv_empty = kv_full + TC_STAGES;
   uint64_t* s_full = kv_empty + TC_STAGES;  // [2], as p_ready and o_done: block i uses entry i & 1, phase (i / 2) & 1
@@ -63,9 +62,12 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc_kernel(const __grid_co
   const int group = a.nheads / a.kvheads;
   const int gh = tc_heads_per_block(group), pp = TC_ROWS / gh;
   const int chunks = (group + gh - 1) / gh;
-  const int kvh = blockIdx.y / chunks, g0 = (blockIdx.y - kvh * chunks) * gh;
+  // heads vary fastest and the tiles run from the last to the first: later positions have more keys, and the long
+  // blocks of every head start before any short one
+  const int hc = blockIdx.x % (a.kvheads * chunks);
+  const int tile = n_tiles - 1 - blockIdx.x / (a.kvheads * chunks);
+  const int kvh = hc / chunks, g0 = (hc - kvh * chunks) * gh;
   const int ng = min(gh, group - g0);
-  const int tile = gridDim.x - 1 - blockIdx.x;  // later positions have more keys: the long tiles start first
   const int seq = tiles[2 * tile], r0 = tiles[2 * tile + 1];
   const int row_begin = a.first_row[seq];
   const int n_new = a.first_row[seq + 1] - row_begin;
@@ -144,13 +146,13 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc_kernel(const __grid_co
         tc_fence_after();
         const int s = i % TC_STAGES;
         const uint32_t vaddr = smem_u32(kv + (size_t)s * 2 * TC_KV_TILE) + TC_KV_TILE;
-        const uint32_t paddr = smem_u32(p_tile + (i & 1) * TC_P_BYTES);
-        // O += P V: P K-major (64 keys = one 128-byte row); V MN-major: 16 keys of a step are 16 rows of 128 bytes,
-        // the head's second 64 values lie one tile (BLK * 128 bytes) further
+        // O += P V: P from tensor memory, where it lies over the scores it came from (16 keys = 8 columns);
+        // V MN-major: 16 keys of a step are 16 rows of 128 bytes, the head's second 64 values lie one tile
+        // (BLK * 128 bytes) further.  The scores of block i + 2 are issued after this product and overwrite P then.
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)
-          umma(tmem_o, umma_desc(paddr + kk * 32), umma_desc_offsets(vaddr + kk * 16 * 128, BLK * 128, 1024), IDESC_O,
-               i > 0 || kk > 0);
+          umma_a_tmem(tmem_o, tmem_s + (i & 1) * BLK + kk * 8, umma_desc_offsets(vaddr + kk * 16 * 128, BLK * 128, 1024),
+                      IDESC_O, i > 0 || kk > 0);
         tc_commit(&kv_empty[s]);
         tc_commit(&o_done[i & 1]);
       }
@@ -223,26 +225,17 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc_kernel(const __grid_co
           tmem_store_32(tmem_o + lane_base + c0, o);
         }
       }
-      // the P buffer of this block was read by the product of the block two before
-      if (i >= 2) {
-        ok = __all_sync(0xffffffffu, wait_or_abort(&o_done[i & 1], ((i - 2) >> 1) & 1, failed));
-        if (!ok) break;
-      }
       const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
       float ps[4] = {0.f, 0.f, 0.f, 0.f};
-      unsigned char* p_row = p_tile + (i & 1) * TC_P_BYTES + r * 128;
+      float pk[BLK / 2];  // probabilities as bfloat16, two keys a word, into the columns their scores came from
 #pragma unroll
-      for (int c = 0; c < BLK / 8; ++c) {  // probabilities as bfloat16: 8 pieces of 8 keys, swizzled
-        uint32_t w[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float p0 = fast_exp2(fmaf(sc[8 * c + 2 * e], scale2, neg_m));  // 2^-inf = 0 for a masked key
-          const float p1 = fast_exp2(fmaf(sc[8 * c + 2 * e + 1], scale2, neg_m));
-          ps[e] += p0 + p1;
-          w[e] = pack_bf16(p0, p1);
-        }
-        *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      for (int j = 0; j < BLK / 2; ++j) {
+        const float p0 = fast_exp2(fmaf(sc[2 * j], scale2, neg_m));  // 2^-inf = 0 for a masked key
+        const float p1 = fast_exp2(fmaf(sc[2 * j + 1], scale2, neg_m));
+        ps[j & 3] += p0 + p1;
+        pk[j] = __uint_as_float(pack_bf16(p0, p1));
       }
+      tmem_store_32(tmem_s + (i & 1) * BLK + lane_base, pk);
       const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
       l += psum;
       // the values of a block that the sequence fills only partly: rows beyond its length become zeros
@@ -256,8 +249,8 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_tc_kernel(const __grid_co
           const int row = first_bad + idx / (HD / 8), c = idx % (HD / 8);
           *reinterpret_cast<uint4*>(vdst + (c / 8) * (BLK * 128) + row * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
+        fence_proxy_async();
       }
-      fence_proxy_async();
       tc_fence_before();
       mbar_arrive(&p_ready[i & 1]);
     }

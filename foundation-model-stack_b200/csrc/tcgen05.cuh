@@ -50,6 +50,16 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t 
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc), "r"(zero)
       : "memory");
 }
+// The same with the A operand in tensor memory: row m of A in lane m, two 16-bit values of consecutive k in a
+// 32-bit column (a k-step of 16 is 8 columns); A cannot be transposed there.
+__device__ __forceinline__ void umma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u, zero = 0u;
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(acc), "r"(zero)
+      : "memory");
+}
 // 32 consecutive float32 columns of this thread's row (lane) of tensor memory
 __device__ __forceinline__ void tmem_load_32(uint32_t taddr, float* v) {
   uint32_t r[32];
