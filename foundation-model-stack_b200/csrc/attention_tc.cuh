@@ -47,9 +47,13 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
   unsigned char* q_tile = smem;                            // HD / 64 tiles of [128 rows][128 bytes], swizzled
   unsigned char* kv = q_tile + TC_Q_BYTES;                 // per stage: keys (HD / 64 tiles of [64][128 B]), then values
-  uint64_t* kv_full = reinterpret_cast<uint64_t*>(kv + (size_t)TC_STAGES * 2 * TC_KV_TILE);
-  uint64_t* kv_empty = kv_full + TC_STAGES;
-  uint64_t* s_full = kv_empty + TC_STAGES;  // [2], as p_ready and o_done: block i uses entry i & 1, phase (i / 2) & 1
+  // keys and values have barriers of their own: the keys of block i + 2 may come once the scores of block i are
+  // computed, the values only after its product
+  uint64_t* k_full = reinterpret_cast<uint64_t*>(kv + (size_t)TC_STAGES * 2 * TC_KV_TILE);
+  uint64_t* k_empty = k_full + TC_STAGES;
+  uint64_t* v_full = k_empty + TC_STAGES;
+  uint64_t* v_empty = v_full + TC_STAGES;
+  uint64_t* s_full = v_empty + TC_STAGES;  // [2], as p_ready and o_done: block i uses entry i & 1, phase (i / 2) & 1
   uint64_t* p_ready = s_full + 2;
   uint64_t* o_done = p_ready + 2;
   uint64_t* q_ready = o_done + 2;
@@ -83,8 +87,10 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
   if (threadIdx.x == 0) {
     failed_flag = 0;
     for (int s = 0; s < TC_STAGES; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_full[b], 1);
@@ -106,17 +112,18 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
     if (elect_one()) {
       for (int i = 0; i < nblocks && !*failed; ++i) {
         const int s = i % TC_STAGES;
-        if (!wait_or_abort(&kv_empty[s], ((i / TC_STAGES) & 1) ^ 1, failed)) break;
         const int blk = a.table[(size_t)slot * a.table_stride + kb_lo + i];
         unsigned char* kdst = kv + (size_t)s * 2 * TC_KV_TILE;
         unsigned char* vdst = kdst + TC_KV_TILE;
         const int row = (max(blk, 0) * a.kvheads + kvh) * BLK;  // first row of the block in the [positions, HD] view
-        mbar_arrive_expect_tx(&kv_full[s], 2 * TC_KV_TILE);
+        if (!wait_or_abort(&k_empty[s], ((i / TC_STAGES) & 1) ^ 1, failed)) break;
+        mbar_arrive_expect_tx(&k_full[s], TC_KV_TILE);
 #pragma unroll
-        for (int c = 0; c < HD / 64; ++c) {
-          tma_load_2d(kdst + c * (BLK * 128), &map_k, c * 64, row, &kv_full[s]);
-          tma_load_2d(vdst + c * (BLK * 128), &map_v, c * 64, row, &kv_full[s]);
-        }
+        for (int c = 0; c < HD / 64; ++c) tma_load_2d(kdst + c * (BLK * 128), &map_k, c * 64, row, &k_full[s]);
+        if (!wait_or_abort(&v_empty[s], ((i / TC_STAGES) & 1) ^ 1, failed)) break;
+        mbar_arrive_expect_tx(&v_full[s], TC_KV_TILE);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c) tma_load_2d(vdst + c * (BLK * 128), &map_v, c * 64, row, &v_full[s]);
       }
     }
   } else if (warp == 1) {
@@ -127,7 +134,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
       // S(i) = Q K(i)^T into buffer i & 1: both operands K-major; k-step kk lies in tile kk / 4 at byte 32 (kk % 4)
       auto issue_scores = [&](int i) -> bool {
         const int s = i % TC_STAGES;
-        if (!wait_or_abort(&kv_full[s], (i / TC_STAGES) & 1, failed)) return false;
+        if (!wait_or_abort(&k_full[s], (i / TC_STAGES) & 1, failed)) return false;
         tc_fence_after();
         const uint32_t kaddr = smem_u32(kv + (size_t)s * 2 * TC_KV_TILE);
 #pragma unroll
@@ -135,6 +142,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
           umma(tmem_s + (i & 1) * BLK, umma_desc(qaddr + (kk / 4) * (TC_ROWS * 128) + (kk % 4) * 32),
                umma_desc(kaddr + (kk / 4) * (BLK * 128) + (kk % 4) * 32), IDESC_S, kk > 0);
         tc_commit(&s_full[i & 1]);
+        tc_commit(&k_empty[s]);
         return true;
       };
       bool go = wait_or_abort(q_ready, 0, failed) && issue_scores(0);  // the query tile is in shared memory
@@ -142,9 +150,10 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
         // the scores of the next block, while the rows of this one are exponentiated (its buffer was read two
         // blocks ago: p_ready of that block has been seen)
         if (i + 1 < nblocks && !issue_scores(i + 1)) break;
+        const int s = i % TC_STAGES;
+        if (!wait_or_abort(&v_full[s], (i / TC_STAGES) & 1, failed)) break;
         if (!wait_or_abort(&p_ready[i & 1], (i >> 1) & 1, failed)) break;  // probabilities written, O rescaled
         tc_fence_after();
-        const int s = i % TC_STAGES;
         const uint32_t vaddr = smem_u32(kv + (size_t)s * 2 * TC_KV_TILE) + TC_KV_TILE;
         // O += P V: P from tensor memory, where it lies over the scores it came from (16 keys = 8 columns);
         // V MN-major: 16 keys of a step are 16 rows of 128 bytes, the head's second 64 values lie one tile
@@ -153,7 +162,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
         for (int kk = 0; kk < BLK / 16; ++kk)
           umma_a_tmem(tmem_o, tmem_s + (i & 1) * BLK + kk * 8, umma_desc_offsets(vaddr + kk * 16 * 128, BLK * 128, 1024),
                       IDESC_O, i > 0 || kk > 0);
-        tc_commit(&kv_empty[s]);
+        tc_commit(&v_empty[s]);
         tc_commit(&o_done[i & 1]);
       }
     }
@@ -185,8 +194,8 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
       if (!ok) break;                                                    // every lane: tensor-memory loads are warp-wide
       tc_fence_after();
       float sc[BLK];
-      tmem_load_32(tmem_s + (i & 1) * BLK + lane_base, sc);
-      tmem_load_32(tmem_s + (i & 1) * BLK + lane_base + 32, sc + 32);
+      static_assert(BLK == 64, "a row of scores is read as 64 columns");
+      tmem_load_64(tmem_s + (i & 1) * BLK + lane_base, sc);
       // raw scores; the scale (positive) goes into the exponent's multiply-add.  A block that every row of the tile
       // sees whole needs no mask; rows without a query hold zeros there and are never stored.
       const bool whole = kb * BLK + BLK - 1 <= p_first && (a.window <= 0 || kb * BLK > p_last - a.window);
@@ -241,7 +250,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
       // the values of a block that the sequence fills only partly: rows beyond its length become zeros
       const int blk = a.table[(size_t)slot * a.table_stride + kb];
       if (kb * BLK + BLK > len || blk < 0) {
-        ok = __all_sync(0xffffffffu, wait_or_abort(&kv_full[s], (i / TC_STAGES) & 1, failed));
+        ok = __all_sync(0xffffffffu, wait_or_abort(&v_full[s], (i / TC_STAGES) & 1, failed));
         if (!ok) break;
         unsigned char* vdst = kv + (size_t)s * 2 * TC_KV_TILE + TC_KV_TILE;
         const int first_bad = blk < 0 ? 0 : len - kb * BLK;  // a block that has left the window holds nothing
