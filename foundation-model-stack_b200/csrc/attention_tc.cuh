@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&p_ready[b], 128);
+      mbar_init(&p_ready[b], 4);  // one arrival a warp
       mbar_init(&o_done[b], 1);
     }
     mbar_init(q_ready, 128);
@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
       tc_fence_after();
       float sc[BLK];
       static_assert(BLK == 64, "a row of scores is read as 64 columns");
-      tmem_load_64(tmem_s + (i & 1) * BLK + lane_base, sc);
+      tmem_load_2x32(tmem_s + (i & 1) * BLK + lane_base, tmem_s + (i & 1) * BLK + lane_base + 32, sc, sc + 32);
       // raw scores; the scale (positive) goes into the exponent's multiply-add.  A block that every row of the tile
       // sees whole needs no mask; rows without a query hold zeros there and are never stored.
       const bool whole = kb * BLK + BLK - 1 <= p_first && (a.window <= 0 || kb * BLK > p_last - a.window);
@@ -261,7 +261,8 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
         fence_proxy_async();
       }
       tc_fence_before();
-      mbar_arrive(&p_ready[i & 1]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready[i & 1]);
     }
     if (ok && __all_sync(0xffffffffu, wait_or_abort(&o_done[(nblocks - 1) & 1], ((nblocks - 1) >> 1) & 1, failed))) {
       tc_fence_after();
