@@ -381,7 +381,7 @@ int check_args(const char* what, int nheads, int kvheads, int head_dim, int bloc
 // Launches the decode kernels (splits, then combine) with the given scratch.  float32: CUDA-core kernel;
 // bfloat16: tensor-core kernel.  Both entry points below go through here.
 int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, int n_splits, float* part_o,
-                  float* part_ml, cudaStream_t stream) {
+                  float* part_ml, int pool_blocks, cudaStream_t stream) {
   if (n_splits <= 0 || n_splits > 65535) return fms_fail("%s: %d splits", what, n_splits);
   const int group = a.nheads / a.kvheads;
   if (a.nheads > 65535) return fms_fail("%s: %d heads", what, a.nheads);
@@ -407,8 +407,9 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
       if (e != cudaSuccess) return fms_fail("%s: %zu bytes of shared memory refused: %s", what, smem, cudaGetErrorString(e));
       configured[slot] = true;
     }
+    // the early L2 hints pay only while the GPU is not full of key and value traffic anyway
     fms_launch(kernel, dim3(n_seqs, a.kvheads * chunks, n_splits), dim3(nw * 32), smem, stream, a, part_o, part_ml,
-               n_splits);
+               n_splits, nw == 4 ? pool_blocks : 0);
     fms_launch(attn_combine_kernel<__nv_bfloat16>, dim3(n_seqs, a.nheads), dim3(HD >= 128 ? 128 : 64), 0, stream, a,
                (const float*)part_o, (const float*)part_ml, n_splits);
   } else {
@@ -489,15 +490,16 @@ FMS_API int fms_attention_prefill(const void* q, void* out, int dtype, const voi
 }
 
 // part_o: float [seqs, nheads, n_splits, HD]; part_ml: float [seqs, nheads, n_splits, 2]; both scratch.
+// pool_blocks: blocks in the cache (bounds the early L2 hints; 0 turns them off).
 FMS_API int fms_attention_decode(const void* q, void* out, int dtype, const void* keys, const void* values,
                                  const int* table, int table_stride, int block_tokens, const int* slots,
                                  const int* first_row, const int* len_after, int n_seqs, int n_splits, float* part_o,
                                  float* part_ml, int nheads, int kvheads, int head_dim, float scale, int window,
-                                 cudaStream_t stream) {
+                                 int pool_blocks, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (check_args("attention_decode", nheads, kvheads, head_dim, block_tokens)) return 1;
   AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window};
-  return launch_decode("attention_decode", a, dtype, n_seqs, n_splits, part_o, part_ml, stream);
+  return launch_decode("attention_decode", a, dtype, n_seqs, n_splits, part_o, part_ml, pool_blocks, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -555,5 +557,5 @@ FMS_API int fms_attention_decode_no_alloc(const void* q, void* out, int dtype, c
   float* part_o = scratch;                  // [seqs, nheads, n_splits, HD]
   float* part_ml = scratch + entries * HD;  // [seqs, nheads, n_splits, 2]
   AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window};
-  return launch_decode("attention_decode_no_alloc", a, dtype, n_seqs, n_splits, part_o, part_ml, stream);
+  return launch_decode("attention_decode_no_alloc", a, dtype, n_seqs, n_splits, part_o, part_ml, 0, stream);
 }

@@ -89,16 +89,35 @@ __device__ __forceinline__ void copy_block_async(unsigned char* dst, const __nv_
 constexpr int GROWS = 16;  // query heads per block (rows of the mma tile)
 
 template <int NW>
-__global__ void __launch_bounds__(NW * 32) attn_decode_mma_kernel(AttnArgs a, float* __restrict__ part_o,
-                                                                   float* __restrict__ part_ml, int n_splits) {
+__global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12)) attn_decode_mma_kernel(AttnArgs a, float* __restrict__ part_o,
+                                                                   float* __restrict__ part_ml, int n_splits,
+                                                                   int pool_blocks) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   pdl_launch_dependents();
-  pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
   const int seq = blockIdx.x, split = blockIdx.z;
   const int group = a.nheads / a.kvheads;
   const int chunks = (group + GROWS - 1) / GROWS;
   const int kvh = blockIdx.y / chunks, chunk = blockIdx.y - kvh * chunks;
+  // While the kernels before this one are still running: ask for this block's keys and values to be brought into
+  // L2.  Nothing orders these reads of the lengths and the table after the kernels that write them, so they may
+  // be a step old; they only choose the addresses of a hint, and a block number outside the pool is left alone.
+  // (Loads that bypass L1, so that no stale line is found again after the wait.)
+  if (pool_blocks > 0 && lane == 0) {
+    const int len0 = __ldcg(a.len_after + seq), slot0 = __ldcg(a.slots + seq);
+    const int start0 = a.window > 0 ? max(0, len0 - a.window) : 0;
+    const int lo0 = max(start0, split * SPLIT), hi0 = min(len0, (split + 1) * SPLIT);
+    if (slot0 >= 0) {
+      for (int kb = lo0 / BLK + warp; kb * BLK < hi0 && kb < a.table_stride; kb += NW) {
+        const int blk = __ldcg(a.table + (size_t)slot0 * a.table_stride + kb);
+        if (blk < 0 || blk >= pool_blocks) continue;
+        const size_t at = ((size_t)blk * a.kvheads + kvh) * BLK * HD;
+        prefetch_l2((const __nv_bfloat16*)a.keys + at, BLK * HD * 2);
+        prefetch_l2((const __nv_bfloat16*)a.values + at, BLK * HD * 2);
+      }
+    }
+  }
+  pdl_wait();
   const int g0 = chunk * GROWS;
   const int ng = min(GROWS, group - g0);
   const int len = a.len_after[seq];
