@@ -81,17 +81,32 @@ __device__ __forceinline__ void copy_block_async(unsigned char* dst, const __nv_
 }
 
 // ---------------------------------------------------------------------------------------------------
-// decode: grid (sequences, kv heads * head chunks, splits of 256 keys), NW warps.  The 16 rows of the mma tile
-// are up to 16 query heads that share the kv head.  Warp w takes the 64-key blocks w, w + NW, ... of the
-// split, each warp with a running softmax of its own; the warps' results are merged in shared memory and
-// written as one unnormalised partial result (m, l, o) per head, which attn_combine_kernel merges over splits.
+// decode: grid (sequences, kv heads * head chunks, splits of 256 keys), NW warps.  With one query per sequence the
+// products are taken transposed, so that the 8 columns of the mma tile are up to 8 query heads that share the kv
+// head and nothing of the 16 rows is wasted:
+//   S^T [64 keys x 8 heads]   = K [keys x HD] . Q^T      A = keys, read from global memory straight into
+//                                                          registers (16 contiguous bytes a lane; the k index of
+//                                                          the instruction is permuted alike for both operands)
+//   O^T [HD x 8 heads]       += V^T [HD x keys] . P^T     A = values, copied to shared memory while the scores are
+//                                                          taken and read transposed (ldmatrix.trans); B = the
+//                                                          probabilities, turned from accumulator to operand
+//                                                          layout by movmatrix
+// Warp w takes the 64-key blocks w, w + NW, ... of the split, each warp with a running softmax of its own; the
+// warps' results are merged in shared memory and written as one unnormalised partial result (m, l, o) per head,
+// which attn_combine_kernel merges over splits.
 // ---------------------------------------------------------------------------------------------------
-constexpr int GROWS = 16;  // query heads per block (rows of the mma tile)
+constexpr int GROWS = 8;  // query heads per block (columns of the mma tile)
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
+  return y;
+}
 
 template <int NW>
-__global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12)) attn_decode_mma_kernel(AttnArgs a, float* __restrict__ part_o,
-                                                                   float* __restrict__ part_ml, int n_splits,
-                                                                   int pool_blocks) {
+__global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
+    attn_decode_mma_kernel(AttnArgs a, float* __restrict__ part_o, float* __restrict__ part_ml, int n_splits,
+                           int pool_blocks) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   pdl_launch_dependents();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
@@ -130,115 +145,150 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12)) att
                            (size_t)(kvh * group + g0) * HD;
   const __nv_bfloat16* kc = (const __nv_bfloat16*)a.keys;
   const __nv_bfloat16* vc = (const __nv_bfloat16*)a.values;
-  // one buffer per warp: first the block's keys, then, once the scores are taken, its values (which were
-  // meanwhile brought into L2), so that a block of threads is small and several fit on a multiprocessor
-  unsigned char* kbuf = smem_raw + (size_t)warp * BLK * ROWB;
-  unsigned char* vbuf = kbuf;
+  unsigned char* vbuf = smem_raw + (size_t)warp * BLK * ROWB;  // one buffer of values per warp
 
-  // query fragments: rows g and g + 8 are heads g0 + g and g0 + g + 8 (zero beyond the group)
-  uint32_t qf[HD / 16][4];
+  // A lane's part of the k index: of every 32 values of a row it holds the 8 from 8 c on (k-steps 2 s and
+  // 2 s + 1 take two pairs each); of a last 16 alone, the instruction's own pairs 2 c and 2 c + 8.
+  constexpr int G32 = HD / 32;
+  constexpr bool TAIL = HD % 32 != 0;
+  uint32_t qf[G32 + 1][4];  // B operand: head g0 + g (zeros beyond the group)
+  {
+    const __nv_bfloat16* qrow = q + (size_t)g * HD;
 #pragma unroll
-  for (int s = 0; s < HD / 16; ++s) {
-    const uint32_t* r0 = reinterpret_cast<const uint32_t*>(q + (size_t)g * HD + 16 * s + 2 * c);
-    const uint32_t* r1 = reinterpret_cast<const uint32_t*>(q + (size_t)(g + 8) * HD + 16 * s + 2 * c);
-    qf[s][0] = g < ng ? r0[0] : 0u;
-    qf[s][1] = g + 8 < ng ? r1[0] : 0u;
-    qf[s][2] = g < ng ? r0[4] : 0u;
-    qf[s][3] = g + 8 < ng ? r1[4] : 0u;
+    for (int s = 0; s < G32; ++s) {
+      const uint4 v = g < ng ? *reinterpret_cast<const uint4*>(qrow + 32 * s + 8 * c) : make_uint4(0, 0, 0, 0);
+      qf[s][0] = v.x; qf[s][1] = v.y; qf[s][2] = v.z; qf[s][3] = v.w;
+    }
+    if (TAIL) {
+      const uint32_t* t = reinterpret_cast<const uint32_t*>(qrow + 32 * G32 + 2 * c);
+      qf[G32][0] = g < ng ? t[0] : 0u;
+      qf[G32][1] = g < ng ? t[4] : 0u;
+      qf[G32][2] = qf[G32][3] = 0u;
+    }
   }
-  float o[HD / 8][4];
+  float o[HD / 16][4];  // O^T: element e of tile j is (value 16 j + g + 8 (e / 2), head 2 c + (e % 2))
 #pragma unroll
-  for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};  // running maximum in units of log2, and sum
+  for (int j = 0; j < HD / 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};  // of heads 2 c and 2 c + 1; maximum in units of log2
   const float scale2 = a.scale * LOG2E;  // scores are kept times log2(e): exp(x) = exp2(x log2 e)
 
   for (int kb = k_lo / BLK + warp; kb * BLK < k_hi; kb += NW) {
     const int blk = a.table[(size_t)slot * a.table_stride + kb];
     if (blk < 0) continue;
+    const __nv_bfloat16* ksrc = kc + ((size_t)blk * a.kvheads + kvh) * BLK * HD;
     __syncwarp();  // the buffer is free: every lane is past the previous block
-    const __nv_bfloat16* vsrc = vc + ((size_t)blk * a.kvheads + kvh) * BLK * HD;
-    copy_block_async(kbuf, kc + ((size_t)blk * a.kvheads + kvh) * BLK * HD, kb * BLK, k_lo, k_hi, lane);
+    copy_block_async(vbuf, vc + ((size_t)blk * a.kvheads + kvh) * BLK * HD, kb * BLK, k_lo, k_hi, lane);
     cp_async_commit_group();
-    if (lane == 0) prefetch_l2(vsrc, BLK * HD * 2);
-    cp_async_wait_group<0>();
-    __syncwarp();
-    // scores of 16 rows x 64 keys
-    float s[8][4];
-    scores_16x64(s, qf, kbuf, lane);
-    // element e of tile j: row g + 8 (e / 2), key 8 j + 2 c + (e % 2)
+    // scores, 16 keys at a time: element e of tile t is (key 16 t + g + 8 (e / 2), head 2 c + (e % 2)).  Rows of
+    // the block beyond the sequence are read too (they exist) and masked below.
+    float st[4][4];
+    uint4 ka[2][G32 > 0 ? G32 : 1][2];
+    uint32_t kt[2][2][2];
+    auto load_keys = [&](int t) {
+      const __nv_bfloat16* r0 = ksrc + (size_t)(16 * t + g) * HD;
+      const __nv_bfloat16* r1 = r0 + 8 * HD;
+#pragma unroll
+      for (int s = 0; s < G32; ++s) {
+        ka[t & 1][s][0] = *reinterpret_cast<const uint4*>(r0 + 32 * s + 8 * c);
+        ka[t & 1][s][1] = *reinterpret_cast<const uint4*>(r1 + 32 * s + 8 * c);
+      }
+      if (TAIL) {
+        const uint32_t* t0 = reinterpret_cast<const uint32_t*>(r0 + 32 * G32 + 2 * c);
+        const uint32_t* t1 = reinterpret_cast<const uint32_t*>(r1 + 32 * G32 + 2 * c);
+        kt[t & 1][0][0] = t0[0]; kt[t & 1][0][1] = t0[4];
+        kt[t & 1][1][0] = t1[0]; kt[t & 1][1][1] = t1[4];
+      }
+    };
+    load_keys(0);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      if (t + 1 < 4) load_keys(t + 1);
+      st[t][0] = st[t][1] = st[t][2] = st[t][3] = 0.f;
+#pragma unroll
+      for (int s = 0; s < G32; ++s) {
+        const uint4 k0 = ka[t & 1][s][0], k1 = ka[t & 1][s][1];
+        const uint32_t a0[4] = {k0.x, k1.x, k0.y, k1.y}, a1[4] = {k0.z, k1.z, k0.w, k1.w};
+        mma16816(st[t], a0, qf[s][0], qf[s][1]);
+        mma16816(st[t], a1, qf[s][2], qf[s][3]);
+      }
+      if (TAIL) {
+        const uint32_t a0[4] = {kt[t & 1][0][0], kt[t & 1][1][0], kt[t & 1][0][1], kt[t & 1][1][1]};
+        mma16816(st[t], a0, qf[G32][0], qf[G32][1]);
+      }
+    }
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int t = 0; t < 4; ++t)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int kpos = kb * BLK + 8 * j + 2 * c + (e & 1);
-        s[j][e] = (kpos >= k_lo && kpos < k_hi) ? s[j][e] * scale2 : -INFINITY;
-        tile_max[e >> 1] = fmaxf(tile_max[e >> 1], s[j][e]);
+        const int kpos = kb * BLK + 16 * t + g + 8 * (e >> 1);
+        st[t][e] = (kpos >= k_lo && kpos < k_hi) ? st[t][e] * scale2 : -INFINITY;
+        tile_max[e & 1] = fmaxf(tile_max[e & 1], st[t][e]);
       }
     float alpha[2], psum[2] = {0.f, 0.f}, m_use[2];
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
-      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
-      const float m_new = fmaxf(m[r], tile_max[r]);
-      m_use[r] = m_new == -INFINITY ? 0.f : m_new;
-      alpha[r] = m[r] == -INFINITY ? 0.f : exp2f(m[r] - m_use[r]);
-      m[r] = m_new;
+    for (int h = 0; h < 2; ++h) {  // over the keys: the lanes that differ in g
+      tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 4));
+      tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 8));
+      tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 16));
+      const float m_new = fmaxf(m[h], tile_max[h]);
+      m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+      alpha[h] = m[h] == -INFINITY ? 0.f : exp2f(m[h] - m_use[h]);
+      m[h] = m_new;
     }
-    uint32_t pf[4][4];  // probabilities as A fragments: k-step t covers keys 16 t .. 16 t + 15
+    uint32_t pb[4][2];  // P^T as B operand of k-step t (keys 16 t ..): (keys 2 c, 2 c + 1 (+ 8); head g)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int t = 0; t < 4; ++t) {
       float p[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        p[e] = s[j][e] == -INFINITY ? 0.f : exp2f(s[j][e] - m_use[e >> 1]);
-        psum[e >> 1] += p[e];
+        p[e] = st[t][e] == -INFINITY ? 0.f : exp2f(st[t][e] - m_use[e & 1]);
+        psum[e & 1] += p[e];
       }
-      pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
-      pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
+      pb[t][0] = movmatrix_trans(pack_bf16(p[0], p[1]));
+      pb[t][1] = movmatrix_trans(pack_bf16(p[2], p[3]));
     }
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 1);
-      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 2);
-      l[r] = l[r] * alpha[r] + psum[r];
+    for (int h = 0; h < 2; ++h) {
+      psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], 4);
+      psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], 8);
+      psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], 16);
+      l[h] = l[h] * alpha[h] + psum[h];
     }
 #pragma unroll
-    for (int j = 0; j < HD / 8; ++j) {
-      o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+    for (int j = 0; j < HD / 16; ++j) {
+      o[j][0] *= alpha[0]; o[j][1] *= alpha[1]; o[j][2] *= alpha[0]; o[j][3] *= alpha[1];
     }
-    __syncwarp();  // every lane has taken its scores: the keys may be overwritten by the values
-    copy_block_async(vbuf, vsrc, kb * BLK, k_lo, k_hi, lane);
-    cp_async_commit_group();
     cp_async_wait_group<0>();
     __syncwarp();
+    // V^T tiles of 16 values x 16 keys: matrix (lane >> 3) of the four is (values + 8 ((lane >> 3) & 1),
+    // keys + 8 (lane >> 4)), its rows in shared memory are keys
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
-      const unsigned char* vrow = vbuf + (16 * t + (lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (lane >> 4) * 16;
+      const unsigned char* vrow = vbuf + (16 * t + (lane & 7) + (lane >> 4) * 8) * ROWB + ((lane >> 3) & 1) * 16;
 #pragma unroll
-      for (int jd = 0; jd < HD / 8; jd += 2) {
-        uint32_t b[4];
-        ldmatrix_x4_trans(b, vrow + jd * 16);
-        mma16816(o[jd], pf[t], b[0], b[1]);
-        mma16816(o[jd + 1], pf[t], b[2], b[3]);
+      for (int j = 0; j < HD / 16; ++j) {
+        uint32_t av[4];
+        ldmatrix_x4_trans(av, vrow + j * 32);
+        mma16816(o[j], av, pb[t][0], pb[t][1]);
       }
     }
   }
 
-  // merge the warps: each writes (m, l, o) of its 16 rows over its own key buffer
+  // merge the warps: each writes (m, l, o) of its 8 heads over its own buffer
   __syncwarp();
-  float* wo = reinterpret_cast<float*>(kbuf);          // [16][HD]
-  float* wml = wo + 16 * HD;                           // [16][2]
+  float* wo = reinterpret_cast<float*>(vbuf);          // [8][HD]
+  float* wml = wo + GROWS * HD;                        // [8][2]
 #pragma unroll
-  for (int j = 0; j < HD / 8; ++j) {
-    wo[g * HD + 8 * j + 2 * c] = o[j][0];
-    wo[g * HD + 8 * j + 2 * c + 1] = o[j][1];
-    wo[(g + 8) * HD + 8 * j + 2 * c] = o[j][2];
-    wo[(g + 8) * HD + 8 * j + 2 * c + 1] = o[j][3];
+  for (int j = 0; j < HD / 16; ++j) {
+    wo[(2 * c) * HD + 16 * j + g] = o[j][0];
+    wo[(2 * c + 1) * HD + 16 * j + g] = o[j][1];
+    wo[(2 * c) * HD + 16 * j + g + 8] = o[j][2];
+    wo[(2 * c + 1) * HD + 16 * j + g + 8] = o[j][3];
   }
-  if (c == 0) {
-    wml[2 * g] = m[0]; wml[2 * g + 1] = l[0];
-    wml[2 * (g + 8)] = m[1]; wml[2 * (g + 8) + 1] = l[1];
+  if (g == 0) {
+    wml[2 * (2 * c)] = m[0]; wml[2 * (2 * c) + 1] = l[0];
+    wml[2 * (2 * c + 1)] = m[1]; wml[2 * (2 * c + 1) + 1] = l[1];
   }
   __syncthreads();
   for (int i = tid; i < ng * HD; i += NW * 32) {
@@ -246,12 +296,12 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12)) att
     float mm = -INFINITY;
 #pragma unroll
     for (int w = 0; w < NW; ++w)
-      mm = fmaxf(mm, (reinterpret_cast<const float*>(smem_raw + (size_t)w * BLK * ROWB) + 16 * HD)[2 * r]);
+      mm = fmaxf(mm, (reinterpret_cast<const float*>(smem_raw + (size_t)w * BLK * ROWB) + GROWS * HD)[2 * r]);
     float sum = 0.f, lsum = 0.f;
 #pragma unroll
     for (int w = 0; w < NW; ++w) {
       const float* wv = reinterpret_cast<const float*>(smem_raw + (size_t)w * BLK * ROWB);
-      const float* wm = wv + 16 * HD;
+      const float* wm = wv + GROWS * HD;
       const float f = wm[2 * r] == -INFINITY ? 0.f : exp2f(wm[2 * r] - mm);
       sum += wv[r * HD + d] * f;
       lsum += wm[2 * r + 1] * f;
