@@ -29,21 +29,11 @@ constexpr int TQ = 16;            // query rows per prefill block
 
 template <typename T> struct Vec;  // 16-byte vectors
 template <> struct Vec<float> { static constexpr int N = 4; };
-template <> struct Vec<__nv_bfloat16> { static constexpr int N = 8; };
 
 template <typename T> __device__ __forceinline__ void load_vec(const T* p, float* out);
 template <> __device__ __forceinline__ void load_vec<float>(const float* p, float* out) {
   const float4 v = *reinterpret_cast<const float4*>(p);
   out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
-}
-template <> __device__ __forceinline__ void load_vec<__nv_bfloat16>(const __nv_bfloat16* p, float* out) {
-  const uint4 v = *reinterpret_cast<const uint4*>(p);
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    out[2 * i] = __uint_as_float(w[i] << 16);
-    out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-  }
 }
 
 struct AttnArgs {
@@ -361,6 +351,7 @@ __global__ void attn_combine_kernel(AttnArgs a, const float* __restrict__ part_o
 #define FMS_ATTENTION_TC 0
 #endif
 
+#if FMS_ATTENTION_TC
 // whether bfloat16 prefill takes the tcgen05 kernel (head sizes 64 and 128; FMS_B200_ATTN_TC=0 turns it off)
 static bool prefill_on_tcgen05() {
   static int on = -1;
@@ -370,6 +361,7 @@ static bool prefill_on_tcgen05() {
   }
   return on == 1;
 }
+#endif
 
 int check_args(const char* what, int nheads, int kvheads, int head_dim, int block_tokens) {
   if (head_dim != HD) return fms_fail("%s: this library is built for head size %d, not %d", what, HD, head_dim);

@@ -116,6 +116,58 @@ def test_attention_part_alone(dtype, nheads, kvheads, hd, window):
         close(torch.cat(outs), want, dtype)
 
 
+def test_toy_position_encoding_is_registered_and_used_by_the_mixer():
+    """Another position encoding, defined here: rotation of pairs with frequencies that fall linearly instead of
+    geometrically.  It is registered under a name of its own and chosen by the mixer's spec; the attention part and
+    its kernels take it without a change."""
+    from fms_b200.cache import Cache
+    from fms_b200.config import MixerSpec, PositionSpec
+    from fms_b200.parts import Part, build_mixer, register_position, registered
+
+    class LinearFrequencies(Part):
+        def __init__(self, spec):
+            super().__init__()
+            self.half, self.top = spec.head_dim // 2, spec.theta
+            self._f = None
+
+        def frequencies(self):
+            return (self.top * (1.0 - torch.arange(self.half).float() / self.half)).float()
+
+        def finalize(self, device, dtype):
+            self._f = self.frequencies().to(device).contiguous()
+
+        def rotary_frequencies(self):
+            return self._f
+
+    if "toy_linear_frequencies" not in registered("position"):
+        register_position("toy_linear_frequencies", LinearFrequencies)
+    nheads, kvheads, hd, n, dtype = 4, 2, 32, 90, torch.float32
+    spec = MixerSpec("attention", dim=nheads * hd, nheads=nheads, kvheads=kvheads, head_dim=hd,
+                     position=PositionSpec("toy_linear_frequencies", head_dim=hd, theta=0.3))
+    mixer = build_mixer(spec)
+    assert type(mixer.position).__name__ == "LinearFrequencies"
+    w = fill(mixer, dtype, 12, scale=0.08)
+    x = torch.randn(n, nheads * hd, generator=torch.Generator().manual_seed(13))
+    inv = mixer.position.frequencies().double()
+    qkv = x.double() @ w["in_proj.qkv_fused.weight"].T
+    q, k, v = qkv.split([nheads * hd, kvheads * hd, kvheads * hd], -1)
+    pos = torch.arange(n)
+    a = pl.plain_attention(pl.plain_rope(q.view(n, nheads, hd), pos, inv), pl.plain_rope(k.view(n, kvheads, hd), pos, inv),
+                           v.view(n, kvheads, hd)).reshape(n, -1)
+    want = a @ w["dense.weight"].T
+    cache = Cache([mixer.cache_request()], max_tokens=256, max_positions=256, dtype=dtype, device="cuda")
+    (slot,) = cache.begin(1)
+    outs, at = [], 0
+    for k_new in (60, 1, 29):
+        batch = one_sequence_batch(k_new, at, cache, slot)
+        outs.append(mixer.forward(x[at:at + k_new].cuda().contiguous(), batch, cache.layer_view(0), True))
+        cache.commit([slot], [k_new])
+        at += k_new
+    close(torch.cat(outs), want, dtype)
+    # the toy's frequencies are not the ordinary ones, so the agreement above is not an accident
+    assert not torch.allclose(inv.float(), pl.plain_rope_inv_freq(hd, 10000.0).float())
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("rows", [3, 40])
 def test_feed_forward_part_alone(dtype, rows):
