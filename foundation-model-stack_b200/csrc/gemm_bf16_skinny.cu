@@ -1,4 +1,4 @@
-// y[M, N] = x[M, K] . w[N, K]^T (+ bias) for few rows (M <= 16): the products of a decode step, which read
+// y[M, N] = x[M, K] . w[N, K]^T (+ bias) for few rows (M <= 8): the products of a decode step, which read
 // every weight once and are bound by memory bandwidth.  bfloat16 operands, float32 accumulation on the
 // tensor cores (mma.sync m16n8k16: 16 weight rows x 8 batch rows per instruction), float32 or bfloat16 out.
 //
@@ -230,31 +230,28 @@ int launch(const void* x, const void* w, const void* bias, void* y, int out_dtyp
 }
 }  // namespace
 
-FMS_API int fms_linear_skinny_max_rows() { return 16; }
+// More rows than the 8 columns of one mma would make every block read twice as much of x as of w (a block owns 16
+// rows of w and all of x); from 9 rows on the caller takes another product.
+FMS_API int fms_linear_skinny_max_rows() { return 8; }
 
-// y [M, N] (out_dtype) = x [M, K] w[N, K]^T + bias.  M <= 16, K a multiple of 8, all bfloat16 inputs.
+// y [M, N] (out_dtype) = x [M, K] w[N, K]^T + bias.  M <= 8, K a multiple of 8, all bfloat16 inputs.
 FMS_API int fms_linear_bf16_skinny(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M, int N,
                                    int K, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (M > 16) return fms_fail("linear_bf16_skinny: %d rows, at most 16", M);
+  if (M > 8) return fms_fail("linear_bf16_skinny: %d rows, at most 8", M);
   if (K <= 0 || K % 8) return fms_fail("linear_bf16_skinny: K %d must be a positive multiple of 8", K);
   if (out_dtype != FMS_F32 && out_dtype != FMS_BF16) return fms_fail("linear_bf16_skinny: out dtype %d", out_dtype);
   // very many weight rows: 32 rows a block, which halves the re-reading of x
-  if (M <= 8) {
-    if (N < 16384) return launch<1, 1, ROWS16>(x, w, bias, y, out_dtype, M, N, K, 0, 0, stream);
-    return launch<1, 2, ROWS16>(x, w, bias, y, out_dtype, M, N, K, 0, 0, stream);
-  }
-  if (N < 16384) return launch<2, 1, ROWS16>(x, w, bias, y, out_dtype, M, N, K, 0, 0, stream);
-  return launch<2, 2, ROWS16>(x, w, bias, y, out_dtype, M, N, K, 0, 0, stream);
+  if (N < 16384) return launch<1, 1, ROWS16>(x, w, bias, y, out_dtype, M, N, K, 0, 0, stream);
+  return launch<1, 2, ROWS16>(x, w, bias, y, out_dtype, M, N, K, 0, 0, stream);
 }
 
 // y [M, hidden] = act(x w_gate^T + b_gate) * (x w_up^T + b_up) with w = [gate; up] of 2 hidden rows.
 FMS_API int fms_glu_bf16_skinny(const void* x, const void* w, const void* bias, void* y, int M, int hidden, int K,
                                 int act, cudaStream_t stream) {
   if (M <= 0 || hidden <= 0) return 0;
-  if (M > 16) return fms_fail("glu_bf16_skinny: %d rows, at most 16", M);
+  if (M > 8) return fms_fail("glu_bf16_skinny: %d rows, at most 8", M);
   if (K <= 0 || K % 8) return fms_fail("glu_bf16_skinny: K %d must be a positive multiple of 8", K);
   if (act < 0 || act > 3) return fms_fail("glu_bf16_skinny: activation %d", act);
-  if (M <= 8) return launch<1, 2, GLU8>(x, w, bias, y, FMS_BF16, M, 2 * hidden, K, hidden, act, stream);
-  return launch<2, 2, GLU8>(x, w, bias, y, FMS_BF16, M, 2 * hidden, K, hidden, act, stream);
+  return launch<1, 2, GLU8>(x, w, bias, y, FMS_BF16, M, 2 * hidden, K, hidden, act, stream);
 }

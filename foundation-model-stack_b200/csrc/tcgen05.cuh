@@ -160,14 +160,6 @@ __device__ __forceinline__ void tmem_store_32(uint32_t taddr, const float* v) {
       : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
 }
-// 16 consecutive columns of this thread's row
-__device__ __forceinline__ void tmem_store_16(uint32_t taddr, const float* v) {
-  uint32_t r[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(v[i]);
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
-  asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-}
 // makes writes to shared memory by ordinary stores visible to the tensor cores and to TMA
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 // shared-memory matrix descriptor with the 128-byte swizzle and explicit offsets (in bytes): `lbo` between the

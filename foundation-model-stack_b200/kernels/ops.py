@@ -202,7 +202,7 @@ def gated_linear_tensor_core(x: torch.Tensor, weight: torch.Tensor, bias: Option
     return y
 
 
-SKINNY_ROWS = 16  # rows up to which the weight-streaming kernels are used
+SKINNY_ROWS = 8  # rows up to which the weight-streaming kernels are used (more rows re-read x too often)
 
 
 # ---- feed-forward ------------------------------------------------------------------------------------

@@ -87,7 +87,7 @@ def test_linear_float32_is_true_float32(ops, m, n, k, bias):
     assert torch.equal(alone[0], got[0])
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 331, 240), (8, 512, 96), (33, 1000, 328), (200, 384, 64)])
+@pytest.mark.parametrize("m,n,k", [(1, 331, 240), (8, 512, 96), (9, 331, 240), (16, 512, 96), (33, 1000, 328), (200, 384, 64)])
 def test_linear_bfloat16(ops, m, n, k):
     g = torch.Generator().manual_seed(4)
     x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
@@ -101,12 +101,12 @@ def test_linear_bfloat16(ops, m, n, k):
     torch.testing.assert_close(got32.double(), want, atol=1e-3, rtol=1e-3)
 
 
-@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("m", [1, 3, 8])
 @pytest.mark.parametrize("n,k", [(331, 240), (40, 8), (4096 + 16, 1000), (16400, 96), (331, 256), (4099, 1152), (7, 128)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_linear_bfloat16_few_rows(ops, m, n, k, out_dtype):
     """The weight-streaming kernel of decode steps: odd numbers of weight rows, K that is no multiple of 32,
-    one to sixteen batch rows, with and without bias."""
+    one to eight batch rows, with and without bias."""
     g = torch.Generator().manual_seed(40 + m)
     x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
     w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).cuda()
@@ -122,7 +122,7 @@ def test_linear_bfloat16_few_rows(ops, m, n, k, out_dtype):
     assert torch.equal(alone[0], ops.linear(x, w, None, out_dtype)[0])
 
 
-@pytest.mark.parametrize("m", [1, 8, 13])
+@pytest.mark.parametrize("m", [1, 5, 8])
 @pytest.mark.parametrize("hidden,k", [(176, 64), (328, 240), (1000, 96), (14336, 128), (331, 384), (5, 1024)])
 @pytest.mark.parametrize("act", [0, 2])
 def test_gated_linear_few_rows(ops, m, hidden, k, act):
