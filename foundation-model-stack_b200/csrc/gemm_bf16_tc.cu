@@ -2,15 +2,18 @@
 // memory, on the fifth-generation tensor cores of sm_100a (tcgen05.mma issued by one thread, operands brought
 // into shared memory by TMA, the accumulator read back with tcgen05.ld for the epilogue).
 //
-// A tile of y is 128 x 256 (128 rows of x against 256 rows of w) — or, in the GLU variant, a 128 x 128 tile of
-// act(x w_gate^T) * (x w_up^T), whose 256 accumulator columns are 128 gate and the 128 matching up rows of a
-// fused [gate; up] weight (fms/modules/feedforward.py:288-297).  One persistent thread block per
-// multiprocessor walks over the tiles.
+// A tile of y is 128 x TN (128 rows of x against TN rows of w; TN a multiple of 16 up to 256) — or, in the GLU
+// variant, a 128 x TN/2 tile of act(x w_gate^T) * (x w_up^T), whose TN accumulator columns are TN/2 gate and the
+// TN/2 matching up rows of a fused [gate; up] weight (fms/modules/feedforward.py:288-297).  One persistent thread
+// block per multiprocessor walks over the tiles.  TN is chosen per product so that the tiles fill whole rounds of
+// the multiprocessors: 256 tiles of 128 x 256 on 148 multiprocessors are two rounds of which the second is 3/4
+// idle, 592 tiles of 128 x 112 are exactly four.
 //
-//   warp 0   one lane issues the TMA loads: per step of 64 k, a 128 x 64 box of x and two 128 x 64 boxes of w
-//            (128-byte swizzle) into one of 4 stages, completion counted on the stage's "full" mbarrier
+//   warp 0   one lane issues the TMA loads: per step of 64 k, a 128 x 64 box of x and a TN x 64 box of w (GLU: two
+//            of TN/2 rows), 128-byte swizzle, into one of 4 to 8 stages, completion counted on the stage's "full"
+//            mbarrier
 //   warp 1   allocates all 512 columns of tensor memory (two accumulators); one lane waits for "full", issues 4
-//            tcgen05.mma (128 x 256 x 16 each) on the stage and commits them to the stage's "empty" mbarrier;
+//            tcgen05.mma (128 x TN x 16 each) on the stage and commits them to the stage's "empty" mbarrier;
 //            after a tile's last step it commits to that accumulator's "ready" mbarrier
 //   warps 2-5  wait for an accumulator, read their 32 rows of it 32 columns at a time, convert, store, and
 //            give the accumulator back, while the mma warp already works on the next tile in the other one
@@ -23,14 +26,13 @@
 #include "common.cuh"
 
 namespace {
-constexpr int TILE_M = 128, TILE_N = 256, TILE_K = 64, STAGES = 4, UMMA_K = 16;
-constexpr int A_BYTES = TILE_M * TILE_K * 2, B_BYTES = TILE_N * TILE_K * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TILE_M = 128, MAX_TILE_N = 256, TILE_K = 64, MAX_STAGES = 8, UMMA_K = 16;
+constexpr int A_BYTES = TILE_M * TILE_K * 2;
 constexpr int THREADS = 192;
-constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int RING_BYTES = 192 * 1024;  // of the stages together
+constexpr size_t SMEM_BYTES = (size_t)RING_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 
 #include "tcgen05.cuh"
-
-constexpr uint32_t IDESC = umma_idesc(TILE_M, TILE_N);
 
 __device__ __forceinline__ float activate(float g, int act) {
   switch (act) {
@@ -45,14 +47,17 @@ struct Epilogue {
   void* out;          // [M, N] bfloat16 or float32; GLU: [M, hidden] bfloat16
   const void* bias;   // bfloat16 [N] (GLU: [2 hidden]) or null
   int out_f32;        // plain only
-  int glu;            // 1: columns 0-127 of the accumulator are gate rows, 128-255 the matching up rows
+  int glu;            // 1: the first half of the accumulator's columns are gate rows, the second the matching up rows
   int hidden;         // GLU: rows of the gate matrix
   int act;
+  int tile_n;         // accumulator columns of a tile: rows of w per tile (GLU: gate and up together)
+  int stages;
 };
 
 // Persistent: block b computes tiles b, b + gridDim.x, ...; tiles are numbered with the row index fastest, so
 // that the blocks running at the same time share few tiles of w.  The accumulator is double-buffered in tensor
-// memory (2 x 256 columns): the epilogue of a tile runs while the mma of the block's next tile are issued.
+// memory (2 x 256 columns, of which TN are used): the epilogue of a tile runs while the mma of the block's next
+// tile are issued.
 // Barriers that a consumer gives back ("empty") are waited for with the opposite parity, which a freshly
 // initialised mbarrier satisfies at once.
 __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -60,9 +65,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
                                                              int N, int K, int* __restrict__ error_flag) {
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)STAGES * STAGE_BYTES);
-  uint64_t* empty = full + STAGES;
-  uint64_t* acc_full = empty + STAGES;   // [2]
+  const int b_bytes = ep.tile_n * TILE_K * 2, stage_bytes = A_BYTES + b_bytes, stages = ep.stages;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)RING_BYTES);
+  uint64_t* empty = full + MAX_STAGES;
+  uint64_t* acc_full = empty + MAX_STAGES;   // [2]
   uint64_t* acc_empty = acc_full + 2;    // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   __shared__ int failed_flag;
@@ -70,14 +76,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile_n = ep.glu ? TILE_N / 2 : TILE_N;  // output columns of a tile
+  const int tile_n = ep.glu ? ep.tile_n / 2 : ep.tile_n;  // output columns of a tile
   const int tiles_m = (M + TILE_M - 1) / TILE_M, tiles_n = (N + tile_n - 1) / tile_n;
   const int n_tiles = tiles_m * tiles_n;
   const int k_steps = (K + TILE_K - 1) / TILE_K;
 
   if (threadIdx.x == 0) {
     failed_flag = 0;
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < MAX_STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
@@ -87,7 +93,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
     }
     mbar_fence_init();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, 2 * TILE_N);
+  if (warp == 1) tmem_alloc(tmem_slot, 2 * MAX_TILE_N);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -101,34 +107,35 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
       for (int tile = blockIdx.x; tile < n_tiles && !*failed; tile += gridDim.x) {
         const int m0 = (tile % tiles_m) * TILE_M, n0 = (tile / tiles_m) * tile_n;
         for (int i = 0; i < k_steps; ++i, ++it) {
-          const int s = it % STAGES;
-          if (!wait_or_abort(&empty[s], ((it / STAGES) & 1) ^ 1, failed)) break;
-          unsigned char* a = smem + (size_t)s * STAGE_BYTES;
+          const int s = it % stages;
+          if (!wait_or_abort(&empty[s], ((it / stages) & 1) ^ 1, failed)) break;
+          unsigned char* a = smem + (size_t)s * stage_bytes;
           unsigned char* b = a + A_BYTES;
-          mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+          mbar_arrive_expect_tx(&full[s], stage_bytes);
           tma_load_2d(a, &map_a, i * TILE_K, m0, &full[s]);
-          // the tile's 256 rows of w: a whole range, or 128 gate rows and the 128 up rows that belong to them
+          // the tile's rows of w: a whole range in one box, or the gate rows and the up rows that belong to them
           tma_load_2d(b, &map_b, i * TILE_K, n0, &full[s]);
-          tma_load_2d(b + B_BYTES / 2, &map_b, i * TILE_K, ep.glu ? ep.hidden + n0 : n0 + TILE_N / 2, &full[s]);
+          if (ep.glu) tma_load_2d(b + b_bytes / 2, &map_b, i * TILE_K, ep.hidden + n0, &full[s]);
         }
       }
     }
   } else if (warp == 1) {
     if (elect_one()) {
+      const uint32_t idesc = umma_idesc(TILE_M, ep.tile_n);
       int it = 0, j = 0;
       for (int tile = blockIdx.x; tile < n_tiles && !*failed; tile += gridDim.x, ++j) {
         const int acc = j & 1;
         if (!wait_or_abort(&acc_empty[acc], ((j >> 1) & 1) ^ 1, failed)) break;  // the epilogue has read this buffer
         tc_fence_after();
-        const uint32_t d = tmem + acc * TILE_N;
+        const uint32_t d = tmem + acc * MAX_TILE_N;
         for (int i = 0; i < k_steps; ++i, ++it) {
-          const int s = it % STAGES;
-          if (!wait_or_abort(&full[s], (it / STAGES) & 1, failed)) break;
+          const int s = it % stages;
+          if (!wait_or_abort(&full[s], (it / stages) & 1, failed)) break;
           tc_fence_after();
-          const uint32_t a = smem_u32(smem + (size_t)s * STAGE_BYTES), b = a + A_BYTES;
+          const uint32_t a = smem_u32(smem + (size_t)s * stage_bytes), b = a + A_BYTES;
 #pragma unroll
           for (int kk = 0; kk < TILE_K / UMMA_K; ++kk)
-            umma(d, umma_desc(a + kk * UMMA_K * 2), umma_desc(b + kk * UMMA_K * 2), IDESC, i > 0 || kk > 0);
+            umma(d, umma_desc(a + kk * UMMA_K * 2), umma_desc(b + kk * UMMA_K * 2), idesc, i > 0 || kk > 0);
           tc_commit(&empty[s]);  // the stage may be filled again once these mma have read it
         }
         tc_commit(&acc_full[acc]);  // arrives when everything issued so far is done
@@ -144,79 +151,53 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
       if (!wait_or_abort(&acc_full[acc], (j >> 1) & 1, failed)) break;
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
-      const uint32_t taddr = tmem + acc * TILE_N + ((uint32_t)(quarter * 32) << 16);
-      if (ep.glu) {
-        __nv_bfloat16* out = (__nv_bfloat16*)ep.out;
-        const __nv_bfloat16* bias = (const __nv_bfloat16*)ep.bias;
-        for (int c0 = 0; c0 < TILE_N / 2; c0 += 32) {
-          float g[32], u[32];
-          tmem_load_32(taddr + c0, g);
-          tmem_load_32(taddr + TILE_N / 2 + c0, u);
-          if (row < M) {
-            __nv_bfloat16* o = out + (size_t)row * ep.hidden + n0 + c0;
-            if (n0 + c0 + 32 <= ep.hidden && (ep.hidden % 8) == 0 && bias == nullptr) {
+      const uint32_t taddr = tmem + acc * MAX_TILE_N + ((uint32_t)(quarter * 32) << 16);
+      const __nv_bfloat16* bias = (const __nv_bfloat16*)ep.bias;
+      // 16 columns at a time (every lane loads: tensor-memory loads are warp-wide; only rows inside M store)
+      for (int c0 = 0; c0 < tile_n; c0 += 16) {
+        float v[16];
+        tmem_load_16(taddr + c0, v);
+        const int ncols = ep.glu ? ep.hidden : N, col0 = n0 + c0;
+        if (ep.glu) {
+          float u[16];
+          tmem_load_16(taddr + tile_n + c0, u);
 #pragma unroll
-              for (int jj = 0; jj < 32; jj += 8) {
-                uint32_t p[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  __nv_bfloat162 t = __floats2bfloat162_rn(activate(g[jj + 2 * q], ep.act) * u[jj + 2 * q],
-                                                           activate(g[jj + 2 * q + 1], ep.act) * u[jj + 2 * q + 1]);
-                  p[q] = *reinterpret_cast<uint32_t*>(&t);
-                }
-                *reinterpret_cast<uint4*>(o + jj) = make_uint4(p[0], p[1], p[2], p[3]);
-              }
-            } else {
-#pragma unroll
-              for (int jj = 0; jj < 32; ++jj) {
-                const int col = n0 + c0 + jj;
-                if (col < ep.hidden) {
-                  float gv = g[jj], uv = u[jj];
-                  if (bias) {
-                    gv += __bfloat162float(bias[col]);
-                    uv += __bfloat162float(bias[ep.hidden + col]);
-                  }
-                  o[jj] = __float2bfloat16_rn(activate(gv, ep.act) * uv);
-                }
-              }
+          for (int jj = 0; jj < 16; ++jj) {
+            float gv = v[jj], uv = u[jj];
+            if (bias && col0 + jj < ncols) {
+              gv += __bfloat162float(bias[col0 + jj]);
+              uv += __bfloat162float(bias[ep.hidden + col0 + jj]);
             }
+            v[jj] = activate(gv, ep.act) * uv;
           }
+        } else if (bias) {
+#pragma unroll
+          for (int jj = 0; jj < 16; ++jj)
+            if (col0 + jj < ncols) v[jj] += __bfloat162float(bias[col0 + jj]);
         }
-      } else {
-        const __nv_bfloat16* bias = (const __nv_bfloat16*)ep.bias;
-        for (int c0 = 0; c0 < TILE_N; c0 += 32) {
-          float v[32];
-          tmem_load_32(taddr + c0, v);
-          if (row < M) {
-            if (bias) {
+        if (row >= M) continue;
+        if (ep.out_f32) {
+          float* o = (float*)ep.out + (size_t)row * ncols + col0;
 #pragma unroll
-              for (int jj = 0; jj < 32; ++jj)
-                if (n0 + c0 + jj < N) v[jj] += __bfloat162float(bias[n0 + c0 + jj]);
-            }
-            if (ep.out_f32) {
-              float* o = (float*)ep.out + (size_t)row * N + n0 + c0;
+          for (int jj = 0; jj < 16; ++jj)
+            if (col0 + jj < ncols) o[jj] = v[jj];
+        } else {
+          __nv_bfloat16* o = (__nv_bfloat16*)ep.out + (size_t)row * ncols + col0;
+          if (col0 + 16 <= ncols && (ncols % 8) == 0) {
 #pragma unroll
-              for (int jj = 0; jj < 32; ++jj)
-                if (n0 + c0 + jj < N) o[jj] = v[jj];
-            } else {
-              __nv_bfloat16* o = (__nv_bfloat16*)ep.out + (size_t)row * N + n0 + c0;
-              if (n0 + c0 + 32 <= N && (N % 8) == 0) {
+            for (int jj = 0; jj < 16; jj += 8) {
+              uint32_t pk[4];
 #pragma unroll
-                for (int jj = 0; jj < 32; jj += 8) {
-                  uint32_t p[4];
-#pragma unroll
-                  for (int q = 0; q < 4; ++q) {
-                    __nv_bfloat162 t = __floats2bfloat162_rn(v[jj + 2 * q], v[jj + 2 * q + 1]);
-                    p[q] = *reinterpret_cast<uint32_t*>(&t);
-                  }
-                  *reinterpret_cast<uint4*>(o + jj) = make_uint4(p[0], p[1], p[2], p[3]);
-                }
-              } else {
-#pragma unroll
-                for (int jj = 0; jj < 32; ++jj)
-                  if (n0 + c0 + jj < N) o[jj] = __float2bfloat16_rn(v[jj]);
+              for (int q = 0; q < 4; ++q) {
+                __nv_bfloat162 t = __floats2bfloat162_rn(v[jj + 2 * q], v[jj + 2 * q + 1]);
+                pk[q] = *reinterpret_cast<uint32_t*>(&t);
               }
+              *reinterpret_cast<uint4*>(o + jj) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
+          } else {
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj)
+              if (col0 + jj < ncols) o[jj] = __float2bfloat16_rn(v[jj]);
           }
         }
       }
@@ -231,30 +212,64 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
   if (threadIdx.x == 0 && *failed && error_flag) atomicExch(error_flag, 4);
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem, 2 * TILE_N);
+    tmem_dealloc(tmem, 2 * MAX_TILE_N);
   }
 }
 
-int launch(const void* x, const void* w, int w_rows, const Epilogue& ep, int M, int N, int K, int* error_flag,
-           cudaStream_t stream) {
-  if (K <= 0 || K % 8) return fms_fail("gemm_tc: K %d must be a positive multiple of 8", K);
-  if (((uintptr_t)x | (uintptr_t)w) & 15) return fms_fail("gemm_tc: operands must be 16-byte aligned");
-  CUtensorMap map_a, map_b;
-  if (make_map(&map_a, x, M, K) || make_map(&map_b, w, w_rows, K)) return 1;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-    if (e != cudaSuccess) return fms_fail("gemm_tc: %zu bytes of shared memory refused: %s", SMEM_BYTES, cudaGetErrorString(e));
-    configured = true;
-  }
-  const int tile_n = ep.glu ? TILE_N / 2 : TILE_N;
-  const long tiles = (long)((N + tile_n - 1) / tile_n) * ((M + TILE_M - 1) / TILE_M);
+int multiprocessors() {
   static int sms = 0;
   if (sms == 0) {
     int device = 0;
     cudaGetDevice(&device);
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
   }
+  return sms;
+}
+
+// The tile width (accumulator columns) for a product with `cols` output columns a tile row: the one whose tiles
+// cost least in whole rounds of the multiprocessors.  A tile's cost is its width plus a constant for what does not
+// shrink with it (the x box, the barriers of a step).  step: 16 (GLU: 32, so that a half is a multiple of 16).
+int choose_tile_n(int M, int cols, bool glu) {
+  static int forced = -1;
+  if (forced < 0) {
+    const char* e = getenv("FMS_B200_TC_TILE_N");
+    forced = e ? atoi(e) : 0;
+  }
+  const int step = glu ? 32 : 16;
+  if (forced >= step && forced <= MAX_TILE_N && forced % step == 0) return forced;
+  const int sms = multiprocessors(), tiles_m = (M + TILE_M - 1) / TILE_M;
+  long best_cost = -1;
+  int best = MAX_TILE_N;
+  for (int tn = MAX_TILE_N; tn >= 64; tn -= step) {
+    const int out = glu ? tn / 2 : tn;
+    const long tiles = (long)tiles_m * ((cols + out - 1) / out);
+    const long cost = ((tiles + sms - 1) / sms) * (tn + 48);
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = tn;
+    }
+  }
+  return best;
+}
+
+int launch(const void* x, const void* w, int w_rows, Epilogue ep, int M, int N, int K, int* error_flag,
+           cudaStream_t stream) {
+  if (K <= 0 || K % 8) return fms_fail("gemm_tc: K %d must be a positive multiple of 8", K);
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return fms_fail("gemm_tc: operands must be 16-byte aligned");
+  ep.tile_n = choose_tile_n(M, N, ep.glu != 0);
+  const int stage_bytes = A_BYTES + ep.tile_n * TILE_K * 2;
+  ep.stages = RING_BYTES / stage_bytes < MAX_STAGES ? RING_BYTES / stage_bytes : MAX_STAGES;
+  CUtensorMap map_a, map_b;
+  if (make_map(&map_a, x, M, K) || make_map(&map_b, w, w_rows, K, ep.glu ? ep.tile_n / 2 : ep.tile_n)) return 1;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (e != cudaSuccess) return fms_fail("gemm_tc: %zu bytes of shared memory refused: %s", SMEM_BYTES, cudaGetErrorString(e));
+    configured = true;
+  }
+  const int out = ep.glu ? ep.tile_n / 2 : ep.tile_n;
+  const long tiles = (long)((N + out - 1) / out) * ((M + TILE_M - 1) / TILE_M);
+  const int sms = multiprocessors();
   const int blocks = (int)(tiles < sms ? tiles : sms);  // one persistent block per multiprocessor
   fms_launch(gemm_tc_kernel, dim3(blocks), dim3(THREADS), SMEM_BYTES, stream, map_a, map_b, ep, M, N, K, error_flag);
   return fms_launch_status("gemm_tc");
@@ -266,7 +281,7 @@ FMS_API int fms_gemm_bf16_tc(const void* x, const void* w, const void* bias, voi
                              int* error_flag, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (out_dtype != FMS_F32 && out_dtype != FMS_BF16) return fms_fail("gemm_tc: out dtype %d", out_dtype);
-  Epilogue ep{y, bias, out_dtype == FMS_F32 ? 1 : 0, 0, 0, 0};
+  Epilogue ep{y, bias, out_dtype == FMS_F32 ? 1 : 0, 0, 0, 0, 0, 0};
   return launch(x, w, N, ep, M, N, K, error_flag, stream);
 }
 
@@ -275,6 +290,6 @@ FMS_API int fms_glu_bf16_tc(const void* x, const void* w, const void* bias, void
                             int* error_flag, cudaStream_t stream) {
   if (M <= 0 || hidden <= 0) return 0;
   if (act < 0 || act > 3) return fms_fail("glu_tc: activation %d", act);
-  Epilogue ep{y, bias, 0, 1, hidden, act};
+  Epilogue ep{y, bias, 0, 1, hidden, act, 0, 0};
   return launch(x, w, 2 * hidden, ep, M, hidden, K, error_flag, stream);
 }
