@@ -54,6 +54,60 @@ struct Epilogue {
   int stages;
 };
 
+// One thread's row of a tile's accumulator (tensor-memory address `taddr`, lane = row), `tile_n` output columns
+// from column n0 on: bias, the GLU product, conversion, store.  Every lane of the warp must call it.
+__device__ __forceinline__ void store_rows(const Epilogue& ep, uint32_t taddr, int row, int n0, int tile_n, int M, int N) {
+  const __nv_bfloat16* bias = (const __nv_bfloat16*)ep.bias;
+  // 16 columns at a time (every lane loads: tensor-memory loads are warp-wide; only rows inside M store)
+  for (int c0 = 0; c0 < tile_n; c0 += 16) {
+    float v[16];
+    tmem_load_16(taddr + c0, v);
+    const int ncols = ep.glu ? ep.hidden : N, col0 = n0 + c0;
+    if (ep.glu) {
+      float u[16];
+      tmem_load_16(taddr + tile_n + c0, u);
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj) {
+        float gv = v[jj], uv = u[jj];
+        if (bias && col0 + jj < ncols) {
+          gv += __bfloat162float(bias[col0 + jj]);
+          uv += __bfloat162float(bias[ep.hidden + col0 + jj]);
+        }
+        v[jj] = activate(gv, ep.act) * uv;
+      }
+    } else if (bias) {
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj)
+        if (col0 + jj < ncols) v[jj] += __bfloat162float(bias[col0 + jj]);
+    }
+    if (row >= M) continue;
+    if (ep.out_f32) {
+      float* o = (float*)ep.out + (size_t)row * ncols + col0;
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj)
+        if (col0 + jj < ncols) o[jj] = v[jj];
+    } else {
+      __nv_bfloat16* o = (__nv_bfloat16*)ep.out + (size_t)row * ncols + col0;
+      if (col0 + 16 <= ncols && (ncols % 8) == 0) {
+#pragma unroll
+        for (int jj = 0; jj < 16; jj += 8) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            __nv_bfloat162 t = __floats2bfloat162_rn(v[jj + 2 * q], v[jj + 2 * q + 1]);
+            pk[q] = *reinterpret_cast<uint32_t*>(&t);
+          }
+          *reinterpret_cast<uint4*>(o + jj) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+      } else {
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj)
+          if (col0 + jj < ncols) o[jj] = __float2bfloat16_rn(v[jj]);
+      }
+    }
+  }
+}
+
 // Persistent: block b computes tiles b, b + gridDim.x, ...; tiles are numbered with the row index fastest, so
 // that the blocks running at the same time share few tiles of w.  The accumulator is double-buffered in tensor
 // memory (2 x 256 columns, of which TN are used): the epilogue of a tile runs while the mma of the block's next
@@ -152,55 +206,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t taddr = tmem + acc * MAX_TILE_N + ((uint32_t)(quarter * 32) << 16);
-      const __nv_bfloat16* bias = (const __nv_bfloat16*)ep.bias;
-      // 16 columns at a time (every lane loads: tensor-memory loads are warp-wide; only rows inside M store)
-      for (int c0 = 0; c0 < tile_n; c0 += 16) {
-        float v[16];
-        tmem_load_16(taddr + c0, v);
-        const int ncols = ep.glu ? ep.hidden : N, col0 = n0 + c0;
-        if (ep.glu) {
-          float u[16];
-          tmem_load_16(taddr + tile_n + c0, u);
-#pragma unroll
-          for (int jj = 0; jj < 16; ++jj) {
-            float gv = v[jj], uv = u[jj];
-            if (bias && col0 + jj < ncols) {
-              gv += __bfloat162float(bias[col0 + jj]);
-              uv += __bfloat162float(bias[ep.hidden + col0 + jj]);
-            }
-            v[jj] = activate(gv, ep.act) * uv;
-          }
-        } else if (bias) {
-#pragma unroll
-          for (int jj = 0; jj < 16; ++jj)
-            if (col0 + jj < ncols) v[jj] += __bfloat162float(bias[col0 + jj]);
-        }
-        if (row >= M) continue;
-        if (ep.out_f32) {
-          float* o = (float*)ep.out + (size_t)row * ncols + col0;
-#pragma unroll
-          for (int jj = 0; jj < 16; ++jj)
-            if (col0 + jj < ncols) o[jj] = v[jj];
-        } else {
-          __nv_bfloat16* o = (__nv_bfloat16*)ep.out + (size_t)row * ncols + col0;
-          if (col0 + 16 <= ncols && (ncols % 8) == 0) {
-#pragma unroll
-            for (int jj = 0; jj < 16; jj += 8) {
-              uint32_t pk[4];
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                __nv_bfloat162 t = __floats2bfloat162_rn(v[jj + 2 * q], v[jj + 2 * q + 1]);
-                pk[q] = *reinterpret_cast<uint32_t*>(&t);
-              }
-              *reinterpret_cast<uint4*>(o + jj) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            }
-          } else {
-#pragma unroll
-            for (int jj = 0; jj < 16; ++jj)
-              if (col0 + jj < ncols) o[jj] = __float2bfloat16_rn(v[jj]);
-          }
-        }
-      }
+      store_rows(ep, taddr, row, n0, tile_n, M, N);
       // this warp has read its part of the buffer: give it back to the mma warp
       tc_fence_before();
       __syncwarp();
@@ -216,6 +222,126 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
   }
 }
 
+// The same product by pairs of thread blocks (a cluster of two, tcgen05 cta_group::2): a pair owns a tile of 256
+// rows of x by TN rows of w.  Each block of the pair brings its own 128 rows of x and its half of the rows of w
+// (GLU: block 0 the gate rows, block 1 the up rows) into its own shared memory, so a multiprocessor takes in a
+// third less per flop than with tiles of 128 x 256 of its own, and that intake is what limits the kernel.  Block 0
+// issues the mma for both (256 x TN x 16) and counts the arriving bytes of both on its "full" barriers; the
+// commits go to the "empty" and "accumulator ready" barriers of both blocks; each block's epilogue reads its own
+// tensor memory (its 128 rows) and gives the accumulator back on block 0's barrier.  No block leaves before its
+// partner has (cluster barrier at the end).
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+    gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, Epilogue ep,
+                        int M, int N, int K, int* __restrict__ error_flag) {
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
+  const int b_rows = ep.tile_n / 2;  // rows of w that this block loads
+  const int b_bytes = b_rows * TILE_K * 2, stage_bytes = A_BYTES + b_bytes, stages = ep.stages;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)RING_BYTES);
+  uint64_t* empty = full + MAX_STAGES;
+  uint64_t* acc_full = empty + MAX_STAGES;   // [2]
+  uint64_t* acc_empty = acc_full + 2;        // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  __shared__ int failed_flag;
+  volatile int* failed = &failed_flag;
+
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const bool leader = rank == 0;
+  const int tile_n = ep.glu ? ep.tile_n / 2 : ep.tile_n;  // output columns of a tile
+  const int tiles_m = (M + 2 * TILE_M - 1) / (2 * TILE_M), tiles_n = (N + tile_n - 1) / tile_n;
+  const int n_tiles = tiles_m * tiles_n;
+  const int k_steps = (K + TILE_K - 1) / TILE_K;
+  const int pair = blockIdx.x / 2, pairs = gridDim.x / 2;
+
+  if (threadIdx.x == 0) {
+    failed_flag = 0;
+    for (int s = 0; s < MAX_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 8);  // one arrival per epilogue warp of either block (used in block 0)
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc_pair(tmem_slot, 2 * MAX_TILE_N);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the partner's barriers exist before anything is sent to them
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  pdl_wait();
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int it = 0;
+      for (int tile = pair; tile < n_tiles && !*failed; tile += pairs) {
+        const int m0 = (tile % tiles_m) * 2 * TILE_M + (int)rank * TILE_M, n0 = (tile / tiles_m) * tile_n;
+        const int w_row = ep.glu ? (leader ? n0 : ep.hidden + n0) : n0 + (int)rank * b_rows;
+        for (int i = 0; i < k_steps; ++i, ++it) {
+          const int s = it % stages;
+          if (!wait_or_abort(&empty[s], ((it / stages) & 1) ^ 1, failed)) break;
+          unsigned char* a = smem + (size_t)s * stage_bytes;
+          if (leader) mbar_arrive_expect_tx(&full[s], 2 * stage_bytes);  // the bytes of both blocks
+          tma_load_2d_pair(a, &map_a, i * TILE_K, m0, &full[s]);
+          tma_load_2d_pair(a + A_BYTES, &map_b, i * TILE_K, w_row, &full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (leader && elect_one()) {
+      const uint32_t idesc = umma_idesc(2 * TILE_M, ep.tile_n);
+      int it = 0, j = 0;
+      for (int tile = pair; tile < n_tiles && !*failed; tile += pairs, ++j) {
+        const int acc = j & 1;
+        if (!wait_or_abort(&acc_empty[acc], ((j >> 1) & 1) ^ 1, failed)) break;  // both epilogues have read this buffer
+        tc_fence_after();
+        const uint32_t d = tmem + acc * MAX_TILE_N;
+        for (int i = 0; i < k_steps; ++i, ++it) {
+          const int s = it % stages;
+          if (!wait_or_abort(&full[s], (it / stages) & 1, failed)) break;
+          tc_fence_after();
+          const uint32_t a = smem_u32(smem + (size_t)s * stage_bytes), b = a + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < TILE_K / UMMA_K; ++kk)
+            umma_pair(d, umma_desc(a + kk * UMMA_K * 2), umma_desc(b + kk * UMMA_K * 2), idesc, i > 0 || kk > 0);
+          tc_commit_pair(&empty[s]);
+        }
+        tc_commit_pair(&acc_full[acc]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    int j = 0;
+    for (int tile = pair; tile < n_tiles; tile += pairs, ++j) {
+      const int acc = j & 1;
+      const int m0 = (tile % tiles_m) * 2 * TILE_M + (int)rank * TILE_M, n0 = (tile / tiles_m) * tile_n;
+      if (!wait_or_abort(&acc_full[acc], (j >> 1) & 1, failed)) break;
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t taddr = tmem + acc * MAX_TILE_N + ((uint32_t)(quarter * 32) << 16);
+      store_rows(ep, taddr, row, n0, tile_n, M, N);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (leader) mbar_arrive(&acc_empty[acc]);
+        else mbar_arrive_remote(&acc_empty[acc], 0);
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  cluster_sync_all();  // nothing is sent to a block that has left
+  if (threadIdx.x == 0 && *failed && error_flag) atomicExch(error_flag, 4);
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem, 2 * MAX_TILE_N);
+  }
+}
+
 int multiprocessors() {
   static int sms = 0;
   if (sms == 0) {
@@ -227,23 +353,26 @@ int multiprocessors() {
 }
 
 // The tile width (accumulator columns) for a product with `cols` output columns a tile row: the one whose tiles
-// cost least in whole rounds of the multiprocessors.  A tile's cost is its width plus a constant for what does not
-// shrink with it (the x box, the barriers of a step).  step: 16 (GLU: 32, so that a half is a multiple of 16).
-int choose_tile_n(int M, int cols, bool glu) {
+// cost least in whole rounds of the `units` that work at the same time (multiprocessors, or pairs of them).
+// A pair's tile costs, measured, 1.0 at 256 columns and 0.56 + 0.0014 TN below (the tensor cores limit the widest
+// tile, what a multiprocessor takes in per step the others); a single block's tile costs as its intake per step
+// of 64 k: 128 rows of x, TN rows of w and a constant.  step: 16 (GLU and pairs: 32, so that a half is a multiple
+// of 16).
+int choose_tile_n(int tiles_m, int cols, bool glu, bool pair, int units) {
   static int forced = -1;
   if (forced < 0) {
     const char* e = getenv("FMS_B200_TC_TILE_N");
     forced = e ? atoi(e) : 0;
   }
-  const int step = glu ? 32 : 16;
-  if (forced >= step && forced <= MAX_TILE_N && forced % step == 0) return forced;
-  const int sms = multiprocessors(), tiles_m = (M + TILE_M - 1) / TILE_M;
+  const int step = (glu || pair) ? 32 : 16;
+  if (forced >= 64 && forced <= MAX_TILE_N && forced % step == 0) return forced;
   long best_cost = -1;
   int best = MAX_TILE_N;
   for (int tn = MAX_TILE_N; tn >= 64; tn -= step) {
     const int out = glu ? tn / 2 : tn;
     const long tiles = (long)tiles_m * ((cols + out - 1) / out);
-    const long cost = ((tiles + sms - 1) / sms) * (tn + 48);
+    const long tile_cost = pair ? (tn == MAX_TILE_N ? 10000 : 5600 + 14 * tn) : (TILE_M + tn + 64);
+    const long cost = ((tiles + units - 1) / units) * tile_cost;
     if (best_cost < 0 || cost < best_cost) {
       best_cost = cost;
       best = tn;
@@ -252,26 +381,44 @@ int choose_tile_n(int M, int cols, bool glu) {
   return best;
 }
 
+bool pairs_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("FMS_B200_TC_PAIR");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
 int launch(const void* x, const void* w, int w_rows, Epilogue ep, int M, int N, int K, int* error_flag,
            cudaStream_t stream) {
   if (K <= 0 || K % 8) return fms_fail("gemm_tc: K %d must be a positive multiple of 8", K);
   if (((uintptr_t)x | (uintptr_t)w) & 15) return fms_fail("gemm_tc: operands must be 16-byte aligned");
-  ep.tile_n = choose_tile_n(M, N, ep.glu != 0);
-  const int stage_bytes = A_BYTES + ep.tile_n * TILE_K * 2;
+  const int sms = multiprocessors();
+  const bool pair = pairs_enabled() && M > TILE_M && sms >= 2;
+  const int tiles_m = pair ? (M + 2 * TILE_M - 1) / (2 * TILE_M) : (M + TILE_M - 1) / TILE_M;
+  const int units = pair ? sms / 2 : sms;
+  ep.tile_n = choose_tile_n(tiles_m, N, ep.glu != 0, pair, units);
+  const int b_rows = pair ? ep.tile_n / 2 : ep.tile_n;  // rows of w in a block's stage
+  const int stage_bytes = A_BYTES + b_rows * TILE_K * 2;
   ep.stages = RING_BYTES / stage_bytes < MAX_STAGES ? RING_BYTES / stage_bytes : MAX_STAGES;
   CUtensorMap map_a, map_b;
-  if (make_map(&map_a, x, M, K) || make_map(&map_b, w, w_rows, K, ep.glu ? ep.tile_n / 2 : ep.tile_n)) return 1;
+  if (make_map(&map_a, x, M, K) || make_map(&map_b, w, w_rows, K, (ep.glu || pair) ? ep.tile_n / 2 : ep.tile_n)) return 1;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) return fms_fail("gemm_tc: %zu bytes of shared memory refused: %s", SMEM_BYTES, cudaGetErrorString(e));
     configured = true;
   }
   const int out = ep.glu ? ep.tile_n / 2 : ep.tile_n;
-  const long tiles = (long)((N + out - 1) / out) * ((M + TILE_M - 1) / TILE_M);
-  const int sms = multiprocessors();
-  const int blocks = (int)(tiles < sms ? tiles : sms);  // one persistent block per multiprocessor
-  fms_launch(gemm_tc_kernel, dim3(blocks), dim3(THREADS), SMEM_BYTES, stream, map_a, map_b, ep, M, N, K, error_flag);
+  const long tiles = (long)((N + out - 1) / out) * tiles_m;
+  const int busy = (int)(tiles < units ? tiles : units);  // one persistent block (or pair) per multiprocessor (pair)
+  if (pair)
+    fms_launch(gemm_tc_pair_kernel, dim3(2 * busy), dim3(THREADS), SMEM_BYTES, stream, map_a, map_b, ep, M, N, K, error_flag);
+  else
+    fms_launch(gemm_tc_kernel, dim3(busy), dim3(THREADS), SMEM_BYTES, stream, map_a, map_b, ep, M, N, K, error_flag);
   return fms_launch_status("gemm_tc");
 }
 }  // namespace

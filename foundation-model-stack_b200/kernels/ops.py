@@ -171,7 +171,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return torch.nn.functional.linear(x, weight, b)
 
 
-TENSOR_CORE_ROWS = 256  # rows from which the tcgen05 kernel is used instead of the library product
+# rows from which the tcgen05 kernel is used instead of the library product (measured: at par or ahead from there on)
+TENSOR_CORE_ROWS = int(os.environ.get("FMS_B200_TC_ROWS", "1024"))
 USE_TENSOR_CORE_GEMM = os.environ.get("FMS_B200_TC_GEMM", "1") != "0"
 
 

@@ -256,7 +256,7 @@ def test_trace_run_program(tiny_folders, oracles, tmp_path, dtype):
 
 def test_head_size_128_model_bfloat16_against_float32(tmp_path):
     """A model with the head size, group size and widths (in small) of the benchmark's: prompts long enough for
-    the tcgen05 product (256 rows and more), decode through the weight-streaming product and the CUDA graph.
+    the tcgen05 product (1,024 rows and more in one step), decode through the weight-streaming product and the CUDA graph.
     The float32 path — itself checked against the plain implementation on the tiny models — is the yardstick."""
     from fms_b200.models import get_model
     from fms_b200.models.llama import LLaMA, LLaMAConfig
@@ -266,7 +266,7 @@ def test_head_size_128_model_bfloat16_against_float32(tmp_path):
                              max_expected_seq_len=2048, rope_theta=500000.0))
     folder = write_random_model(str(tmp_path / "m"), arch.config_json(), arch.checkpoint_layout(), seed=5)
     g = torch.Generator().manual_seed(70)
-    reqs = [torch.randint(0, 4099, (k,), generator=g).tolist() for k in (700, 300, 41)]
+    reqs = [torch.randint(0, 4099, (k,), generator=g).tolist() for k in (900, 300, 41)]
     out = {}
     for dtype in ("fp32", "bf16"):
         engine = get_model("hf_pretrained", model_path=folder, device_type="cuda", data_type=dtype).new_engine(2048)
