@@ -139,10 +139,12 @@ def test_gated_linear_few_rows(ops, m, hidden, k, act):
                                P.gated_activation(P.linear(x2, w, None, torch.float32), act), atol=3e-2, rtol=3e-2)
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 512, 256), (129, 331, 200), (1000, 777, 1000), (2048, 1024, 4096)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 512, 256), (129, 331, 200), (1000, 777, 1000), (2048, 1024, 4096),
+                                   (257, 4096 + 32, 72), (1024, 96, 4096), (640, 6144, 520), (100, 700, 136)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_linear_bfloat16_tensor_core(ops, m, n, k, out_dtype):
-    """The tcgen05 kernel of prefill steps: sizes that are no multiples of its 128 x 256 x 64 tiles."""
+    """The tcgen05 kernels of prefill steps (a pair of blocks per tile of 256 rows; one block per tile up to 128
+    rows): sizes that are no multiples of the tiles, more and fewer tiles than multiprocessors."""
     g = torch.Generator().manual_seed(60 + m)
     x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
     w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).cuda()
@@ -155,15 +157,17 @@ def test_linear_bfloat16_tensor_core(ops, m, n, k, out_dtype):
         torch.testing.assert_close(got.double(), want, **t)
 
 
-@pytest.mark.parametrize("m,hidden,k", [(128, 128, 64), (300, 328, 240), (513, 1000, 96)])
+@pytest.mark.parametrize("m,hidden,k", [(128, 128, 64), (300, 328, 240), (513, 1000, 96), (1030, 14336, 264), (90, 331, 64)])
 def test_gated_linear_tensor_core(ops, m, hidden, k):
     g = torch.Generator().manual_seed(70 + m)
     x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
     w = (torch.randn(2 * hidden, k, generator=g) * 0.1).to(torch.bfloat16).cuda()
-    got = ops.gated_linear_tensor_core(x, w, None, 0)
-    ops.check_error_flag("cuda")
-    want = P.gated_activation(P.linear(x, w, None, torch.float32), 0)
-    torch.testing.assert_close(got.float(), want, atol=3e-2, rtol=2e-2)
+    b = (torch.randn(2 * hidden, generator=g) * 0.1).to(torch.bfloat16).cuda()
+    for bias in (None, b):
+        got = ops.gated_linear_tensor_core(x, w, bias, 0)
+        ops.check_error_flag("cuda")
+        want = P.gated_activation(P.linear(x, w, bias, torch.float32), 0)
+        torch.testing.assert_close(got.float(), want, atol=3e-2, rtol=2e-2)
 
 
 def test_linear_float32_matrix_in_a_bfloat16_model(ops):
