@@ -302,13 +302,17 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
   dst[2 * i + 1] = from_f32<T>(x1);
 }
 
-// bfloat16, many tokens: one block per token, a thread per 16-byte piece (8 values = 4 pairs) of a head
+// bfloat16, many tokens: one block per token, a thread per 16-byte piece (8 values = 4 pairs) of a head.  The
+// angle of a pair is the same for every head of the token: its sine and cosine are taken once, into shared memory.
+constexpr int ROPE_VEC_MAX_PAIRS = 1024;  // head_dim / 2 that the table in shared memory holds
+
 __global__ void rope_store_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
                                       const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                       const int* __restrict__ token_seq, const int* __restrict__ slots,
                                       __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
                                       const int* __restrict__ table, int table_stride, int block_tokens, int nheads,
                                       int kvheads, int head_dim, int write_cache, int* __restrict__ error_flag) {
+  extern __shared__ float2 sincos_of_pair[];  // [head_dim / 2]: (sin, cos)
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -321,6 +325,14 @@ __global__ void rope_store_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __n
     blk = table[(size_t)slots[token_seq[t]] * table_stride + pos / block_tokens];
     if (blk < 0 && threadIdx.x == 0 && error_flag) atomicExch(error_flag, 2);
   }
+  if (inv_freq != nullptr) {
+    for (int i = threadIdx.x; i < head_dim / 2; i += blockDim.x) {
+      float sn, cs;
+      sincosf((float)pos * inv_freq[i], &sn, &cs);
+      sincos_of_pair[i] = make_float2(sn, cs);
+    }
+    __syncthreads();
+  }
   for (int i = threadIdx.x; i < total; i += blockDim.x) {
     const int head = i / pieces, piece = i - head * pieces;
     const uint4 v = *reinterpret_cast<const uint4*>(qkv + (size_t)t * width + (size_t)head * head_dim + piece * 8);
@@ -330,9 +342,8 @@ __global__ void rope_store_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __n
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const float x0 = __uint_as_float(w[k] << 16), x1 = __uint_as_float(w[k] & 0xffff0000u);
-        float sn, cs;
-        sincosf((float)pos * inv_freq[piece * 4 + k], &sn, &cs);
-        __nv_bfloat162 r = __floats2bfloat162_rn(cs * x0 - sn * x1, sn * x0 + cs * x1);
+        const float2 sc = sincos_of_pair[piece * 4 + k];
+        __nv_bfloat162 r = __floats2bfloat162_rn(sc.y * x0 - sc.x * x1, sc.x * x0 + sc.y * x1);
         w[k] = *reinterpret_cast<uint32_t*>(&r);
       }
     }
@@ -354,10 +365,11 @@ FMS_API int fms_rope_store(const void* qkv, int dtype, void* q_out, const float*
                            int write_cache, int* error_flag, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (head_dim <= 0 || head_dim % 2 || head_dim > 2048) return fms_fail("rope_store: head_dim %d", head_dim);
-  if (dtype == FMS_BF16 && head_dim % 8 == 0 && n_tokens >= 64) {
+  if (dtype == FMS_BF16 && head_dim % 8 == 0 && n_tokens >= 64 && head_dim / 2 <= ROPE_VEC_MAX_PAIRS) {
     const int total = (nheads + 2 * kvheads) * (head_dim / 8);
     const int threads = total >= 256 ? 256 : ((total + 31) / 32) * 32;
-    fms_launch(rope_store_vec_kernel, dim3(n_tokens), dim3(threads), 0, stream, (const __nv_bfloat16*)qkv,
+    fms_launch(rope_store_vec_kernel, dim3(n_tokens), dim3(threads), (size_t)(head_dim / 2) * sizeof(float2), stream,
+               (const __nv_bfloat16*)qkv,
                (__nv_bfloat16*)q_out, inv_freq, positions, token_seq, slots, (__nv_bfloat16*)k_cache,
                (__nv_bfloat16*)v_cache, table, table_stride, block_tokens, nheads, kvheads, head_dim, write_cache,
                error_flag);
