@@ -302,6 +302,63 @@ def test_attention_finds_one_far_key(ops, dtype):
         torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
 
 
+@pytest.mark.parametrize("hd,nheads,kvheads", [(128, 8, 2), (64, 4, 4), (48, 4, 2)])
+def test_prefill_attention_with_keys_that_outgrow_the_running_maximum(ops, hd, nheads, kvheads):
+    """Random scores are all alike, so a kernel's rescaling of what it has accumulated is never exercised by them.
+    Here three cached keys are copies of one query row, scaled 2, 4 and 8 times: as the key blocks go by, that
+    row's maximum grows in big steps (far past the 2^8 by which the tcgen05 kernel lets it lag), the last copy takes
+    nearly all the weight, and its value must come out.  Head sizes 128 and 64 take the tcgen05 kernel, 48 mma.sync."""
+    dtype = torch.bfloat16
+    cache, view, batch = make_cache_case(dtype, nheads, kvheads, hd, [450], [70], 12)
+    table = cache.groups[0].table_host
+    slot = int(batch.slots[0])
+    g = torch.Generator().manual_seed(13)
+    qkv = torch.randn(70, (nheads + 2 * kvheads) * hd, generator=g).to(dtype).cuda()
+    q = ops.rope_store(qkv, None, batch, view, nheads, kvheads, hd)
+    row, head = 37, nheads - 1                       # a query in the middle of a tile, the last head of its group
+    kvh = head // (nheads // kvheads)
+    qv = q[row, head * hd:(head + 1) * hd].float()
+    marker = torch.full((hd,), 3.0).to(dtype).cuda()
+    for far, factor in ((10, 2.0), (100, 4.0), (300, 8.0)):
+        blk = int(table[slot, far // 64])
+        view.keys[blk, kvh, far % 64] = (qv * factor).to(dtype)
+        view.values[blk, kvh, far % 64] = marker * (factor / 8.0)
+    scale = 1.0 / math.sqrt(hd)
+    got = ops.attention(q, batch, view, nheads, kvheads, hd, scale, 0)
+    ops.check_error_flag("cuda")
+    want = P.attention(q, batch, view, nheads, kvheads, hd, scale, 0)
+    assert not torch.isnan(got).any()
+    torch.testing.assert_close(got[row, head * hd:(head + 1) * hd].float(), marker.float(), atol=8e-2, rtol=0)
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("n_seqs,kvheads", [(70, 8), (30, 8), (3, 2)])
+def test_decode_attention_at_every_batch_size(ops, n_seqs, kvheads):
+    """Decode attention picks the warps per block by the number of (sequence, kv head) pairs: one warp that walks
+    four key blocks with a running maximum of its own (many pairs), two, or four with a block each (few).  Every
+    variant against the plain implementation, with one key in the last block of a long sequence made large so that
+    the running maximum jumps late."""
+    dtype, hd = torch.bfloat16, 64
+    nheads = kvheads * 4
+    g = torch.Generator().manual_seed(14)
+    lens = [int(v) for v in torch.randint(1, 520, (n_seqs,), generator=g)]
+    lens[0] = 519
+    cache, view, batch = make_cache_case(dtype, nheads, kvheads, hd, lens, [1] * n_seqs, 15, poison=False)
+    qkv = torch.randn(n_seqs, (nheads + 2 * kvheads) * hd, generator=g).to(dtype).cuda()
+    q = ops.rope_store(qkv, None, batch, view, nheads, kvheads, hd)
+    table = cache.groups[0].table_host
+    slot, far = int(batch.slots[0]), 500
+    blk = int(table[slot, far // 64])
+    view.keys[blk, 1, far % 64] = (q[0, 5 * hd:6 * hd].float() * 6).to(dtype)  # head 5 uses kv head 1
+    view.values[blk, 1, far % 64] = torch.full((hd,), 2.0).to(dtype).cuda()
+    scale = 1.0 / math.sqrt(hd)
+    got = ops.attention(q, batch, view, nheads, kvheads, hd, scale, 0)
+    want = P.attention(q, batch, view, nheads, kvheads, hd, scale, 0)
+    assert not torch.isnan(got).any()
+    torch.testing.assert_close(got[0, 5 * hd:6 * hd].float(), torch.full((hd,), 2.0).cuda(), atol=5e-2, rtol=0)
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+
+
 def test_attention_refuses_other_head_sizes():
     from fms_b200.kernels.build import KernelBuildError, _spec
 
