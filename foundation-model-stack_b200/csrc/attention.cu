@@ -402,8 +402,9 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
     // the early L2 hints pay only while the GPU is not full of key and value traffic anyway
     fms_launch(kernel, dim3(n_seqs, a.kvheads * chunks, n_splits), dim3(nw * 32), smem, stream, a, part_o, part_ml,
                n_splits, nw == 4 ? pool_blocks : 0);
-    fms_launch(attn_combine_kernel<__nv_bfloat16>, dim3(n_seqs, a.nheads), dim3(HD >= 128 ? 128 : 64), 0, stream, a,
-               (const float*)part_o, (const float*)part_ml, n_splits);
+    if (n_splits > 1)  // with one split the kernel above has written the result itself
+      fms_launch(attn_combine_kernel<__nv_bfloat16>, dim3(n_seqs, a.nheads), dim3(HD >= 128 ? 128 : 64), 0, stream, a,
+                 (const float*)part_o, (const float*)part_ml, n_splits);
   } else {
     return fms_fail("%s: unsupported dtype code %d", what, dtype);
   }

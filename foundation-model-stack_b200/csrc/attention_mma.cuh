@@ -307,6 +307,11 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
       lsum += wm[2 * r + 1] * f;
     }
     const int head = kvh * group + g0 + r;
+    if (n_splits == 1) {  // nothing to merge with: this is the result (no second kernel is launched)
+      __nv_bfloat16* out = (__nv_bfloat16*)a.out + (size_t)a.first_row[seq] * a.nheads * HD + (size_t)head * HD;
+      out[d] = __float2bfloat16_rn(lsum > 0.f ? sum / lsum : 0.f);
+      continue;
+    }
     const size_t at = ((size_t)seq * a.nheads + head) * n_splits + split;
     part_o[at * HD + d] = sum;
     if (d == 0) {

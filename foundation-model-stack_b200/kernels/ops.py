@@ -38,9 +38,8 @@ _SIGNATURES = {
     "fms_attention_decode": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _F, _I, _I, _P],
 }
 _functions = {}
-# kernels launched through this module since import (a decode-attention call launches two)
+# kernels launched through this module since import (a decode-attention call over several splits launches two)
 launches = 0
-_KERNELS_PER_CALL = {"fms_attention_decode": 2}
 
 
 class KernelError(RuntimeError):
@@ -62,7 +61,7 @@ def _fn(library: str, name: str):
 def _call(library: str, name: str, *args):
     global launches
     f, lib = _fn(library, name)
-    launches += _KERNELS_PER_CALL.get(name, 1)
+    launches += 1
     rc = f(*args)
     if rc != 0:
         raise KernelError(f"{name}: {lib.fms_last_error().decode(errors='replace')}")
@@ -281,6 +280,9 @@ def attention(q: torch.Tensor, batch, view, nheads: int, kvheads: int, head_dim:
         part_ml = torch.empty((batch.n_seqs, nheads, n_splits, 2), dtype=torch.float32, device=q.device)
         _call(lib, "fms_attention_decode", *common, batch.n_seqs, n_splits, _ptr(part_o), _ptr(part_ml), nheads,
               kvheads, head_dim, float(scale), int(window), view.keys.shape[0], _stream())
+        if n_splits > 1 or q.dtype == torch.float32:
+            global launches
+            launches += 1  # the kernel that merges the splits
     else:
         tiles = batch.query_tiles(tile_rows)
         _call(lib, "fms_attention_prefill", *common, _ptr(tiles), tiles.shape[0], nheads, kvheads, head_dim,

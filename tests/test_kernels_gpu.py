@@ -261,6 +261,9 @@ ATTN_CASES = [
     (4, 4, 64, [64, 0], [130, 1], 0),               # prefill, head size 64, one query head a kv head
     (6, 2, 64, [10], [300], 50),                    # prefill, head size 64, window
     (3, 1, 128, [129], [64], 0),                    # three query heads a kv head: 42 positions a block, two rows idle
+    (4, 2, 64, [500, 70], [100, 3], 50),            # prefill behind a window whose earlier blocks were given back
+    (8, 2, 128, [300], [40], 64),                   # the same at head size 128
+    (8, 2, 128, [300, 200], [1, 1], 64),            # decode behind a window
 ]
 
 
