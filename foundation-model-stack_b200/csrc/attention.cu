@@ -1,6 +1,8 @@
 // Grouped-query causal softmax attention over the block cache, for one head size (HEAD_DIM, given at
-// compile time: the library is built once per head size a model needs), float32 and bfloat16 storage,
-// all arithmetic in float32 on the CUDA cores.  (fms/modules/attention.py:215-294 is the formula.)
+// compile time: the library is built once per head size a model needs).  (fms/modules/attention.py:215-294 is
+// the formula.)  This file holds the float32 kernels (all arithmetic in float32 on the CUDA cores), the merge of
+// decode splits and the entry points; the bfloat16 kernels are in attention_mma.cuh (mma.sync: prefill for any
+// head size, decode) and attention_tc.cuh (tcgen05: prefill for head sizes 64 and 128).
 //
 //   prefill:  any number of new tokens per sequence; the query at position p sees cached positions
 //             max(0, p - window + 1)..p.  Keys and values of the new tokens are already in the cache.

@@ -4,8 +4,10 @@ Tensors are torch tensors on a CUDA device (torch is used for memory and for the
 product only); every function launches on torch's current stream.  There is no CPU implementation and
 no fallback: a tensor on another device, a missing compiler or a failed build raises.
 
-Matrix products: float32 runs ``gemm_f32`` (FFMA, no tensor-core mode).  bfloat16 runs the library
-product (cuBLAS through ``torch.nn.functional.linear``), as the reference does for every linear layer
+Matrix products: float32 runs ``gemm_f32`` (FFMA, no tensor-core mode).  bfloat16 runs the weight-streaming
+``mma.sync`` kernel up to 8 rows (decode), the tcgen05 kernel from ``TENSOR_CORE_ROWS`` rows on (prefill; pairs of
+thread blocks on one tile, fused GLU epilogue), and in between, or when K is no multiple of 8, the library product
+(cuBLAS through ``torch.nn.functional.linear``), as the reference does for every linear layer
 (fms/modules/linear.py:119-156).
 """
 from __future__ import annotations
