@@ -493,6 +493,7 @@ FMS_API int fms_attention_decode(const void* q, void* out, int dtype, const void
                                  int pool_blocks, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (check_args("attention_decode", nheads, kvheads, head_dim, block_tokens)) return 1;
+  if (!(scale > 0.f)) return fms_fail("attention_decode: the scale of the scores is %g; it must be positive", (double)scale);
   AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window};
   return launch_decode("attention_decode", a, dtype, n_seqs, n_splits, part_o, part_ml, pool_blocks, stream);
 }
@@ -540,6 +541,7 @@ FMS_API int fms_attention_decode_no_alloc(const void* q, void* out, int dtype, c
                                           cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (check_args("attention_decode_no_alloc", nheads, kvheads, head_dim, block_tokens)) return 1;
+  if (!(scale > 0.f)) return fms_fail("attention_decode_no_alloc: the scale of the scores is %g; it must be positive", (double)scale);
   if (n_splits <= 0 || n_splits > 65535) return fms_fail("attention_decode_no_alloc: %d splits", n_splits);
   const size_t entries = (size_t)n_seqs * (size_t)nheads * (size_t)n_splits;
   const size_t need = entries * (size_t)(HD + 2) * sizeof(float);

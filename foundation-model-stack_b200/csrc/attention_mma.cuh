@@ -50,6 +50,13 @@ __device__ __forceinline__ void scores_16x64(float (*s)[4], const uint32_t (*qf)
 }
 constexpr float LOG2E = 1.4426950408889634f;
 
+// 2^x in one special-function instruction (relative error about 2^-22; 0 for -inf)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
   const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem);
   const int bytes = valid ? 16 : 0;  // 0: the destination is filled with zeros
@@ -172,12 +179,28 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};  // of heads 2 c and 2 c + 1; maximum in units of log2
   const float scale2 = a.scale * LOG2E;  // scores are kept times log2(e): exp(x) = exp2(x log2 e)
 
+  bool first_block = true;
   for (int kb = k_lo / BLK + warp; kb * BLK < k_hi; kb += NW) {
     const int blk = a.table[(size_t)slot * a.table_stride + kb];
     if (blk < 0) continue;
     const __nv_bfloat16* ksrc = kc + ((size_t)blk * a.kvheads + kvh) * BLK * HD;
     __syncwarp();  // the buffer is free: every lane is past the previous block
-    copy_block_async(vbuf, vc + ((size_t)blk * a.kvheads + kvh) * BLK * HD, kb * BLK, k_lo, k_hi, lane);
+    const bool whole = kb * BLK >= k_lo && kb * BLK + BLK <= k_hi;  // every key of the block counts: no masks
+    const __nv_bfloat16* vsrc = vc + ((size_t)blk * a.kvheads + kvh) * BLK * HD;
+    if (whole) {  // a lane copies piece (lane % PIECES) of the rows (lane / PIECES) + i (32 / PIECES): constant offsets
+      if (32 % PIECES == 0) {  // the lanes of a warp cover whole rows
+        constexpr int RSTEP = 32 % PIECES == 0 ? 32 / PIECES : 1;
+        const int row0 = lane / PIECES, part = lane % PIECES;
+        unsigned char* dst = vbuf + row0 * ROWB + part * 16;
+        const __nv_bfloat16* src = vsrc + (size_t)row0 * HD + part * 8;
+#pragma unroll
+        for (int i = 0; i < BLK / RSTEP; ++i) cp_async_16(dst + i * RSTEP * ROWB, src + (size_t)i * RSTEP * HD, true);
+      } else {
+        copy_block_async(vbuf, vsrc, kb * BLK, k_lo, k_hi, lane);
+      }
+    } else {
+      copy_block_async(vbuf, vsrc, kb * BLK, k_lo, k_hi, lane);
+    }
     cp_async_commit_group();
     // scores, 16 keys at a time: element e of tile t is (key 16 t + g + 8 (e / 2), head 2 c + (e % 2)).  Rows of
     // the block beyond the sequence are read too (they exist) and masked below.
@@ -216,24 +239,30 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
         mma16816(st[t], a0, qf[G32][0], qf[G32][1]);
       }
     }
+    // raw scores; the scale (positive) goes into the exponent's multiply-add
+    if (!whole) {
+#pragma unroll
+      for (int t = 0; t < 4; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int kpos = kb * BLK + 16 * t + g + 8 * (e >> 1);
+          if (kpos < k_lo || kpos >= k_hi) st[t][e] = -INFINITY;
+        }
+    }
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int t = 0; t < 4; ++t)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int kpos = kb * BLK + 16 * t + g + 8 * (e >> 1);
-        st[t][e] = (kpos >= k_lo && kpos < k_hi) ? st[t][e] * scale2 : -INFINITY;
-        tile_max[e & 1] = fmaxf(tile_max[e & 1], st[t][e]);
-      }
-    float alpha[2], psum[2] = {0.f, 0.f}, m_use[2];
+      for (int e = 0; e < 4; ++e) tile_max[e & 1] = fmaxf(tile_max[e & 1], st[t][e]);
+    float alpha[2], psum[2] = {0.f, 0.f}, neg_m[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {  // over the keys: the lanes that differ in g
       tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 4));
       tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 8));
       tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 16));
-      const float m_new = fmaxf(m[h], tile_max[h]);
-      m_use[h] = m_new == -INFINITY ? 0.f : m_new;
-      alpha[h] = m[h] == -INFINITY ? 0.f : exp2f(m[h] - m_use[h]);
+      const float m_new = fmaxf(m[h], tile_max[h] * scale2);
+      neg_m[h] = m_new == -INFINITY ? 0.f : -m_new;
+      alpha[h] = ex2_approx(m[h] + neg_m[h]);  // 2^-inf = 0 while nothing has been seen
       m[h] = m_new;
     }
     uint32_t pb[4][2];  // P^T as B operand of k-step t (keys 16 t ..): (keys 2 c, 2 c + 1 (+ 8); head g)
@@ -242,7 +271,7 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
       float p[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        p[e] = st[t][e] == -INFINITY ? 0.f : exp2f(st[t][e] - m_use[e & 1]);
+        p[e] = ex2_approx(fmaf(st[t][e], scale2, neg_m[e & 1]));  // 2^-inf = 0 for a masked key
         psum[e & 1] += p[e];
       }
       pb[t][0] = movmatrix_trans(pack_bf16(p[0], p[1]));
@@ -255,10 +284,13 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
       psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], 16);
       l[h] = l[h] * alpha[h] + psum[h];
     }
+    if (!first_block) {  // nothing is accumulated yet in a warp's first block
 #pragma unroll
-    for (int j = 0; j < HD / 16; ++j) {
-      o[j][0] *= alpha[0]; o[j][1] *= alpha[1]; o[j][2] *= alpha[0]; o[j][3] *= alpha[1];
+      for (int j = 0; j < HD / 16; ++j) {
+        o[j][0] *= alpha[0]; o[j][1] *= alpha[1]; o[j][2] *= alpha[0]; o[j][3] *= alpha[1];
+      }
     }
+    first_block = false;
     cp_async_wait_group<0>();
     __syncwarp();
     // V^T tiles of 16 values x 16 keys: matrix (lane >> 3) of the four is (values + 8 ((lane >> 3) & 1),
@@ -291,32 +323,45 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
     wml[2 * (2 * c + 1)] = m[1]; wml[2 * (2 * c + 1) + 1] = l[1];
   }
   __syncthreads();
-  for (int i = tid; i < ng * HD; i += NW * 32) {
-    const int r = i / HD, d = i - r * HD;
+  // a head's weights of the warps are taken once by each of the threads that share its values
+  constexpr int TPH = NW * 32 / GROWS;  // threads per head
+  const int r = tid / TPH;
+  if (r < ng) {
     float mm = -INFINITY;
 #pragma unroll
     for (int w = 0; w < NW; ++w)
       mm = fmaxf(mm, (reinterpret_cast<const float*>(smem_raw + (size_t)w * BLK * ROWB) + GROWS * HD)[2 * r]);
-    float sum = 0.f, lsum = 0.f;
+    float f[NW], lsum = 0.f;
 #pragma unroll
     for (int w = 0; w < NW; ++w) {
-      const float* wv = reinterpret_cast<const float*>(smem_raw + (size_t)w * BLK * ROWB);
-      const float* wm = wv + GROWS * HD;
-      const float f = wm[2 * r] == -INFINITY ? 0.f : exp2f(wm[2 * r] - mm);
-      sum += wv[r * HD + d] * f;
-      lsum += wm[2 * r + 1] * f;
+      const float* wm = reinterpret_cast<const float*>(smem_raw + (size_t)w * BLK * ROWB) + GROWS * HD;
+      f[w] = wm[2 * r] == -INFINITY ? 0.f : ex2_approx(wm[2 * r] - mm);
+      lsum += wm[2 * r + 1] * f[w];
     }
     const int head = kvh * group + g0 + r;
+    const size_t at = ((size_t)seq * a.nheads + head) * n_splits + split;
     if (n_splits == 1) {  // nothing to merge with: this is the result (no second kernel is launched)
       __nv_bfloat16* out = (__nv_bfloat16*)a.out + (size_t)a.first_row[seq] * a.nheads * HD + (size_t)head * HD;
-      out[d] = __float2bfloat16_rn(lsum > 0.f ? sum / lsum : 0.f);
-      continue;
-    }
-    const size_t at = ((size_t)seq * a.nheads + head) * n_splits + split;
-    part_o[at * HD + d] = sum;
-    if (d == 0) {
-      part_ml[at * 2] = mm * (1.f / LOG2E);  // back to natural units, which attn_combine_kernel expects
-      part_ml[at * 2 + 1] = lsum;
+      const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+      for (int d = tid % TPH; d < HD; d += TPH) {
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w)
+          sum += reinterpret_cast<const float*>(smem_raw + (size_t)w * BLK * ROWB)[r * HD + d] * f[w];
+        out[d] = __float2bfloat16_rn(sum * inv);
+      }
+    } else {
+      for (int d = tid % TPH; d < HD; d += TPH) {
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w)
+          sum += reinterpret_cast<const float*>(smem_raw + (size_t)w * BLK * ROWB)[r * HD + d] * f[w];
+        part_o[at * HD + d] = sum;
+      }
+      if (tid % TPH == 0) {
+        part_ml[at * 2] = mm * (1.f / LOG2E);  // back to natural units, which attn_combine_kernel expects
+        part_ml[at * 2 + 1] = lsum;
+      }
     }
   }
 }

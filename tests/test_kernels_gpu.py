@@ -264,6 +264,9 @@ ATTN_CASES = [
     (4, 2, 64, [500, 70], [100, 3], 50),            # prefill behind a window whose earlier blocks were given back
     (8, 2, 128, [300], [40], 64),                   # the same at head size 128
     (8, 2, 128, [300, 200], [1, 1], 64),            # decode behind a window
+    (5, 5, 48, [130, 70], [1, 1], 0),               # decode, a head size whose 16-byte pieces do not divide a warp
+    (4, 2, 80, [100, 200], [1, 1], 0),              # decode, head size 80 (a last k-step of 16 alone)
+    (4, 2, 80, [10], [70], 0),                      # prefill, head size 80
 ]
 
 
