@@ -107,8 +107,10 @@ def generate_batch(engine, sampler: Sampler, prompts: Sequence[Sequence[int]], r
 
 def generate(model, input_ids: Prompts, max_seq_len: int = 4096, max_new_tokens: int = 256,
              temperature: float = 1.0, top_k: int = 10, do_sample: bool = True, num_beams: int = 1,
-             use_cache: bool = True, eos_token_id: Union[int, Sequence[int], None] = None,
-             pad_token_id: Optional[int] = None, timing: str = "", post_iteration_hook: Optional[Callable] = None,
+             use_cache: bool = True, contiguous_cache: bool = False,
+             eos_token_id: Union[int, Sequence[int], None] = None, pad_token_id: Optional[int] = None,
+             timing: str = "", prepare_model_inputs_hook: Optional[Callable] = None,
+             post_iteration_hook: Optional[Callable] = None, extra_kwargs: Optional[dict] = None,
              seed: int = 0, batch_size: Optional[int] = None, cache_tokens: Optional[int] = None):
     """Generates ``max_new_tokens`` tokens after each prompt.
 
@@ -118,6 +120,9 @@ def generate(model, input_ids: Prompts, max_seq_len: int = 4096, max_new_tokens:
     max_seq_len: prompts longer than this are cut to their last ``max_seq_len`` tokens, as the reference
         clips its input window (fms/utils/generation.py:288).
     temperature, top_k, do_sample: as in the reference; ``do_sample=False`` is greedy.
+    contiguous_cache: accepted for the reference's callers; the cache here is made of blocks and has no such mode.
+    prepare_model_inputs_hook, extra_kwargs: the reference passes these into its model's forward; the engine
+        builds its own inputs, so anything but None (or an empty mapping) is refused.
     eos_token_id: one stop token or several; a sequence ends with its stop token.
     timing: "" | "per-token" | "e2e": also return the seconds of each step, or of the whole call.
     post_iteration_hook(step, logits, tokens, requests): called after every step of a batch.
@@ -130,6 +135,10 @@ def generate(model, input_ids: Prompts, max_seq_len: int = 4096, max_new_tokens:
     """
     if num_beams != 1:
         raise NotImplementedError("generate() does yet not support beam search")
+    if prepare_model_inputs_hook is not None:
+        raise NotImplementedError("prepare_model_inputs_hook: the engine builds the inputs of a step itself")
+    if extra_kwargs:
+        raise NotImplementedError(f"extra_kwargs {sorted(extra_kwargs)}: the engine's step takes no further arguments")
     if not use_cache:
         raise NotImplementedError("generation always uses the cache")
     if timing not in ("", "per-token", "e2e"):

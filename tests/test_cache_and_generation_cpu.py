@@ -226,6 +226,12 @@ def test_generate_argument_checks_and_release_on_error(greedy_on_cpu):
         generate(e, [[1]], timing="sometimes")
     with pytest.raises(ValueError):
         generate(e, [[1]], do_sample=True, temperature=0.0)
+    # the reference's remaining parameters are accepted where they mean nothing here and refused where they would
+    assert generate(e, [[1]], max_new_tokens=1, do_sample=False, contiguous_cache=True, extra_kwargs={})[0].tolist() == [1, 2]
+    with pytest.raises(NotImplementedError):
+        generate(e, [[1]], prepare_model_inputs_hook=lambda *a: a)
+    with pytest.raises(NotImplementedError):
+        generate(e, [[1]], extra_kwargs={"attn_name": "sdpa_causal"})
 
     def boom(*a, **k):
         raise RuntimeError("hook failed")
