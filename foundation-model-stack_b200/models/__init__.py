@@ -73,6 +73,7 @@ def read_config_json(model_path: str) -> dict:
 
 def get_model(architecture: str, variant: Optional[str] = None, model_path: Optional[str] = None,
               source: Optional[str] = None, device_type: str = "cuda", data_type: Union[str, torch.dtype, None] = None,
+              distributed_strategy: Optional[str] = None, checkpoint_sharding: Optional[str] = None, group=None,
               seed: int = 0, **kwargs) -> Model:
     """Builds a model and fills its weights.
 
@@ -81,8 +82,13 @@ def get_model(architecture: str, variant: Optional[str] = None, model_path: Opti
     model_path: folder (or file, or glob) of safetensors; None means random weights from ``seed``.
     source: the checkpoint's naming ("hf" by default; "fms" for the engine's own names).
     data_type: "bf16" (default) or "fp32": the compute dtype; float32 uses no reduced-precision product.
+    distributed_strategy, checkpoint_sharding, group: the reference's parameters for several devices
+        (fms/models/__init__.py:298-308); this library runs on one GPU and refuses anything but None.
     kwargs: overrides of configuration fields, as in the reference.
     """
+    if distributed_strategy is not None or checkpoint_sharding is not None or group is not None:
+        raise NotImplementedError("this library runs a model on one GPU: distributed_strategy, checkpoint_sharding "
+                                  "and group must be None")
     from ..weights.sources import FileSource, RandomSource
 
     config = None

@@ -69,6 +69,8 @@ def test_registry():
         models.get_model("no_such_architecture", "x", device_type="cpu")
     m = models.get_model("llama", "micro", device_type="cpu", data_type="fp32", nlayers=1)
     assert m.config.nlayers == 1 and m.config.emb_dim == 192
+    with pytest.raises(NotImplementedError):  # the reference's parameters for several devices: one GPU here
+        models.get_model("llama", "micro", device_type="cpu", distributed_strategy="tp")
 
 
 def test_state_dict_names_are_the_references(tmp_path):
