@@ -282,6 +282,35 @@ def test_head_size_128_model_bfloat16_against_float32(tmp_path):
     assert (out["bf16"].argmax(-1) == out["fp32"].argmax(-1)).float().mean() > 0.9
 
 
+def test_many_short_requests_in_one_batch_bfloat16_against_float32(tmp_path):
+    """Forty requests of 1 to 120 tokens in one batch (prompts in one step of more than a thousand rows, whose
+    attention tiles span many sequences; then decode steps of forty rows, which take the library product), on the
+    model shape of the test above; the float32 path is the yardstick."""
+    from fms_b200.models import get_model
+    from fms_b200.models.llama import LLaMA, LLaMAConfig
+    from fms_b200.weights import write_random_model
+
+    arch = LLaMA(LLaMAConfig(src_vocab_size=4099, emb_dim=1024, nheads=8, kvheads=2, nlayers=2, hidden_dim=2816,
+                             max_expected_seq_len=2048, rope_theta=500000.0))
+    folder = write_random_model(str(tmp_path / "m"), arch.config_json(), arch.checkpoint_layout(), seed=6)
+    g = torch.Generator().manual_seed(71)
+    lens = [1, 2, 63, 64, 65, 120] + [int(v) for v in torch.randint(1, 121, (34,), generator=g)]
+    reqs = [torch.randint(0, 4099, (k + 3,), generator=g).tolist() for k in lens]
+    assert sum(lens) > 1024
+    out = {}
+    for dtype in ("fp32", "bf16"):
+        engine = get_model("hf_pretrained", model_path=folder, device_type="cuda", data_type=dtype).new_engine(64 * 120)
+        slots = engine.begin(len(reqs))
+        rows = [engine.step(slots, [r[:k] for r, k in zip(reqs, lens)], [[k - 1] for k in lens]).float().cpu()]
+        for t in range(3):
+            rows.append(engine.step(slots, [[r[k + t]] for r, k in zip(reqs, lens)]).float().cpu())
+        engine.release(slots)
+        engine.check()
+        out[dtype] = torch.cat(rows)
+    close(out["bf16"], out["fp32"], "bf16")
+    assert (out["bf16"].argmax(-1) == out["fp32"].argmax(-1)).float().mean() > 0.9
+
+
 def test_window_attention_through_the_engine(tmp_path):
     """A decoder whose mixers keep a window of 40 keys: the cache gives blocks back as they leave the window, and
     the logits equal the plain implementation's with the same window, whole and token by token."""
