@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const __grid_consta
 // (GLU: block 0 the gate rows, block 1 the up rows) into its own shared memory, so a multiprocessor takes in a
 // third less per flop than with tiles of 128 x 256 of its own, and that intake is what limits the kernel.  Block 0
 // issues the mma for both (256 x TN x 16) and counts the arriving bytes of both on its "full" barriers; the
-// commits go to the "empty" and "accumulator ready" barriers of both blocks; each block's epilogue reads its own
+// commits go to the "empty" and "accumulator ready" barriers of both blocks (one commit each); each block's epilogue reads its own
 // tensor memory (its 128 rows) and gives the accumulator back on block 0's barrier.  No block leaves before its
 // partner has (cluster barrier at the end).
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)

@@ -163,13 +163,14 @@ __device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t desc_a, uint
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc), "r"(zero)
       : "memory");
 }
-// arrives on the mbarrier at this offset in both blocks once all mma issued so far are done
+// arrives on the mbarrier at this offset in both blocks once all mma issued so far are done: one commit to this
+// block's barrier (the leader's), one to its partner's
 __device__ __forceinline__ void tc_commit_pair(void* bar) {
-  const uint16_t both = 3;
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n" ::"r"(
-                   smem_u32(bar)),
-               "h"(both)
-               : "memory");
+  asm volatile(
+      "{\n.reg .b32 partner;\nmapa.shared::cluster.u32 partner, %0, 1;\n"
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [partner];\n}\n" ::"r"(smem_u32(bar))
+      : "memory");
 }
 // arrives on the mbarrier at this offset in block `rank` of the cluster
 __device__ __forceinline__ void mbar_arrive_remote(void* bar, uint32_t rank) {

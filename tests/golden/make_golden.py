@@ -66,4 +66,6 @@ def main(reference_root: str):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <path of a checkout of foundation-model-stack>")
+    main(sys.argv[1])
