@@ -202,6 +202,13 @@ _8b_llama3 = LLaMAConfig(src_vocab_size=128256, emb_dim=4096, norm_eps=1e-5, nhe
                          hidden_grow_factor=3.5, multiple_of=1024, max_expected_seq_len=8192, rope_theta=500_000.0)
 
 
+# two tiny shapes for trying things out (a few layers, sizes that are no powers of two, grouped and single kv heads)
+_tiny_a = LLaMAConfig(src_vocab_size=256, emb_dim=64, nheads=4, kvheads=2, nlayers=2, hidden_dim=176,
+                      max_expected_seq_len=64)
+_tiny_b = LLaMAConfig(src_vocab_size=384, emb_dim=96, nheads=3, kvheads=1, nlayers=3, hidden_dim=256, norm_eps=1e-6,
+                      rope_theta=500_000.0, max_expected_seq_len=128, tie_heads=True)
+
+
 def _factory(config: LLaMAConfig):
     def make(**kwargs) -> LLaMA:
         return LLaMA(config, **kwargs)
@@ -211,7 +218,7 @@ def _factory(config: LLaMAConfig):
 
 register_architecture("llama", LLaMA, config_json_names=("LlamaForCausalLM",))
 for _name, _cfg in (("micro", _micro), ("7b", _7b), ("2-7b", _7b), ("13b", _13b), ("2-13b", _13b), ("70b", _70b),
-                    ("2-70b", _70b), ("3-8b", _8b_llama3)):
+                    ("2-70b", _70b), ("3-8b", _8b_llama3), ("tiny-a", _tiny_a), ("tiny-b", _tiny_b)):
     register_model("llama", _name, _factory(_cfg))
 
 
