@@ -315,7 +315,8 @@ def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", "1")))
     ap.add_argument("--steps", type=int, default=64)
-    ap.add_argument("--warmup", type=int, default=8)
+    # the default covers the 20 or so steps (80 ms) that the GPU's clocks take to come back up after the prefill
+    ap.add_argument("--warmup", type=int, default=24)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--only", default="", help="decode_b<batch> or prefill: run and print that part only")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model's 32 (named in config)")

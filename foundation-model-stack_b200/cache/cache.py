@@ -107,12 +107,23 @@ class KVGroup:
         self._dirty.add(slot)
 
     def sync(self) -> None:
+        """Brings the changed rows of the table to the device: a snapshot in pinned memory (later host changes do not
+        reach a copy that is still on its way), then one asynchronous copy per run of consecutive rows, on the
+        stream of the kernels that read the table.  Nothing waits and no kernel is launched."""
         if not self._dirty:
             return
         idx = sorted(self._dirty)
-        rows = self.table_host[idx]  # a snapshot: later host changes do not reach this copy
-        self.table[torch.tensor(idx, dtype=torch.long, device=self.table.device)] = rows.to(self.table.device)
         self._dirty.clear()
+        if self.table.device.type != "cuda":
+            self.table[idx] = self.table_host[idx]
+            return
+        staging = torch.empty((len(idx), self.blocks_per_sequence), dtype=torch.int32, pin_memory=True)
+        torch.index_select(self.table_host, 0, torch.tensor(idx, dtype=torch.long), out=staging)
+        start = 0
+        for j in range(1, len(idx) + 1):
+            if j == len(idx) or idx[j] != idx[j - 1] + 1:  # rows idx[start..j) are consecutive
+                self.table[idx[start]:idx[start] + (j - start)].copy_(staging[start:j], non_blocking=True)
+                start = j
 
     def view(self, layer: int) -> KVLayerView:
         i = self.layers.index(layer)
