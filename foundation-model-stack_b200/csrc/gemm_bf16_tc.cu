@@ -356,15 +356,14 @@ int multiprocessors() {
 // cost least in whole rounds of the `units` that work at the same time (multiprocessors, or pairs of them).
 // A pair's tile costs, measured, 1.0 at 256 columns and 0.56 + 0.0014 TN below (the tensor cores limit the widest
 // tile, what a multiprocessor takes in per step the others); a single block's tile costs as its intake per step
-// of 64 k: 128 rows of x, TN rows of w and a constant.  step: 16 (GLU and pairs: 32, so that a half is a multiple
-// of 16).
+// of 64 k: 128 rows of x, TN rows of w and a constant.  step: 16 (GLU: 32, so that a half is a multiple of 16).
 int choose_tile_n(int tiles_m, int cols, bool glu, bool pair, int units) {
   static int forced = -1;
   if (forced < 0) {
     const char* e = getenv("FMS_B200_TC_TILE_N");
     forced = e ? atoi(e) : 0;
   }
-  const int step = (glu || pair) ? 32 : 16;
+  const int step = glu ? 32 : 16;
   if (forced >= 64 && forced <= MAX_TILE_N && forced % step == 0) return forced;
   long best_cost = -1;
   int best = MAX_TILE_N;
