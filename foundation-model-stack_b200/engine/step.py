@@ -112,9 +112,9 @@ class Engine:
         if len(slots) != len(tokens) or not slots:
             raise ValueError("a step needs one token list per slot, and at least one")
         for t in tokens:
-            for x in t:
-                if not (0 <= int(x) < self.vocab_size):
-                    raise ValueError(f"token id {x} outside the vocabulary of {self.vocab_size}")
+            if len(t) and not (0 <= min(t) and max(t) < self.vocab_size):
+                bad = next(x for x in t if not (0 <= int(x) < self.vocab_size))
+                raise ValueError(f"token id {bad} outside the vocabulary of {self.vocab_size}")
         if all(len(t) == 1 for t in tokens) and (want is None or all(list(w) == [0] for w in want)):
             return self.decode(slots, [int(t[0]) for t in tokens]).clone()
         if want is None:
