@@ -114,6 +114,76 @@ def prefill_flops(nlayers, tokens, m=MODEL):
 # --------------------------------------------------------------------------------------------------
 # this library
 # --------------------------------------------------------------------------------------------------
+def run_kernels(args):
+    """--only gemm_rows / attention_prefill / attention_decode: single kernels at the model's layer sizes over a
+    range of rows, tokens or contexts, timed alone with CUDA events (L2 flushed before every launch), the products
+    beside the library's.  One JSON line a size."""
+    import torch
+
+    from fms_b200.cache import Cache, KVRequest
+    from fms_b200.engine.batch import Batch
+    from fms_b200.kernels import ops
+
+    m = MODEL
+    d, hd, h, kv, f = m["emb_dim"], m["head_dim"], m["nheads"], m["kvheads"], m["ffn_hidden"]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def timed(fn, repeats=10):
+        for _ in range(3):
+            fn()
+        us = []
+        for _ in range(repeats):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            us.append(a.elapsed_time(b) * 1e3)
+        return round(statistics.median(us), 1)
+
+    bf16 = torch.bfloat16
+    if args.only == "gemm_rows":
+        shapes = {"qkv": ((h + 2 * kv) * hd, d), "dense": (d, h * hd), "down": (d, f)}
+        ws = {k: (torch.randn(n, kk, device="cuda") * 0.02).to(bf16) for k, (n, kk) in shapes.items()}
+        wg = (torch.randn(2 * f, d, device="cuda") * 0.02).to(bf16)
+        for rows in (1, 8, 16, 64, 256, 512, 1024, 2048, 4096):
+            xs = {d: torch.randn(rows, d, device="cuda").to(bf16), f: torch.randn(rows, f, device="cuda").to(bf16)}
+            line = {"only": "gemm_rows", "rows": rows, "us": "own, library"}
+            for name, (n, kk) in shapes.items():
+                line[name] = [timed(lambda: ops.linear(xs[kk], ws[name])),
+                              timed(lambda: torch.nn.functional.linear(xs[kk], ws[name]))]
+            line["glu"] = [timed(lambda: ops.gated_linear(xs[d], wg, None, 0)),
+                           timed(lambda: ops.gated_activation(torch.nn.functional.linear(xs[d], wg), 0))]
+            print(json.dumps(line), flush=True)
+    else:
+        cases = [(1, n) for n in (512, 1024, 2048, 4096, 8192)] if args.only == "attention_prefill" else \
+            [(b, n) for b, n in ((1, 1024), (1, 8192), (8, 1155), (8, 8192), (64, 1155), (64, 4096))]
+        for b, n in cases:
+            decode = args.only == "attention_decode"
+            cache = Cache([KVRequest(kv, hd, 0)], max_tokens=b * (n + 128), max_positions=n + 128, dtype=bf16, device="cuda")
+            slots = cache.begin(b)
+            if decode:
+                cache.prepare(slots, [n] * b)
+                cache.commit(slots, [n] * b)
+            new = 1 if decode else n
+            cache.prepare(slots, [new] * b)
+            view = cache.layer_view(0)
+            view.keys.normal_()
+            view.values.normal_()
+            batch = Batch.from_lists(slots, [n if decode else 0] * b, [[0] * new] * b, [[]] * b, "cuda")
+            q = torch.randn(b * new, h * hd, device="cuda").to(bf16)
+            us = timed(lambda: ops.attention(q, batch, view, h, kv, hd, hd ** -0.5, 0), repeats=20)
+            line = {"only": args.only, "sequences": b, "tokens": n, "us": us}
+            if decode:
+                line["kv_GBs"] = round(b * n * kv * hd * 2 * 2 / us / 1e3, 1)
+            else:
+                line["tflops"] = round(4.0 * n * n / 2 * hd * h / us / 1e6, 1)
+            print(json.dumps(line), flush=True)
+            del cache, view
+    ops.check_error_flag("cuda")
+
+
 def run_ours(args):
     import torch
 
@@ -318,7 +388,8 @@ def main():
     # the default covers the 20 or so steps (80 ms) that the GPU's clocks take to come back up after the prefill
     ap.add_argument("--warmup", type=int, default=24)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--only", default="", help="decode_b<batch> or prefill: run and print that part only")
+    ap.add_argument("--only", default="", help="decode_b<batch> or prefill: run and print that part only; gemm_rows, "
+                    "attention_prefill, attention_decode: single kernels over a range of sizes")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model's 32 (named in config)")
     args = ap.parse_args()
     if args.gpus != 1:
@@ -327,6 +398,8 @@ def main():
         sys.exit(2)
     if args.impl == "reference":
         run_reference(args)
+    elif args.only in ("gemm_rows", "attention_prefill", "attention_decode"):
+        run_kernels(args)
     else:
         run_ours(args)
 
