@@ -11,6 +11,11 @@ and a device-to-host read of every step's result inside the timed region).  ``pr
 cache of the live requests) over its time, against the measured copy bandwidth.  ``points``: decode at
 batch 1 and 64.  Weights (15 GB a step) are larger than L2, so no flush is needed between steps.
 
+``--only decode_b<N>`` or ``--only prefill`` prints that part alone (for profilers); ``--only gemm_rows``,
+``attention_prefill`` and ``attention_decode`` time single kernels at the model's layer sizes over a range of rows,
+tokens or contexts, one JSON line a size.  The default warm-up of 24 steps covers the 80 ms or so that the GPU's
+clocks take to come back up after the prefill's power-capped run.
+
 ``--impl reference`` runs the unmodified reference (baseline/_ref) through its own get_model/generate.
 For more than one GPU the program says that it has no such path and exits with 2.
 """
