@@ -285,3 +285,17 @@ def test_sampler_arguments():
     with pytest.raises(ValueError):
         Sampler(do_sample=True, top_k=-1)
     Sampler(do_sample=False, temperature=0.0)  # greedy ignores the temperature
+
+
+def test_bench_says_that_it_measures_one_gpu_only():
+    """For more than one GPU bench.py prints one line that says so and exits with 2 (no GPU is needed for that)."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--gpus", "2"], capture_output=True, text=True,
+                       timeout=120)
+    assert r.returncode == 2
+    lines = [line for line in r.stdout.splitlines() if line.strip()]
+    assert len(lines) == 1 and "one GPU" in lines[0]
