@@ -368,3 +368,26 @@ def test_command_line(tiny_folders):
     oracle = pl.PlainLlama(tiny_folders["a"])
     assert [[int(x) for x in l.split(",")] for l in lines] == [pl.plain_generate(oracle, p, 6)
                                                               for p in ([5, 17, 3], [9, 8, 7, 6, 5, 4])]
+
+
+def test_bench_line_has_the_keys_of_its_contract():
+    """bench.py on two layers and a few steps: one JSON line with the figures and a flat config of at most 20 keys."""
+    import json
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--layers", "2", "--steps", "4", "--warmup", "3"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [line for line in r.stdout.splitlines() if line.strip()]
+    assert len(lines) == 1
+    out = json.loads(lines[0])
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                "vs_baseline", "dtype", "data", "config", "clocks", "e2e", "gpu_launches", "prefill", "roofline", "points"):
+        assert key in out, key
+    assert out["n_gpus"] == 1 and out["steps"] == 4 and out["value"] > 0 and out["gpu_launches"] > 0
+    assert len(out["config"]) <= 20 and all(not isinstance(v, (dict, list)) for v in out["config"].values())
+    assert out["config"]["layers"] == 2 and out["config"]["layers_of_model"] == 32
+    assert set(out["prefill"]) >= {"value", "tokens", "ms", "frac"} and out["prefill"]["tokens"] == 2048
+    assert set(out["roofline"]) >= {"bound", "achieved", "peak", "unit", "frac"} and out["roofline"]["bound"] == "hbm"
+    assert set(out["points"]) >= {"decode_b1", "decode_b64"}
+    assert out["e2e"]["h2d_bytes_per_step"] > 0 and out["e2e"]["d2h_bytes_per_step"] > 0
