@@ -365,6 +365,32 @@ def test_decode_attention_at_every_batch_size(ops, n_seqs, kvheads):
     torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
 
 
+def test_kernels_report_what_the_host_should_have_prevented(ops):
+    """A token id outside the vocabulary and a position without a cache block do not fault: the kernel leaves the
+    row alone, sets the error flag, and the host's check raises (and clears the flag)."""
+    from fms_b200.kernels.ops import KernelError
+
+    ops.check_error_flag("cuda")
+    table = torch.randn(10, 16).cuda()
+    ops.embed(table, torch.tensor([3, 10, 2], dtype=torch.int32).cuda())  # 10 is one past the last row
+    with pytest.raises(KernelError, match="vocabulary"):
+        ops.check_error_flag("cuda")
+    ops.check_error_flag("cuda")  # cleared
+
+    for dtype, n_new in ((torch.float32, 2), (torch.bfloat16, 70)):  # the per-token and the many-token kernel
+        cache, view, batch = make_cache_case(dtype, 4, 2, 16, [63], [n_new], 16, poison=False)
+        view.table[int(batch.slots[0]), 1] = -1  # positions 64..127 have lost their block
+        keys0 = view.keys.clone()
+        qkv = torch.randn(n_new, 8 * 16).to(dtype).cuda()
+        ops.rope_store(qkv, None, batch, view, 4, 2, 16)
+        with pytest.raises(KernelError, match="cache block"):
+            ops.check_error_flag("cuda")
+        row = cache.groups[0].table_host[int(batch.slots[0])]
+        still_there = sorted(int(row[i]) for i in range((63 + n_new + 63) // 64) if i != 1)
+        changed = (view.keys != keys0).flatten(1).any(1).nonzero().flatten().tolist()
+        assert changed == still_there  # only the blocks that exist were written
+
+
 def test_attention_refuses_other_head_sizes():
     from fms_b200.kernels.build import KernelBuildError, _spec
 
