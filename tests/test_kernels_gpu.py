@@ -87,6 +87,22 @@ def test_linear_float32_is_true_float32(ops, m, n, k, bias):
     assert torch.equal(alone[0], got[0])
 
 
+@pytest.mark.parametrize("n,k", [(70, 4), (100, 68), (64, 2052), (333, 1024), (130, 30)])
+@pytest.mark.parametrize("few", [1, 3, 8])
+def test_linear_float32_few_rows_are_bit_for_bit_the_same_rows_among_many(ops, few, n, k):
+    """A decode step's rows go through a kernel of their own (one thread a column); its sums run in the same
+    order as the tiled kernel's, so a token's logits do not depend on which of the two its step took."""
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(40, k, generator=g).cuda()
+    w = torch.randn(n, k, generator=g).cuda()
+    b = torch.randn(n, generator=g).cuda()
+    many = ops.linear(x, w, b)
+    got = ops.linear(x[:few].contiguous(), w, b)
+    assert torch.equal(got, many[:few])
+    want = P.linear(x[:few], w, b, torch.float64)
+    assert (got.double() - want).abs().max().item() < 2e-6 * math.sqrt(k) * 4
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 331, 240), (8, 512, 96), (9, 331, 240), (16, 512, 96), (33, 1000, 328), (200, 384, 64)])
 def test_linear_bfloat16(ops, m, n, k):
     g = torch.Generator().manual_seed(4)
