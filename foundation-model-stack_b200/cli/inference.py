@@ -8,7 +8,8 @@ Kept from the reference: --device_type, --architecture, --variant, --model_path,
 --tokenizer, --default_dtype, --batch_input (run all prompts as one batch), --context_file, --deterministic
 (here: greedy).  Added: --prompt (repeatable), --prompt_ids, --max_new_tokens, --do_sample, --temperature,
 --top_k, --seed, --eos_token_id, --timing.  Dropped, with what they selected gone: --no_use_cache,
---unfuse_weights, --compile, --compile_mode, --distributed, --attn_name, --min_pad_length (nothing is padded).
+--unfuse_weights, --compile, --compile_mode, --distributed, --attn_name.  --min_pad_length is kept with its
+meaning: the prompts go through ``pad_input_ids`` and come back out of their padding, which changes no token.
 """
 from __future__ import annotations
 
@@ -30,6 +31,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--default_dtype", type=str, default=None, choices=["bf16", "fp32"],
                    help="Compute dtype; fp32 uses no reduced-precision product")
     p.add_argument("--batch_input", action="store_true", help="Run all prompts as one batch")
+    p.add_argument("--min_pad_length", type=int, default=0,
+                   help="Pad inputs to a minimum length. If any prompt is longer, padding will be determined by "
+                        "the largest prompt")
     p.add_argument("--context_file", type=str, default=None, help="File whose text is put before every prompt")
     p.add_argument("--deterministic", action="store_true", help="Greedy decoding (the kernels are deterministic)")
     p.add_argument("--prompt", action="append", default=[], help="A prompt; may be given several times")
@@ -49,7 +53,7 @@ def main(argv=None) -> int:
     import torch
 
     from ..models import get_model
-    from ..utils.generation import generate
+    from ..utils.generation import generate, pad_input_ids, truncate_after_eos
     from ..utils.tokenizers import get_tokenizer
 
     tokenizer = get_tokenizer(args.tokenizer) if args.tokenizer else None
@@ -84,12 +88,19 @@ def main(argv=None) -> int:
     do_sample = args.do_sample and not args.deterministic
     groups = [prompts] if args.batch_input else [[p] for p in prompts]
     for group in groups:
-        out = generate(model, [torch.tensor(p) for p in group], max_new_tokens=args.max_new_tokens,
+        ids, padding = [torch.tensor(p) for p in group], None
+        if args.min_pad_length > 0:
+            ids, padding = pad_input_ids(ids, min_pad_length=args.min_pad_length)
+        out = generate(model, ids, max_new_tokens=args.max_new_tokens,
                        do_sample=do_sample, temperature=args.temperature, top_k=args.top_k, seed=args.seed,
-                       eos_token_id=eos, timing=args.timing)
+                       eos_token_id=eos, timing=args.timing, extra_kwargs=padding)
         if args.timing:
             out, times = out
             print(f"timing ({args.timing}): {[round(t * 1e3, 3) for t in times]} ms", file=sys.stderr)
+        if padding is not None:  # out of the rectangle again: no padding in front, nothing after a stop token
+            width = ids.shape[1]
+            out = [torch.cat((row[width - len(p):width], truncate_after_eos(row[width:], eos)))
+                   for row, p in zip(out, group)]
         for ids in out:
             ids = ids.tolist()
             print(tokenizer.decode(ids) if tokenizer else ",".join(str(i) for i in ids))

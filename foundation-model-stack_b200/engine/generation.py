@@ -32,6 +32,58 @@ def _as_lists(input_ids: Prompts):
     return out, "list"
 
 
+def pad_input_ids(input_ids_list: Sequence[torch.Tensor], min_pad_length: int = 0, is_causal_mask: bool = True,
+                  padding_side: str = "left", position_ids_offset: int = 0, pad_token_id: int = 0):
+    """Prompts of unequal lengths as one rectangle, with what tells its padding from its tokens: the call
+    of the reference's users (fms/utils/generation.py:16-109, same arguments and results).  Returns the
+    [n, width] ids, filled with ``pad_token_id`` on ``padding_side``, and a mapping with ``position_ids``
+    [n, width] (a prompt's own count from 0 plus ``position_ids_offset``; the offset alone on padding) and
+    ``mask`` [n, width, width] (0 where a row may look, -inf elsewhere: tokens at tokens, padding at
+    padding, and not ahead if ``is_causal_mask``).  ``generate`` takes both back through ``extra_kwargs``
+    and runs the prompts without their padding, so padding changes no result."""
+    if padding_side not in ("left", "right"):
+        raise ValueError('padding_side must be "left" or "right"')
+    prompts = [torch.as_tensor(p) for p in input_ids_list]
+    if not prompts:
+        raise ValueError("no prompts")
+    width = max([int(min_pad_length)] + [int(p.shape[0]) for p in prompts])
+    device = prompts[0].device
+    ids = torch.full((len(prompts), width), int(pad_token_id), dtype=torch.long, device=device)
+    real = torch.zeros((len(prompts), width), dtype=torch.bool, device=device)
+    position = torch.zeros((len(prompts), width), dtype=torch.long, device=device)
+    for i, p in enumerate(prompts):
+        n = int(p.shape[0])
+        where = slice(width - n, width) if padding_side == "left" else slice(0, n)
+        ids[i, where] = p.to(torch.long)
+        real[i, where] = True
+        position[i, where] = torch.arange(n, device=device)
+    allowed = real[:, :, None] == real[:, None, :]
+    if is_causal_mask:
+        allowed = allowed.tril()
+    mask = torch.zeros(allowed.shape, device=device).masked_fill(~allowed, float("-inf"))
+    return ids, {"mask": mask, "position_ids": position + int(position_ids_offset)}
+
+
+def _tokens_of_padded_rows(input_ids: torch.Tensor, position_ids: torch.Tensor):
+    """For each row of a rectangle that ``pad_input_ids`` made: (first, last + 1) of its tokens.  A prompt
+    counts its positions up from the smallest one, padding stays at it; a row whose positions say nothing
+    about the side (one token) is taken as padded on the left, the default."""
+    if position_ids.shape != input_ids.shape:
+        raise ValueError(f"position_ids {tuple(position_ids.shape)} for input_ids {tuple(input_ids.shape)}")
+    spans = []
+    width = input_ids.shape[1]
+    for row in position_ids.tolist():
+        n = max(row) - min(row) + 1
+        if n > width:
+            raise ValueError("position_ids are not those of pad_input_ids")
+        left = row[width - n:] == list(range(min(row), min(row) + n))
+        right = row[:n] == list(range(min(row), min(row) + n))
+        if not (left or right):
+            raise ValueError("position_ids are not those of pad_input_ids")
+        spans.append((width - n, width) if left else (0, n))
+    return spans
+
+
 def plan_batches(lengths: Sequence[int], max_new_tokens: int, batch_size: Optional[int], cache_tokens: int,
                  max_slots: int, block_tokens: int = 64) -> List[List[int]]:
     """Cuts request numbers 0..n-1 into batches, in order: at most ``batch_size`` (and ``max_slots``)
@@ -121,8 +173,10 @@ def generate(model, input_ids: Prompts, max_seq_len: int = 4096, max_new_tokens:
         clips its input window (fms/utils/generation.py:288).
     temperature, top_k, do_sample: as in the reference; ``do_sample=False`` is greedy.
     contiguous_cache: accepted for the reference's callers; the cache here is made of blocks and has no such mode.
-    prepare_model_inputs_hook, extra_kwargs: the reference passes these into its model's forward; the engine
-        builds its own inputs, so anything but None (or an empty mapping) is refused.
+    prepare_model_inputs_hook, extra_kwargs: the reference passes these into its model's forward
+        (fms/utils/generation.py:246-252).  The engine builds its own inputs, so a hook is refused, and of
+        ``extra_kwargs`` only what ``pad_input_ids`` returned is taken (``position_ids``, ``mask``), with a
+        2-D ``input_ids``: each row then runs without its padding, and comes back with it.
     eos_token_id: one stop token or several; a sequence ends with its stop token.
     timing: "" | "per-token" | "e2e": also return the seconds of each step, or of the whole call.
     post_iteration_hook(step, logits, tokens, requests): called after every step of a batch.
@@ -134,18 +188,28 @@ def generate(model, input_ids: Prompts, max_seq_len: int = 4096, max_new_tokens:
     their stop token when that is None).
     """
     if num_beams != 1:
-        raise NotImplementedError("generate() does yet not support beam search")
+        raise NotImplementedError("generate() does not support beam search")
     if prepare_model_inputs_hook is not None:
         raise NotImplementedError("prepare_model_inputs_hook: the engine builds the inputs of a step itself")
-    if extra_kwargs:
-        raise NotImplementedError(f"extra_kwargs {sorted(extra_kwargs)}: the engine's step takes no further arguments")
+    extra = {k: v for k, v in (extra_kwargs or {}).items() if v is not None}
+    if set(extra) - {"position_ids", "mask"}:
+        raise NotImplementedError(f"extra_kwargs {sorted(set(extra) - {'position_ids', 'mask'})}: "
+                                  "the engine's step takes no further arguments")
     if not use_cache:
         raise NotImplementedError("generation always uses the cache")
     if timing not in ("", "per-token", "e2e"):
         raise ValueError('timing must be "", "per-token" or "e2e"')
     prompts, kind = _as_lists(input_ids)
+    padded_rows = None
+    if extra:
+        if kind != "2d" or "position_ids" not in extra:
+            raise ValueError("extra_kwargs of pad_input_ids go with its 2-D input_ids and need position_ids")
+        padded_rows = prompts
+        spans = _tokens_of_padded_rows(input_ids, torch.as_tensor(extra["position_ids"]))
+        prompts = [row[a:b] for row, (a, b) in zip(prompts, spans)]
     if not prompts or any(len(p) == 0 for p in prompts):
         raise ValueError("every prompt needs at least one token")
+    given = [len(p) for p in prompts]
     prompts = [p[-max_seq_len:] for p in prompts]
     stop = [] if eos_token_id is None else ([int(eos_token_id)] if isinstance(eos_token_id, int) else list(eos_token_id))
     sampler = Sampler(do_sample, temperature, top_k, seed)
@@ -183,6 +247,8 @@ def generate(model, input_ids: Prompts, max_seq_len: int = 4096, max_new_tokens:
     elif kind == "list":
         out = [torch.tensor(r, dtype=torch.long, device=device) for r in results]
     else:
+        if padded_rows is not None:  # each row as it came, padding and all, and its new tokens behind it
+            results = [row + r[min(n, max_seq_len):] for row, r, n in zip(padded_rows, results, given)]
         longest = max(len(r) for r in results)
         rows = [r + [pad_token_id if pad_token_id is not None else r[-1]] * (longest - len(r)) for r in results]
         out = torch.tensor(rows, dtype=torch.long, device=device)

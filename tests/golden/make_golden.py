@@ -9,6 +9,10 @@ Run once where the reference's sources are present:
 The reference is not pip-installed there, and its ``fms/__init__.py`` asks importlib.metadata for the
 version of "ibm-fms"; only that lookup is patched.  Nothing of the reference is modified or copied.
 tests/test_plain_vs_golden.py compares the plain implementation with the stored file.
+
+Also writes tests/golden/reference_padding.safetensors: what the reference's ``pad_input_ids``
+(fms/utils/generation.py:16-109) returns for the prompts and settings of ``PADDING_CASES``, which
+``fms_b200.utils.generation.pad_input_ids`` has to return too.
 """
 import importlib.metadata as md
 import os
@@ -19,6 +23,30 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(HERE))
+
+
+PADDING_PROMPTS = [[4], [1, 2, 3], [9, 10], [7, 7, 7, 7, 7, 7]]
+# keyword arguments of pad_input_ids, by case
+PADDING_CASES = {
+    "default": {},
+    "min_pad_length": {"min_pad_length": 9},
+    "right": {"padding_side": "right", "pad_token_id": 3},
+    "offset_not_causal": {"position_ids_offset": 2, "is_causal_mask": False, "pad_token_id": 11},
+}
+
+
+def padding_golden():
+    from fms.utils.generation import pad_input_ids
+
+    out = {}
+    for name, kwargs in PADDING_CASES.items():
+        ids, extra = pad_input_ids([torch.tensor(p) for p in PADDING_PROMPTS], **kwargs)
+        out[f"{name}.ids"] = ids.to(torch.int32).contiguous()
+        out[f"{name}.position_ids"] = extra["position_ids"].to(torch.int32).contiguous()
+        mask = extra["mask"]
+        assert ((mask == 0) | (mask == float("-inf"))).all()
+        out[f"{name}.mask_is_zero"] = (mask == 0).to(torch.uint8).contiguous()
+    return out
 
 
 def main(reference_root: str):
@@ -63,6 +91,8 @@ def main(reference_root: str):
             print(which, n, len(prompt), "max|whole - stepped| =", (whole - stepped).abs().max().item())
     save_file(out, os.path.join(HERE, "reference_logits.safetensors"))
     print("wrote", os.path.join(HERE, "reference_logits.safetensors"))
+    save_file(padding_golden(), os.path.join(HERE, "reference_padding.safetensors"))
+    print("wrote", os.path.join(HERE, "reference_padding.safetensors"))
 
 
 if __name__ == "__main__":

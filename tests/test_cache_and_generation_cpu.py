@@ -245,6 +245,48 @@ def test_generate_argument_checks_and_release_on_error(greedy_on_cpu):
     assert len(times) == 1 and out[0].tolist() == [3, 4, 5, 6]  # the prompt was cut to its last 2 tokens
 
 
+def test_padded_rectangle_runs_without_its_padding_and_comes_back_with_it(greedy_on_cpu):
+    """The reference's way with unequal prompts (fms/utils/generation.py:16-109, scripts/inference.py:205-218):
+    pad_input_ids, then generate with what it returned as extra_kwargs."""
+    from fms_b200.utils.generation import generate, pad_input_ids, trim_prefix, truncate_after_eos
+
+    prompts = [torch.tensor([4]), torch.tensor([1, 2, 3]), torch.tensor([9, 10])]
+    ids, extra = pad_input_ids(prompts, min_pad_length=5)
+    assert ids.tolist() == [[0, 0, 0, 0, 4], [0, 0, 1, 2, 3], [0, 0, 0, 9, 10]]
+    assert extra["position_ids"].tolist() == [[0, 0, 0, 0, 0], [0, 0, 0, 1, 2], [0, 0, 0, 0, 1]]
+    m = extra["mask"]
+    assert m.shape == (3, 5, 5) and m.dtype == torch.float32
+    # row 1: its tokens (places 2..4) look at tokens up to themselves, its padding at padding up to itself
+    assert (m[1] == 0).tolist() == [[True, False, False, False, False], [True, True, False, False, False],
+                                    [False, False, True, False, False], [False, False, True, True, False],
+                                    [False, False, True, True, True]]
+    assert torch.isinf(m[1][~(m[1] == 0)]).all()
+
+    e = CountingEngine()
+    out = generate(e, ids, max_new_tokens=4, do_sample=False, eos_token_id=12, extra_kwargs=extra)
+    assert e.steps[0] == ("step", 3, [1, 3, 2])  # only the tokens ran: padding can change no result
+    assert out.tolist() == [[0, 0, 0, 0, 4, 5, 6, 7, 8], [0, 0, 1, 2, 3, 4, 5, 6, 7], [0, 0, 0, 9, 10, 11, 12, 12, 12]]
+    assert truncate_after_eos(trim_prefix(out[2]), 12).tolist() == [9, 10, 11, 12]
+    # the same tokens as from the list of prompts
+    plain = generate(CountingEngine(), prompts, max_new_tokens=4, do_sample=False, eos_token_id=12)
+    assert [trim_prefix(r).tolist()[:len(p)] for r, p in zip(out, plain)] == [p.tolist() for p in plain]
+
+    # padding on the right, an offset, another pad token
+    ids, extra = pad_input_ids(prompts, padding_side="right", position_ids_offset=2, pad_token_id=7, is_causal_mask=False)
+    assert ids.tolist() == [[4, 7, 7], [1, 2, 3], [9, 10, 7]]
+    assert extra["position_ids"].tolist() == [[2, 2, 2], [2, 3, 4], [2, 3, 2]]
+    assert (extra["mask"][2] == 0).tolist() == [[True, True, False], [True, True, False], [False, False, True]]
+    out = generate(CountingEngine(), ids[1:], max_new_tokens=2, do_sample=False,
+                   extra_kwargs={k: v[1:] for k, v in extra.items()})
+    assert out.tolist() == [[1, 2, 3, 4, 5], [9, 10, 7, 11, 12]]
+
+    with pytest.raises(ValueError):  # the mapping belongs to the rectangle it was made with
+        generate(CountingEngine(), prompts, max_new_tokens=1, do_sample=False, extra_kwargs=extra)
+    with pytest.raises(ValueError):
+        generate(CountingEngine(), ids, max_new_tokens=1, do_sample=False,
+                 extra_kwargs={"position_ids": torch.tensor([[0, 5, 1], [0, 1, 2], [0, 1, 0]])})
+
+
 def test_plan_batches_respects_cache_and_slots():
     from fms_b200.utils.generation import plan_batches
 

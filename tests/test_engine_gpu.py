@@ -175,6 +175,15 @@ def test_greedy_generation_through_the_entry_point(models, oracles, which):
     # one prompt alone gives the same tokens as in the batch
     alone = generate(model, torch.tensor(prompts[1]), max_new_tokens=8, do_sample=False)
     assert alone.tolist() == out[1].tolist()
+    # the reference's way with unequal prompts, a padded rectangle: padding changes no token
+    from fms_b200.utils.generation import pad_input_ids, trim_prefix
+
+    pad = max(max(p) for p in prompts) + 1  # an id that no prompt starts with
+    ids, extra = pad_input_ids([torch.tensor(p) for p in prompts], min_pad_length=max(map(len, prompts)) + 7,
+                               pad_token_id=pad)
+    padded = generate(model, ids, max_new_tokens=8, do_sample=False, extra_kwargs=extra)
+    assert padded.shape == (len(prompts), ids.shape[1] + 8)
+    assert [trim_prefix(r, pad).tolist() for r in padded] == [o.tolist() for o in out]
 
 
 def test_sampled_generation_is_the_same_alone_and_in_batches(models, oracles):
@@ -366,8 +375,12 @@ def test_command_line(tiny_folders):
     assert proc.returncode == 0, proc.stderr[-2000:]
     lines = [l for l in proc.stdout.splitlines() if l.strip()]
     oracle = pl.PlainLlama(tiny_folders["a"])
-    assert [[int(x) for x in l.split(",")] for l in lines] == [pl.plain_generate(oracle, p, 6)
-                                                              for p in ([5, 17, 3], [9, 8, 7, 6, 5, 4])]
+    want = [pl.plain_generate(oracle, p, 6) for p in ([5, 17, 3], [9, 8, 7, 6, 5, 4])]
+    assert [[int(x) for x in l.split(",")] for l in lines] == want
+    # with the reference's --min_pad_length the prompts are padded to a rectangle first: the same tokens
+    padded = subprocess.run(proc.args + ["--min_pad_length", "11"], capture_output=True, text=True, timeout=600)
+    assert padded.returncode == 0, padded.stderr[-2000:]
+    assert [[int(x) for x in l.split(",")] for l in padded.stdout.splitlines() if l.strip()] == want
 
 
 def test_bench_line_has_the_keys_of_its_contract():

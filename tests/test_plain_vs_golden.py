@@ -19,6 +19,28 @@ def golden():
     return load_file(GOLDEN)
 
 
+def test_pad_input_ids_returns_what_the_reference_returns():
+    """Not the plain implementation but the library's own helper: it has the reference's signature, so it
+    is held against the reference's stored results (tests/golden/make_golden.py, PADDING_CASES)."""
+    import importlib.util
+    from safetensors.torch import load_file
+
+    from fms_b200.utils.generation import pad_input_ids
+
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(os.path.dirname(GOLDEN), "make_golden.py"))
+    made = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(made)
+    stored = load_file(os.path.join(os.path.dirname(GOLDEN), "reference_padding.safetensors"))
+    for name, kwargs in made.PADDING_CASES.items():
+        ids, extra = pad_input_ids([torch.tensor(p) for p in made.PADDING_PROMPTS], **kwargs)
+        assert ids.dtype == torch.long and extra["position_ids"].dtype == torch.long
+        assert torch.equal(ids.to(torch.int32), stored[f"{name}.ids"]), name
+        assert torch.equal(extra["position_ids"].to(torch.int32), stored[f"{name}.position_ids"]), name
+        zero = extra["mask"] == 0
+        assert torch.equal(zero.to(torch.uint8), stored[f"{name}.mask_is_zero"]), name
+        assert torch.isinf(extra["mask"][~zero]).all() and (extra["mask"][~zero] < 0).all()
+
+
 @pytest.mark.parametrize("which", ["a", "b", "c"])
 def test_weights_are_the_ones_the_golden_was_made_with(golden, which):
     cfg, seed, gain_dtype = TINY[which]
