@@ -19,6 +19,20 @@ class BaseTokenizer:
     def decode(self, ids, skip_special_tokens: bool = True) -> str:
         raise NotImplementedError
 
+    # The older four calls of the reference's tokenizers (fms/utils/tokenizers.py:66-91), which its scripts
+    # still use: text -> token strings -> ids and back.
+    def tokenize(self, text: str) -> List[str]:
+        raise NotImplementedError
+
+    def convert_tokens_to_ids(self, tokens):
+        raise NotImplementedError
+
+    def convert_ids_to_tokens(self, ids) -> List[str]:
+        raise NotImplementedError
+
+    def convert_tokens_to_string(self, tokens: List[str]) -> str:
+        raise NotImplementedError
+
     def vocab_size(self) -> int:
         raise NotImplementedError
 
@@ -26,6 +40,25 @@ class BaseTokenizer:
 class CharTokenizer(BaseTokenizer):
     def __init__(self) -> None:
         super().__init__(2, 3)
+
+    def tokenize(self, text: str) -> List[str]:
+        return list(text)
+
+    def convert_tokens_to_ids(self, tokens):
+        def one(t: str) -> int:
+            return ord(t) if len(t) == 1 and ord(t) < 256 else 0
+
+        if isinstance(tokens, str):  # one token gives one id
+            if len(tokens) != 1:
+                raise RuntimeError("a token of the character tokenizer is one character")
+            return one(tokens)
+        return [one(t) for t in tokens]
+
+    def convert_ids_to_tokens(self, ids) -> List[str]:
+        return [chr(int(i)) for i in ids]
+
+    def convert_tokens_to_string(self, tokens: List[str]) -> str:
+        return "".join(tokens)
 
     def encode(self, text: str, add_special_tokens: bool = False) -> List[int]:
         ids = [ord(ch) if ord(ch) < 256 else 0 for ch in text]
@@ -46,9 +79,11 @@ class JsonTokenizer(BaseTokenizer):
         from tokenizers import Tokenizer  # optional dependency
 
         self._tok = Tokenizer.from_file(path)
-        bos = self._tok.token_to_id("<s>") or self._tok.token_to_id("<|begin_of_text|>") or 1
-        eos = self._tok.token_to_id("</s>") or self._tok.token_to_id("<|end_of_text|>") or 2
-        super().__init__(bos, eos)
+        def first_id(names, default):  # an id may be 0: compare with None, not by truth
+            found = [i for i in (self._tok.token_to_id(n) for n in names) if i is not None]
+            return found[0] if found else default
+
+        super().__init__(first_id(("<s>", "<|begin_of_text|>"), 1), first_id(("</s>", "<|end_of_text|>"), 2))
 
     def encode(self, text: str, add_special_tokens: bool = False) -> List[int]:
         ids = self._tok.encode(text, add_special_tokens=False).ids
@@ -56,6 +91,20 @@ class JsonTokenizer(BaseTokenizer):
 
     def decode(self, ids, skip_special_tokens: bool = True) -> str:
         return self._tok.decode([int(i) for i in ids], skip_special_tokens=skip_special_tokens)
+
+    def tokenize(self, text: str) -> List[str]:
+        return self._tok.encode(text, add_special_tokens=False).tokens
+
+    def convert_tokens_to_ids(self, tokens):
+        if isinstance(tokens, str):
+            return self._tok.token_to_id(tokens)
+        return [self._tok.token_to_id(t) for t in tokens]
+
+    def convert_ids_to_tokens(self, ids) -> List[str]:
+        return [self._tok.id_to_token(int(i)) for i in ids]
+
+    def convert_tokens_to_string(self, tokens: List[str]) -> str:
+        return self.decode(self.convert_tokens_to_ids(tokens), skip_special_tokens=False)
 
     def vocab_size(self) -> int:
         return self._tok.get_vocab_size()

@@ -311,12 +311,36 @@ def test_helpers_and_tokenizer_and_parser():
     assert isinstance(t, CharTokenizer) and t.vocab_size() == 256 and (t.bos_token_id, t.eos_token_id) == (2, 3)
     ids = t.encode("héllo", add_special_tokens=True)
     assert ids == [2, 104, 233, 108, 108, 111] and t.decode(ids + [3]) == "héllo"
+    # the older calls that the reference's scripts use (scripts/inference.py:178-186, :232-236)
+    tokens = t.tokenize("héllo")
+    assert tokens == list("héllo") and t.convert_tokens_to_ids(tokens) == ids[1:] and t.convert_tokens_to_ids("h") == 104
+    assert t.convert_tokens_to_ids(["ab", "\u4e2d"]) == [0, 0]  # what is no single character below 256 becomes 0
+    assert t.convert_tokens_to_string(t.convert_ids_to_tokens(torch.tensor(ids[1:]))) == "héllo"
     with pytest.raises(ValueError):
         get_tokenizer("/no/such/tokenizer")
     args = build_parser().parse_args(["--variant", "micro", "--prompt", "a", "--prompt", "b", "--batch_input",
                                       "--default_dtype", "fp32", "--max_new_tokens", "7"])
     assert args.prompt == ["a", "b"] and args.batch_input and args.default_dtype == "fp32" and args.max_new_tokens == 7
-    assert args.device_type == "cuda" and args.architecture == "llama" and args.top_k == 10
+    assert args.device_type == "cuda" and args.architecture == "llama" and args.top_k == 10 and args.min_pad_length == 0
+
+
+def test_tokenizer_json_folder(tmp_path):
+    tokenizers = pytest.importorskip("tokenizers")
+    from tokenizers.models import WordLevel
+    from tokenizers.pre_tokenizers import Whitespace
+
+    from fms_b200.utils.tokenizers import JsonTokenizer, get_tokenizer
+
+    vocab = {"<s>": 0, "</s>": 1, "<unk>": 2, "a": 3, "cat": 4, "sat": 5}
+    tok = tokenizers.Tokenizer(WordLevel(vocab, unk_token="<unk>"))
+    tok.pre_tokenizer = Whitespace()
+    tok.save(str(tmp_path / "tokenizer.json"))
+    t = get_tokenizer(str(tmp_path))
+    assert isinstance(t, JsonTokenizer) and t.vocab_size() == 6 and (t.bos_token_id, t.eos_token_id) == (0, 1)
+    assert t.encode("a cat sat") == [3, 4, 5] and t.encode("a dog", add_special_tokens=True) == [0, 3, 2]
+    assert t.tokenize("cat sat") == ["cat", "sat"] and t.convert_tokens_to_ids(["cat", "sat"]) == [4, 5]
+    assert t.convert_ids_to_tokens([5, 3]) == ["sat", "a"] and t.convert_tokens_to_ids("a") == 3
+    assert t.decode([3, 4]).split() == ["a", "cat"]
 
 
 def test_sampler_arguments():
