@@ -5,6 +5,7 @@ tokens of a sequence; generation through the entry point; the replay program."""
 import io
 import json
 import os
+import select
 import subprocess
 import sys
 
@@ -261,6 +262,36 @@ def test_trace_run_program(tiny_folders, oracles, tmp_path, dtype):
         assert o == data.shape[0]
     for i, r in enumerate(reqs):
         close(torch.cat(got[i]), oracles["b"].logits(r), "fp32" if dtype == "float32" else "bf16")
+
+
+def test_trace_run_answers_each_step_before_the_next_is_written(tiny_folders, oracles, tmp_path):
+    """The caller writes a step only after ``done`` of the step before: the program must not wait for more
+    input before it runs a line, and must have written the step's file when it says ``done``."""
+    import numpy as np
+
+    req = tiny_prompts("a")[2]
+    vocab = TINY["a"][0]["vocab_size"]
+    proc = subprocess.Popen(
+        [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", tiny_folders["a"], "--dtype", "float32",
+         "--out", str(tmp_path), "--max-tokens", "64"], stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
+    try:
+        want = oracles["a"].logits(req)
+        cut = len(req) - 3
+        steps = [{"step": 0, "entries": [{"id": "x", "tokens": req[:cut], "want": [cut - 1]}], "end": []}]
+        steps += [{"step": k + 1, "entries": [{"id": "x", "tokens": [req[cut + k]], "want": [0]}],
+                   "end": ["x"] if cut + k == len(req) - 1 else []} for k in range(3)]
+        for k, step in enumerate(steps):
+            proc.stdin.write(json.dumps(step) + "\n")
+            proc.stdin.flush()
+            assert select.select([proc.stdout], [], [], 600)[0], f"no answer to step {k}"
+            assert proc.stdout.readline().split() == ["done", str(k)]
+            got = torch.from_numpy(np.fromfile(tmp_path / f"{k}.f32", dtype="<f4").reshape(-1, vocab).copy())
+            close(got, want[cut - 1 + k][None], "fp32")
+        proc.stdin.close()
+        assert proc.wait(timeout=120) == 0
+    finally:
+        if proc.poll() is None:
+            proc.kill()
 
 
 def test_head_size_128_model_bfloat16_against_float32(tmp_path):
