@@ -164,6 +164,38 @@ def test_first_tokens_of_a_sequence(models, oracles, which, dtype):
     close(lg, torch.cat([want[:1], want[:2]]), dtype)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which", ["b", "c"])
+def test_prompts_cut_into_steps_of_several_tokens(models, oracles, which, dtype):
+    """Two requests whose tokens come in pieces of unequal sizes (several tokens onto what is already cached,
+    across the edges of cache blocks, one request resting while the other goes on): the same logits as whole.
+    The reference needs an explicit mask for this (fms/modules/attention.py:268-271); here a row sees the
+    cached positions up to its own."""
+    engine = models(which, dtype).new_engine(max_tokens=2048)
+    reqs = long_requests(which, 5)[1:3]
+    want = [oracles[which].logits(r) for r in reqs]
+    slots = engine.begin(2)
+    got = [[], []]
+    at = [0, 0]
+    pieces = [(7, 3), (1, 62), (57, 0), (0, 1), (10 ** 6, 10 ** 6)]  # (tokens of request 0, of request 1) a step
+    for piece in pieces:
+        who = [i for i in (0, 1) if piece[i] and at[i] < len(reqs[i])]
+        if not who:
+            continue
+        toks = [reqs[i][at[i]:at[i] + piece[i]] for i in who]
+        lg = engine.step([slots[i] for i in who], toks, [list(range(len(t))) for t in toks])
+        o = 0
+        for i, t in zip(who, toks):
+            got[i].append(lg[o:o + len(t)])
+            o += len(t)
+            at[i] += len(t)
+    engine.release(slots)
+    engine.check()
+    for i in (0, 1):
+        assert at[i] == len(reqs[i])
+        close(torch.cat(got[i]), want[i], dtype)
+
+
 @pytest.mark.parametrize("which", ["a", "b"])
 def test_greedy_generation_through_the_entry_point(models, oracles, which):
     from fms_b200.utils.generation import generate
