@@ -71,6 +71,11 @@ def test_registry():
     assert m.config.nlayers == 1 and m.config.emb_dim == 192
     with pytest.raises(NotImplementedError):  # the reference's parameters for several devices: one GPU here
         models.get_model("llama", "micro", device_type="cpu", distributed_strategy="tp")
+    # a head size that the kernels do not take is refused when the model is built, in words
+    with pytest.raises(ValueError, match="head size 24 is not supported: a multiple of 16 up to 256"):
+        models.get_model("llama", "micro", device_type="cpu", data_type="fp32", nlayers=1, emb_dim=72, nheads=3)
+    with pytest.raises(ValueError, match="head size 512"):
+        models.get_model("llama", "micro", device_type="cpu", data_type="fp32", nlayers=1, emb_dim=1024, nheads=2)
 
 
 def test_state_dict_names_are_the_references(tmp_path):

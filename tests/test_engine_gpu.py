@@ -326,6 +326,49 @@ def test_trace_run_answers_each_step_before_the_next_is_written(tiny_folders, or
             proc.kill()
 
 
+FURTHER_MODELS = {
+    # biases on every projection, a tied head, eps 1e-3, a feed-forward width that is no multiple of 8
+    "biases_tied_hd16": (dict(vocab=97, hidden=48, intermediate=100, layers=1, heads=3, kvheads=3, eps=1e-3, tied=True,
+                              attention_bias=True, mlp_bias=True), [5, 70, 33]),
+    # one kv head for five, an odd feed-forward width, the llama3 rescaling of the rotation's frequencies
+    "mqa_f173_llama3": (dict(vocab=1000, hidden=160, intermediate=173, layers=2, heads=5, kvheads=1, theta=5e5, context=2048,
+                             rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                           "high_freq_factor": 4.0, "original_max_position_embeddings": 64}),
+                        [300, 65, 1]),
+    # seven query heads a kv head (no whole tile of eight), head size 80
+    "group7_hd80": (dict(vocab=129, hidden=560, intermediate=96, layers=1, heads=7, kvheads=1), [64, 65, 200]),
+    # the largest head size, a feed-forward of 8
+    "hd256_f8": (dict(vocab=50, hidden=512, intermediate=8, layers=1, heads=2, kvheads=1), [40]),
+    # prompts of more than 1,024 rows (the tcgen05 product) with a k of 1,016 and biases in its epilogue
+    "tc_k1016_biases": (dict(vocab=300, hidden=1024, intermediate=1016, layers=1, heads=16, kvheads=4, context=2048,
+                             attention_bias=True, mlp_bias=True), [1030, 20]),
+}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(FURTHER_MODELS))
+def test_further_configurations_against_the_plain_implementation(tmp_path, name, dtype):
+    """Sizes and options that the tiny models do not have: the prompts in one step, then four tokens one by one."""
+    from fms_b200.models import get_model
+    from tiny_models import llama_config, tiny_tensors_with_biases, write_folder
+
+    sizes, lengths = FURTHER_MODELS[name]
+    cfg = llama_config(**sizes)
+    folder = write_folder(str(tmp_path / name), cfg, tiny_tensors_with_biases(cfg, 7))
+    oracle = pl.PlainLlama(folder)
+    g = torch.Generator().manual_seed(3)
+    reqs = [torch.randint(0, cfg["vocab_size"], (n + 4,), generator=g).tolist() for n in lengths]
+    want = torch.cat([oracle.logits(r)[-5:] for r in reqs])
+    engine = get_model("hf_pretrained", model_path=folder, device_type="cuda", data_type=dtype).new_engine(4096)
+    slots = engine.begin(len(reqs))
+    rows = [engine.step(slots, [r[:-4] for r in reqs]).cpu()]
+    for t in range(4, 0, -1):
+        rows.append(engine.step(slots, [[r[-t]] for r in reqs]).cpu())
+    engine.release(slots)
+    engine.check()
+    close(torch.stack(rows, 1).reshape(-1, cfg["vocab_size"]), want, dtype)
+
+
 def test_head_size_128_model_bfloat16_against_float32(tmp_path):
     """A model with the head size, group size and widths (in small) of the benchmark's: prompts long enough for
     the tcgen05 product (1,024 rows and more in one step), decode through the weight-streaming product and the CUDA graph.

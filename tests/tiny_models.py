@@ -108,6 +108,36 @@ def tiny_tensors(cfg: dict, seed: int, gain_dtype: torch.dtype = torch.bfloat16,
     return t
 
 
+def llama_config(vocab, hidden, intermediate, layers, heads, kvheads, eps=1e-5, theta=1e4, context=512, tied=False,
+                 attention_bias=False, mlp_bias=False, rope_scaling=None) -> dict:
+    """A config.json of further sizes and options, for tests that make their own model."""
+    cfg = dict(TINY_A, vocab_size=vocab, hidden_size=hidden, intermediate_size=intermediate, num_hidden_layers=layers,
+               num_attention_heads=heads, num_key_value_heads=kvheads, rms_norm_eps=eps, rope_theta=theta,
+               max_position_embeddings=context, tie_word_embeddings=tied, attention_bias=attention_bias,
+               mlp_bias=mlp_bias)
+    if rope_scaling:
+        cfg["rope_scaling"] = rope_scaling
+    return cfg
+
+
+def tiny_tensors_with_biases(cfg: dict, seed: int) -> dict:
+    """``tiny_tensors`` and, where the configuration asks for them, biases ~ N(0, 0.1) of the projections."""
+    t = tiny_tensors(cfg, seed, torch.float32)
+    g = torch.Generator(device="cpu")
+    g.manual_seed(seed + 99)
+    d, h, kv, f = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["intermediate_size"]
+    hd = d // h
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        if cfg.get("attention_bias"):
+            for name, rows in (("q_proj", h * hd), ("k_proj", kv * hd), ("v_proj", kv * hd), ("o_proj", d)):
+                t[p + f"self_attn.{name}.bias"] = (torch.randn(rows, generator=g) * 0.1).to(torch.bfloat16)
+        if cfg.get("mlp_bias"):
+            for name, rows in (("gate_proj", f), ("up_proj", f), ("down_proj", d)):
+                t[p + f"mlp.{name}.bias"] = (torch.randn(rows, generator=g) * 0.1).to(torch.bfloat16)
+    return t
+
+
 def write_folder(path: str, cfg: dict, tensors: dict) -> str:
     from safetensors.torch import save_file
 
