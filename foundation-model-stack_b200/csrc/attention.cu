@@ -2,18 +2,22 @@
 // compile time: the library is built once per head size a model needs).  (fms/modules/attention.py:215-294 is
 // the formula.)  This file holds the float32 kernels (all arithmetic in float32 on the CUDA cores), the merge of
 // decode splits and the entry points; the bfloat16 kernels are in attention_mma.cuh (mma.sync: prefill for any
-// head size, decode) and attention_tc.cuh (tcgen05: prefill for head sizes 64 and 128).
+// head size, decode), attention_tc.cuh (tcgen05: prefill for head sizes 64 and 128) and attention_stream.cuh
+// (decode with much to read, head sizes 64 and 128: persistent warps fed by TMA).
 //
 //   prefill:  any number of new tokens per sequence; the query at position p sees cached positions
 //             max(0, p - window + 1)..p.  Keys and values of the new tokens are already in the cache.
 //   decode:   one query per sequence; the keys are cut into splits of 256 positions (a fixed size, so
 //             that a sequence's arithmetic depends on its own length only), one thread block per
-//             (sequence, key/value head, split), then a second kernel combines the splits.
+//             (sequence, key/value head, split) or, with much to read, persistent warps that draw such
+//             units from a counter; then a second kernel combines the splits.
 //
 // Cache layout: keys, values [blocks, kv_heads, 64, HEAD_DIM]; table[slot, p / 64] is the block of
 // position p.  Rows of a block beyond the sequence's length hold garbage and are never used: masked
 // scores are set to -inf by selection and their values are skipped or zeroed, not multiplied by 0.
 #include <cuda.h>
+
+#include <algorithm>
 
 #include "common.cuh"
 
@@ -321,9 +325,11 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, float* __r
 
 template <typename T>
 __global__ void attn_combine_kernel(AttnArgs a, const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    int n_splits) {
+                                    int n_splits, int* __restrict__ reset = nullptr) {
   pdl_launch_dependents();
   pdl_wait();
+  // the kernel before this one is done: its work counter (if it has one) is put back for the next launch
+  if (reset != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *reset = 0;
   const int seq = blockIdx.x, head = blockIdx.y;
   const int len = a.len_after[seq];
   const int pos = len - 1;
@@ -349,6 +355,7 @@ __global__ void attn_combine_kernel(AttnArgs a, const float* __restrict__ part_o
 #if HEAD_DIM == 64 || HEAD_DIM == 128
 #define FMS_ATTENTION_TC 1
 #include "attention_tc.cuh"
+#include "attention_stream.cuh"
 #else
 #define FMS_ATTENTION_TC 0
 #endif
@@ -374,8 +381,31 @@ int check_args(const char* what, int nheads, int kvheads, int head_dim, int bloc
 
 // Launches the decode kernels (splits, then combine) with the given scratch.  float32: CUDA-core kernel;
 // bfloat16: tensor-core kernel.  Both entry points below go through here.
+#if FMS_ATTENTION_TC
+constexpr long STREAM_FROM_BLOCKS = 1800;  // cache blocks of 64 keys (times kv heads) from which decode streams
+// whether decode steps with much to read take the streaming kernel (FMS_B200_ATTN_STREAM=0 turns it off)
+bool decode_streams() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("FMS_B200_ATTN_STREAM");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+int multiprocessors() {
+  static int n = 0;
+  if (n == 0) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0)
+      n = 148;
+  }
+  return n;
+}
+#endif
+
 int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, int n_splits, float* part_o,
-                  float* part_ml, int pool_blocks, cudaStream_t stream) {
+                  float* part_ml, int pool_blocks, long total_len, int* work_counter, int* error_flag, cudaStream_t stream) {
   if (n_splits <= 0 || n_splits > 65535) return fms_fail("%s: %d splits", what, n_splits);
   const int group = a.nheads / a.kvheads;
   if (a.nheads > 65535) return fms_fail("%s: %d heads", what, a.nheads);
@@ -384,13 +414,38 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
     fms_launch(attn_decode_kernel<float>, dim3(n_seqs, a.kvheads * chunks, n_splits), dim3(128), 0, stream, a, part_o,
                part_ml, n_splits);
     fms_launch(attn_combine_kernel<float>, dim3(n_seqs, a.nheads), dim3(HD >= 128 ? 128 : 64), 0, stream, a,
-               (const float*)part_o, (const float*)part_ml, n_splits);
+               (const float*)part_o, (const float*)part_ml, n_splits, (int*)nullptr);
   } else if (dtype == FMS_BF16) {
     // Few (sequence, kv head) pairs: four warps share a split, each with one block of 64 keys in flight, which
     // is quickest when the GPU is not full.  Many: one warp per block with a small footprint, so that several
     // blocks of threads fit on a multiprocessor and one's loads overlap another's arithmetic.
     const int chunks = (group + GROWS - 1) / GROWS;
     const long units = (long)n_seqs * a.kvheads * chunks;
+#if FMS_ATTENTION_TC
+    // Much to read (measured: from about 60 MB of keys and values on, whatever the batch): bytes decide, and
+    // persistent warps that keep their requests in flight across the units stream them quickest.  Below that a
+    // block of threads per unit, with its early hints, has the shorter chain.
+    const long key_blocks = (long)(total_len / BLK) * a.kvheads * chunks;  // what the launch will read, in cache blocks
+    if (key_blocks >= STREAM_FROM_BLOCKS && n_splits > 1 && pool_blocks > 0 && work_counter != nullptr && error_flag != nullptr &&
+        units * n_splits < 0x40000000L && decode_streams()) {
+      CUtensorMap map_k, map_v;
+      const long rows = (long)pool_blocks * a.kvheads * BLK;
+      if (make_map(&map_k, a.keys, rows, HD, BLK) || make_map(&map_v, a.values, rows, HD, BLK)) return 1;
+      static bool configured_stream = false;
+      if (!configured_stream) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SR_SMEM);
+        if (e != cudaSuccess) return fms_fail("%s: %zu bytes of shared memory refused: %s", what, SR_SMEM, cudaGetErrorString(e));
+        configured_stream = true;
+      }
+      const long all_units = units * n_splits;
+      const int blocks = (int)std::min<long>(multiprocessors(), (all_units + SR_WARPS - 1) / SR_WARPS);
+      fms_launch(attn_decode_stream_kernel, dim3(blocks), dim3((SR_WARPS + 1) * 32), SR_SMEM, stream, map_k, map_v, a,
+                 part_o, part_ml, n_seqs, n_splits, work_counter, error_flag);
+      fms_launch(attn_combine_kernel<__nv_bfloat16>, dim3(n_seqs, a.nheads), dim3(HD >= 128 ? 128 : 64), 0, stream, a,
+                 (const float*)part_o, (const float*)part_ml, n_splits, work_counter);
+      return fms_launch_status(what);
+    }
+#endif
     const int nw = units >= 512 ? 1 : (units >= 192 ? 2 : 4);
     const size_t smem = (size_t)nw * BLK * ROWB;
     auto kernel = nw == 1 ? attn_decode_mma_kernel<1> : (nw == 2 ? attn_decode_mma_kernel<2> : attn_decode_mma_kernel<4>);
@@ -406,7 +461,7 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
                n_splits, nw == 4 ? pool_blocks : 0);
     if (n_splits > 1)  // with one split the kernel above has written the result itself
       fms_launch(attn_combine_kernel<__nv_bfloat16>, dim3(n_seqs, a.nheads), dim3(HD >= 128 ? 128 : 64), 0, stream, a,
-                 (const float*)part_o, (const float*)part_ml, n_splits);
+                 (const float*)part_o, (const float*)part_ml, n_splits, (int*)nullptr);
   } else {
     return fms_fail("%s: unsupported dtype code %d", what, dtype);
   }
@@ -485,17 +540,20 @@ FMS_API int fms_attention_prefill(const void* q, void* out, int dtype, const voi
 }
 
 // part_o: float [seqs, nheads, n_splits, HD]; part_ml: float [seqs, nheads, n_splits, 2]; both scratch.
-// pool_blocks: blocks in the cache (bounds the early L2 hints; 0 turns them off).
+// pool_blocks: blocks in the cache (bounds the early L2 hints and the streaming kernel's tensor maps; 0 turns both
+// off).  total_len: cached tokens of all sequences together as far as the host knows (0: unknown), by which the
+// kernel is chosen.  work_counter: one int that is 0 between launches, from which the streaming kernel's warps draw their
+// units; error_flag: where a kernel records that a wait ran out (either null: the streaming kernel is not used).
 FMS_API int fms_attention_decode(const void* q, void* out, int dtype, const void* keys, const void* values,
                                  const int* table, int table_stride, int block_tokens, const int* slots,
                                  const int* first_row, const int* len_after, int n_seqs, int n_splits, float* part_o,
                                  float* part_ml, int nheads, int kvheads, int head_dim, float scale, int window,
-                                 int pool_blocks, cudaStream_t stream) {
+                                 int pool_blocks, long total_len, int* work_counter, int* error_flag, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (check_args("attention_decode", nheads, kvheads, head_dim, block_tokens)) return 1;
   if (!(scale > 0.f)) return fms_fail("attention_decode: the scale of the scores is %g; it must be positive", (double)scale);
   AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window};
-  return launch_decode("attention_decode", a, dtype, n_seqs, n_splits, part_o, part_ml, pool_blocks, stream);
+  return launch_decode("attention_decode", a, dtype, n_seqs, n_splits, part_o, part_ml, pool_blocks, total_len, work_counter, error_flag, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -554,5 +612,5 @@ FMS_API int fms_attention_decode_no_alloc(const void* q, void* out, int dtype, c
   float* part_o = scratch;                  // [seqs, nheads, n_splits, HD]
   float* part_ml = scratch + entries * HD;  // [seqs, nheads, n_splits, 2]
   AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window};
-  return launch_decode("attention_decode_no_alloc", a, dtype, n_seqs, n_splits, part_o, part_ml, 0, stream);
+  return launch_decode("attention_decode_no_alloc", a, dtype, n_seqs, n_splits, part_o, part_ml, 0, 0, nullptr, nullptr, stream);
 }

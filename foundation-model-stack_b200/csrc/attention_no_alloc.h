@@ -8,7 +8,8 @@
 //
 // fms_attention_decode (attention.cu) needs scratch memory for the partial results of its key splits and
 // expects the caller to provide it.  fms_attention_decode_no_alloc is the same computation — the same two
-// kernels, the same launch shapes, bit-identical results — but takes its scratch from an array that is
+// kernels, the same launch shapes, bit-identical results (as long as fms_attention_decode is not given what lets
+// it pick its streaming kernel) — but takes its scratch from an array that is
 // part of the library image itself:
 //
 //     static __device__ __align__(256) unsigned char g_decode_scratch[FMS_NO_ALLOC_SCRATCH_BYTES];
@@ -29,8 +30,9 @@
 // same call.  Two calls whose kernels can overlap on the GPU (different streams without an ordering
 // between them, or several host threads) race on the array; serialise them.
 //
-// Arguments are those of fms_attention_decode without the two scratch pointers; inputs and outputs are
-// still the caller's.  Returns 0, or non-zero with the reason in fms_last_error().
+// Arguments are those of fms_attention_decode without the two scratch pointers and without what only its
+// streaming kernel needs (the pool size, the total length, a work counter, the error flag): this entry point
+// always takes the kernels with one block of threads per split.  Inputs and outputs are still the caller's.  Returns 0, or non-zero with the reason in fms_last_error().
 #pragma once
 
 #include <cuda_runtime.h>

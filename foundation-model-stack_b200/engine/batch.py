@@ -24,6 +24,7 @@ class Batch:
         self.decode = False  # every sequence brings exactly one token
         self.max_new = 0  # most tokens any sequence brings
         self.max_len_after = 0  # longest sequence after the step (host value; capacity when unknown)
+        self.total_len = 0  # tokens of all sequences after the step, as far as the host knows (kernels are chosen by it)
         self.num_new: List[int] = []
         self.tokens: Optional[torch.Tensor] = None  # [n_tokens] int32
         self.positions: Optional[torch.Tensor] = None  # [n_tokens] int32
@@ -45,6 +46,7 @@ class Batch:
         b.max_new = max(b.num_new)
         b.decode = b.max_new == 1
         b.max_len_after = max(lb + n for lb, n in zip(len_before, b.num_new))
+        b.total_len = sum(len_before) + b.n_tokens
         flat, pos, seq, first, rows = [], [], [], [0], []
         for i, (lb, t, w) in enumerate(zip(len_before, tokens, want)):
             base = first[-1]

@@ -165,6 +165,7 @@ class Engine:
                 if buf.copied is None:
                     buf.copied = torch.cuda.Event()
                 buf.copied.record()
+        buf.batch.total_len = sum(lengths) + n  # read when a graph is captured: the lengths only grow from here
         logits = self._run_decode(buf, max(max(lengths) + 1, min(int(horizon), self.cache.max_positions)))
         self.cache.commit(slots, [1] * n)
         buf.lengths = [x + 1 for x in lengths]

@@ -21,7 +21,7 @@ import torch
 from .build import load_library
 
 F32, BF16 = 0, 1
-_P, _I, _F, _U64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_ulonglong
+_P, _I, _F, _U64, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_ulonglong, ctypes.c_long
 
 _SIGNATURES = {
     "fms_embed_rows": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
@@ -37,7 +37,7 @@ _SIGNATURES = {
     "fms_argmax": [_P, _P, _I, _I, _P],
     "fms_sample": [_P, _P, _I, _I, _F, _I, _U64, _P, _I, _P],
     "fms_attention_prefill": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P],
-    "fms_attention_decode": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _F, _I, _I, _P],
+    "fms_attention_decode": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _F, _I, _I, _L, _P, _P, _P],
 }
 _functions = {}
 # kernels launched through this module since import (a decode-attention call over several splits launches two)
@@ -104,6 +104,24 @@ def error_flag(device) -> torch.Tensor:
     return _error_flags[key]
 
 
+_work_counters = {}
+WORK_COUNTERS = 4096
+
+
+def _work_counter(device) -> torch.Tensor:
+    """An int32 on the device that is 0 between launches: the persistent decode-attention kernel's warps draw
+    their units from it, and the kernel that merges the splits puts it back.  Every call hands out the next of
+    4,096, so that launches in flight at the same time (other streams, the launches inside captured graphs) do
+    not share one."""
+    device = torch.device(device)
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    if key not in _work_counters:
+        _work_counters[key] = [torch.zeros(WORK_COUNTERS, dtype=torch.int32, device=device), 0]
+    entry = _work_counters[key]
+    entry[1] = (entry[1] + 1) % WORK_COUNTERS
+    return entry[0][entry[1]:entry[1] + 1]
+
+
 def check_error_flag(device) -> None:
     flag = error_flag(device)
     v = int(flag.item())
@@ -111,7 +129,7 @@ def check_error_flag(device) -> None:
         flag.zero_()
         raise KernelError({1: "a token id outside the vocabulary reached the embedding",
                            2: "a token's position has no cache block",
-                           4: "the tensor-core product gave up waiting for a copy or for the tensor cores"}.get(v, f"device error flag {v}"))
+                           4: "a kernel gave up waiting for a copy or for the tensor cores"}.get(v, f"device error flag {v}"))
 
 
 # ---- embedding ---------------------------------------------------------------------------------------
@@ -281,7 +299,8 @@ def attention(q: torch.Tensor, batch, view, nheads: int, kvheads: int, head_dim:
         part_o = torch.empty((batch.n_seqs, nheads, n_splits, head_dim), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((batch.n_seqs, nheads, n_splits, 2), dtype=torch.float32, device=q.device)
         _call(lib, "fms_attention_decode", *common, batch.n_seqs, n_splits, _ptr(part_o), _ptr(part_ml), nheads,
-              kvheads, head_dim, float(scale), int(window), view.keys.shape[0], _stream())
+              kvheads, head_dim, float(scale), int(window), view.keys.shape[0], int(getattr(batch, "total_len", 0)), _ptr(_work_counter(q.device)),
+              _ptr(error_flag(q.device)), _stream())
         if n_splits > 1 or q.dtype == torch.float32:
             global launches
             launches += 1  # the kernel that merges the splits

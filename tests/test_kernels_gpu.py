@@ -381,6 +381,40 @@ def test_decode_attention_at_every_batch_size(ops, n_seqs, kvheads):
     torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
 
 
+@pytest.mark.parametrize("n_seqs,nheads,kvheads,hd,window", [
+    (70, 32, 8, 128, 0),     # the benchmark's head layout
+    (40, 48, 16, 64, 100),   # a window: blocks behind it given back, first blocks cut on the left
+    (66, 24, 8, 64, 0),      # three query heads a kv head: five of the tile's eight columns idle
+    (33, 160, 16, 128, 0),   # ten query heads a kv head: two chunks of columns
+    (600, 2, 1, 64, 0),      # more sequences than the persistent warps: several units each, unequal
+])
+def test_decode_attention_of_many_sequences_streams_the_cache(ops, n_seqs, nheads, kvheads, hd, window):
+    """From 512 (sequence, kv head) pairs on, decode attention is a persistent kernel that streams whole cache
+    blocks through shared memory with TMA.  Everything that is no live position is NaN: a block's rows beyond the
+    sequence are copied too and must not reach the result.  One far key stands out in a long sequence."""
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(21)
+    lens = [int(v) for v in torch.randint(1, 700, (n_seqs,), generator=g)]
+    lens[0], lens[1], lens[2] = 699, 256, 1
+    cache, view, batch = make_cache_case(dtype, nheads, kvheads, hd, lens, [1] * n_seqs, 16, window)
+    qkv = torch.randn(n_seqs, (nheads + 2 * kvheads) * hd, generator=g).to(dtype).cuda()
+    q = ops.rope_store(qkv, None, batch, view, nheads, kvheads, hd)
+    group = nheads // kvheads
+    head = nheads - 1
+    far = 650 if window == 0 else 640
+    table = cache.groups[0].table_host
+    blk = int(table[int(batch.slots[0]), far // 64])
+    view.keys[blk, head // group, far % 64] = (q[0, head * hd:(head + 1) * hd].float() * 6).to(dtype)
+    view.values[blk, head // group, far % 64] = torch.full((hd,), 2.0).to(dtype).cuda()
+    scale = 1.0 / math.sqrt(hd)
+    got = ops.attention(q, batch, view, nheads, kvheads, hd, scale, window)
+    ops.check_error_flag("cuda")
+    want = P.attention(q, batch, view, nheads, kvheads, hd, scale, window)
+    assert not torch.isnan(got).any()
+    torch.testing.assert_close(got[0, head * hd:(head + 1) * hd].float(), torch.full((hd,), 2.0).cuda(), atol=5e-2, rtol=0)
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+
+
 def test_kernels_report_what_the_host_should_have_prevented(ops):
     """A token id outside the vocabulary and a position without a cache block do not fault: the kernel leaves the
     row alone, sets the error flag, and the host's check raises (and clears the flag)."""
