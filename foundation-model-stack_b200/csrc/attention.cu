@@ -381,6 +381,7 @@ int check_args(const char* what, int nheads, int kvheads, int head_dim, int bloc
 
 // Launches the decode kernels (splits, then combine) with the given scratch.  float32: CUDA-core kernel;
 // bfloat16: tensor-core kernel.  Both entry points below go through here.
+long g_stream_launches = 0;  // launches (or captures) of the streaming decode kernel by this process, for tests
 #if FMS_ATTENTION_TC
 constexpr long STREAM_FROM_BLOCKS = 1800;  // cache blocks of 64 keys (times kv heads) from which decode streams
 // whether decode steps with much to read take the streaming kernel (FMS_B200_ATTN_STREAM=0 turns it off)
@@ -439,6 +440,7 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
       }
       const long all_units = units * n_splits;
       const int blocks = (int)std::min<long>(multiprocessors(), (all_units + SR_WARPS - 1) / SR_WARPS);
+      ++g_stream_launches;
       fms_launch(attn_decode_stream_kernel, dim3(blocks), dim3((SR_WARPS + 1) * 32), SR_SMEM, stream, map_k, map_v, a,
                  part_o, part_ml, n_seqs, n_splits, work_counter, error_flag);
       fms_launch(attn_combine_kernel<__nv_bfloat16>, dim3(n_seqs, a.nheads), dim3(HD >= 128 ? 128 : 64), 0, stream, a,
@@ -470,6 +472,7 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
 }  // namespace
 
 FMS_API int fms_attn_head_dim() { return HD; }
+FMS_API long fms_attn_stream_launches() { return g_stream_launches; }
 FMS_API int fms_attn_split_tokens() { return SPLIT; }
 // Positions of one sequence that a prefill block takes (the host cuts the new tokens into such tiles).
 FMS_API int fms_attn_prefill_tile_positions(int dtype, int nheads, int kvheads) {

@@ -311,6 +311,13 @@ def attention(q: torch.Tensor, batch, view, nheads: int, kvheads: int, head_dim:
     return out
 
 
+def attention_stream_launches(head_dim: int) -> int:
+    """How often this process has launched (or captured) the streaming decode-attention kernel of a head size."""
+    lib = load_library(f"attention_hd{head_dim}")
+    lib.fms_attn_stream_launches.restype = ctypes.c_long
+    return int(lib.fms_attn_stream_launches())
+
+
 def decode_advance(positions: torch.Tensor, lengths: torch.Tensor) -> None:
     """positions[i] = lengths[i]; lengths[i] += 1 — the bookkeeping of a decode step, on the device."""
     _call("elementwise", "fms_decode_advance", _ptr(positions), _ptr(lengths), positions.shape[0], _stream())

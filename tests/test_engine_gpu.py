@@ -426,6 +426,38 @@ def test_many_short_requests_in_one_batch_bfloat16_against_float32(tmp_path):
     assert (out["bf16"].argmax(-1) == out["fp32"].argmax(-1)).float().mean() > 0.9
 
 
+def test_decode_of_many_long_sequences_bfloat16_against_float32(tmp_path):
+    """Sixty-four requests of 700 to 1,000 tokens: enough keys and values for decode attention to take its
+    streaming kernel (persistent warps fed by TMA), first by plain launches, then inside the captured graph.  The
+    float32 path is the yardstick."""
+    from fms_b200.kernels import ops
+    from fms_b200.models import get_model
+    from fms_b200.models.llama import LLaMA, LLaMAConfig
+    from fms_b200.weights import write_random_model
+
+    arch = LLaMA(LLaMAConfig(src_vocab_size=1031, emb_dim=512, nheads=8, kvheads=4, nlayers=2, hidden_dim=1024,
+                             max_expected_seq_len=2048, rope_theta=500000.0))
+    folder = write_random_model(str(tmp_path / "m"), arch.config_json(), arch.checkpoint_layout(), seed=6)
+    g = torch.Generator().manual_seed(71)
+    reqs = [torch.randint(0, 1031, (int(k),), generator=g).tolist() for k in torch.randint(700, 1000, (64,), generator=g)]
+    steps = 4
+    out = {}
+    for dtype in ("fp32", "bf16"):
+        engine = get_model("hf_pretrained", model_path=folder, device_type="cuda", data_type=dtype).new_engine(64 * 1024)
+        before = ops.attention_stream_launches(64)
+        slots = engine.begin(len(reqs))
+        rows = [engine.step(slots, [r[:-steps] for r in reqs]).float().cpu()]
+        for t in range(steps, 0, -1):
+            rows.append(engine.step(slots, [[r[-t]] for r in reqs]).float().cpu())
+        engine.release(slots)
+        engine.check()
+        out[dtype] = torch.stack(rows, 1).reshape(-1, 1031)
+        # 2 layers: the first decode step launches them plainly, the second captures them; replays launch nothing new
+        assert ops.attention_stream_launches(64) - before == (4 if dtype == "bf16" else 0)
+    close(out["bf16"], out["fp32"], "bf16")
+    assert (out["bf16"].argmax(-1) == out["fp32"].argmax(-1)).float().mean() > 0.9
+
+
 def test_window_attention_through_the_engine(tmp_path):
     """A decoder whose mixers keep a window of 40 keys: the cache gives blocks back as they leave the window, and
     the logits equal the plain implementation's with the same window, whole and token by token."""

@@ -407,8 +407,10 @@ def test_decode_attention_of_many_sequences_streams_the_cache(ops, n_seqs, nhead
     view.keys[blk, head // group, far % 64] = (q[0, head * hd:(head + 1) * hd].float() * 6).to(dtype)
     view.values[blk, head // group, far % 64] = torch.full((hd,), 2.0).to(dtype).cuda()
     scale = 1.0 / math.sqrt(hd)
+    before = ops.attention_stream_launches(hd)
     got = ops.attention(q, batch, view, nheads, kvheads, hd, scale, window)
     ops.check_error_flag("cuda")
+    assert ops.attention_stream_launches(hd) == before + 1  # it was this kernel that ran
     want = P.attention(q, batch, view, nheads, kvheads, hd, scale, window)
     assert not torch.isnan(got).any()
     torch.testing.assert_close(got[0, head * hd:(head + 1) * hd].float(), torch.full((hd,), 2.0).cuda(), atol=5e-2, rtol=0)
