@@ -1,6 +1,6 @@
 """Decode and prefill throughput of the Llama-3-8B shape on one B200, random weights, bfloat16.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers L] [--model NAME]
 
 Prints ONE JSON line.  ``value``: decoded tokens a second at batch 8 (prompt lengths uniform in
 [128, 2048]), K decode steps timed on the device with CUDA events after W warm-up steps; a step is one
@@ -16,6 +16,8 @@ batch 1 and 64.  Weights (15 GB a step) are larger than L2, so no flush is neede
 tokens or contexts, one JSON line a size.  The default warm-up of 24 steps covers the 80 ms or so that the GPU's
 clocks take to come back up after the prefill's power-capped run.
 
+``--model llama-2-7b`` or ``llama-2-13b`` measures the benchmark's further shapes (32 and 40 kv heads: eight and
+ten times the keys and values a token) with their own prompt lengths instead of the default.
 ``--impl reference`` runs the unmodified reference (baseline/_ref) through its own get_model/generate.
 For more than one GPU the program says that it has no such path and exits with 2.
 """
@@ -32,9 +34,23 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-MODEL = dict(name="llama-3-8b", nlayers=32, emb_dim=4096, nheads=32, kvheads=8, head_dim=128, ffn_hidden=14336,
-             vocab=128256, context=8192)
+# The benchmark's shapes (the default is the first) with their registry variants and prompt lengths.
+MODELS = {
+    "llama-3-8b": dict(name="llama-3-8b", variant="3-8b", label="Llama-3-8B", nlayers=32, emb_dim=4096, nheads=32, kvheads=8,
+                       head_dim=128, ffn_hidden=14336, vocab=128256, context=8192, prompts=(128, 2048)),
+    "llama-2-7b": dict(name="llama-2-7b", variant="7b", label="Llama-2-7B", nlayers=32, emb_dim=4096, nheads=32, kvheads=32,
+                       head_dim=128, ffn_hidden=11008, vocab=32000, context=4096, prompts=(64, 2048)),
+    "llama-2-13b": dict(name="llama-2-13b", variant="13b", label="Llama-2-13B", nlayers=40, emb_dim=5120, nheads=40,
+                        kvheads=40, head_dim=128, ffn_hidden=13824, vocab=32000, context=4096, prompts=(1024, 1024)),
+}
+MODEL = MODELS["llama-3-8b"]
 PROMPT_MIN, PROMPT_MAX, PREFILL_TOKENS, BATCH = 128, 2048, 2048, 8
+
+
+def choose_model(name):
+    global MODEL, PROMPT_MIN, PROMPT_MAX
+    MODEL = MODELS[name]
+    PROMPT_MIN, PROMPT_MAX = MODEL["prompts"]
 
 
 def peaks():
@@ -100,8 +116,9 @@ def random_prompts(lengths, vocab, seed=0):
     return [[int(t) for t in rng.integers(0, vocab, size=n)] for n in lengths]
 
 
-def decode_bytes(nlayers, batch_context_tokens, m=MODEL):
+def decode_bytes(nlayers, batch_context_tokens, m=None):
     """Bytes one decode step has to read: every weight it uses once, and the cache of the live requests."""
+    m = m or MODEL
     d, hd, h, kv, f, v = m["emb_dim"], m["head_dim"], m["nheads"], m["kvheads"], m["ffn_hidden"], m["vocab"]
     per_layer = ((h + 2 * kv) * hd * d + h * hd * d + 2 * f * d + f * d + 2 * d) * 2
     weights = nlayers * per_layer + d * 2 + v * d * 2
@@ -109,7 +126,8 @@ def decode_bytes(nlayers, batch_context_tokens, m=MODEL):
     return weights + cache
 
 
-def prefill_flops(nlayers, tokens, m=MODEL):
+def prefill_flops(nlayers, tokens, m=None):
+    m = m or MODEL
     d, hd, h, kv, f, v = m["emb_dim"], m["head_dim"], m["nheads"], m["kvheads"], m["ffn_hidden"], m["vocab"]
     gemm = 2 * tokens * ((h + 2 * kv) * hd * d + h * hd * d + 3 * f * d) * nlayers
     attention = 2 * tokens * tokens * hd * h * nlayers  # causal half of 4 T^2 hd per head
@@ -198,7 +216,7 @@ def run_ours(args):
 
     pk = peaks()
     nlayers = args.layers or MODEL["nlayers"]
-    model = get_model("llama", "3-8b", device_type="cuda", data_type="bf16", seed=0, nlayers=nlayers)
+    model = get_model("llama", MODEL["variant"], device_type="cuda", data_type="bf16", seed=0, nlayers=nlayers)
     cfg = model.config
     assert (cfg.emb_dim, cfg.nheads, cfg.n_kvheads, cfg.ffn_hidden, cfg.src_vocab_size, cfg.max_expected_seq_len) == (
         MODEL["emb_dim"], MODEL["nheads"], MODEL["kvheads"], MODEL["ffn_hidden"], MODEL["vocab"], MODEL["context"])
@@ -279,7 +297,7 @@ def run_ours(args):
     pf_flops = prefill_flops(nlayers, PREFILL_TOKENS)
     gbs = decode_bytes(nlayers, context) / (ms_step / 1e3) / 1e9
     out = {
-        "metric": "decode tok/s at batch 8 (Llama-3-8B shape, random weights)", "value": round(value, 1),
+        "metric": f"decode tok/s at batch 8 ({MODEL['label']} shape, random weights)", "value": round(value, 1),
         "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic", "impl": "ours",
@@ -289,7 +307,7 @@ def run_ours(args):
             "ffn_hidden": MODEL["ffn_hidden"], "vocab": MODEL["vocab"], "context": MODEL["context"],
             "global_batch": BATCH, "seq_len": f"prompts uniform in [{PROMPT_MIN},{PROMPT_MAX}]",
             "mean_context": round(context / BATCH, 1), "prefill_tokens": PREFILL_TOKENS, "parallelism": "1 gpu",
-            "weights": "random N(0,0.02), seed 0", "l2": "weights read per step (15 GB) exceed L2; no flush",
+            "weights": "random N(0,0.02), seed 0", "l2": f"weights read per step ({decode_bytes(nlayers, 0) / 1e9:.0f} GB) exceed L2; no flush",
             "cache_block_tokens": 64, "peaks": pk["source"],
         },
         "clocks": sampler.summary(),
@@ -323,7 +341,7 @@ def run_reference(args):
 
     nlayers = args.layers or MODEL["nlayers"]
     torch.manual_seed(0)
-    model = get_model("llama", "3-8b", device_type="cuda", data_type=torch.bfloat16, nlayers=nlayers)
+    model = get_model("llama", MODEL["variant"], device_type="cuda", data_type=torch.bfloat16, nlayers=nlayers)
     model.eval()
     torch.set_grad_enabled(False)
     warmup = max(3, args.warmup)
@@ -369,7 +387,7 @@ def run_reference(args):
     pk = peaks()
     gbs = decode_bytes(nlayers, context) / (ms_step / 1e3) / 1e9
     print(json.dumps({
-        "metric": "decode tok/s at batch 8 (Llama-3-8B shape, random weights)", "value": round(value, 1),
+        "metric": f"decode tok/s at batch 8 ({MODEL['label']} shape, random weights)", "value": round(value, 1),
         "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms_step, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "reference",
@@ -395,8 +413,11 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--only", default="", help="decode_b<batch> or prefill: run and print that part only; gemm_rows, "
                     "attention_prefill, attention_decode: single kernels over a range of sizes")
-    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model's 32 (named in config)")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
+    ap.add_argument("--model", choices=sorted(MODELS), default="llama-3-8b",
+                    help="the shape to measure; the default is the benchmark's, the others are its further configurations")
     args = ap.parse_args()
+    choose_model(args.model)
     if args.gpus != 1:
         if int(os.environ.get("RANK", "0")) == 0:
             print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not measured")
