@@ -19,7 +19,9 @@ constexpr int SR_STAGES = 2;
 constexpr int SR_KV_BYTES = BLK * HD * 2;                       // keys (or values) of a block
 constexpr int SR_Q_BYTES = GROWS * HD * 2;                      // queries of a unit
 constexpr int SR_STAGE_BYTES = 2 * SR_KV_BYTES + ((SR_Q_BYTES + 1023) / 1024) * 1024;
-constexpr int SR_DESC_INTS = 8;                                 // what a stage holds: see Stage below
+constexpr int SR_DESC_INTS = 8;                                 // a stage's description, written by the producer: live (0: no
+                                                                // more work), sequence, kv head and chunk, split, key block,
+                                                                // the split's first and last + 1 position, first block of a unit
 constexpr size_t SR_SMEM = 1024 + (size_t)SR_WARPS * SR_STAGES * SR_STAGE_BYTES + SR_WARPS * SR_STAGES * (16 + SR_DESC_INTS * 4);
 
 // byte offset, inside a [64 rows x HD] tile made of TMA boxes of 64 x 64 with the 128-byte swizzle, of the 16-byte
