@@ -11,6 +11,10 @@
 //
 // A tile's two halves (mma rows 0-7 and 8-15) are
 //   ROWS16: weight rows r..r+7 and r+8..r+15;
+//   QKV_ROPE: as ROWS16 for the fused [q; k; v] projection of an attention layer; the epilogue rotates the pairs
+//           (2i, 2i+1) of the q and k heads by the token's position (float32 angles, fms/modules/positions.py:438-456),
+//           writes q to its own buffer and k and v into the token's place in the block cache, so that neither the
+//           [M, N] product nor a second kernel is needed;
 //   GLU8:   rows r..r+7 of the gate and of the up matrix of a fused [gate; up] weight; the epilogue writes
 //           act(gate) * up (fms/modules/feedforward.py:291-292) without the [M, 2 hidden] round trip.
 //
@@ -22,7 +26,21 @@
 namespace {
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
-enum Mode { ROWS16 = 0, GLU8 = 2 };
+enum Mode { ROWS16 = 0, QKV_ROPE = 1, GLU8 = 2 };
+
+// What the QKV_ROPE epilogue needs beyond the product (unused by the other modes).
+struct RopeArgs {
+  __nv_bfloat16* q_out;        // [M, nheads * head_dim]
+  const float* inv_freq;       // [head_dim / 2], or null: nothing is rotated
+  const int* positions;        // [M]
+  const int* token_seq;        // [M] index into slots
+  const int* slots;
+  __nv_bfloat16* k_cache;      // [blocks, kvheads, block_tokens, head_dim]
+  __nv_bfloat16* v_cache;
+  const int* table;            // [slots, table_stride]
+  int table_stride, block_tokens, nheads, kvheads, head_dim, write_cache;
+  int* error_flag;
+};
 
 __device__ __forceinline__ void mma_bf16(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
@@ -60,9 +78,9 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const __nv_bfloa
                                                                 const __nv_bfloat16* __restrict__ w,
                                                                 const __nv_bfloat16* __restrict__ bias,
                                                                 TOut* __restrict__ y, int M, int N, int K, int hidden,
-                                                                int act) {
+                                                                int act, RopeArgs rope) {
   constexpr int HALVES = 2;                           // weight rows a lane reads per tile
-  constexpr int TILE_ROWS = MODE == ROWS16 ? 16 : 8;  // output rows (or gate/up pairs) per tile
+  constexpr int TILE_ROWS = MODE == GLU8 ? 8 : 16;    // output rows (or gate/up pairs) per tile
   constexpr int WL = RT * HALVES;                     // weight pieces per stage
   constexpr int LOADS = WL + NT;
   __shared__ float red[WARPS][RT][NT][32][4];
@@ -185,6 +203,45 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const __nv_bfloa
         y[(size_t)m * hidden + row] = from_f32<TOut>(activate(gate, act) * up);
       }
     }
+  } else if (MODE == QKV_ROPE) {
+    // one (tile, pair of rows, token) per step: rows 2p and 2p + 1 of the tile are a pair of one head
+    static_assert(MODE != QKV_ROPE || NT == 1, "the fused projection is for up to 8 tokens");
+    for (int i = threadIdx.x; i < RT * 8 * 8; i += THREADS) {
+      const int t = i / 64, p = (i / 8) % 8, m = i % 8;
+      const int r0 = (blockIdx.x * RT + t) * TILE_ROWS + 2 * p;
+      if (r0 >= N || m >= M) continue;
+      // element (row rr, token m) of the tile lies with lane (rr % 8) * 4 + m / 2 as element (rr / 8) * 2 + m % 2
+      float x0 = red[0][t][0][((2 * p) & 7) * 4 + (m >> 1)][((2 * p) >> 3) * 2 + (m & 1)];
+      float x1 = red[0][t][0][((2 * p + 1) & 7) * 4 + (m >> 1)][((2 * p + 1) >> 3) * 2 + (m & 1)];
+      if (bias) {
+        x0 += __bfloat162float(bias[r0]);
+        x1 += __bfloat162float(bias[r0 + 1]);
+      }
+      const int head = r0 / rope.head_dim, d = r0 - head * rope.head_dim;
+      const bool is_v = head >= rope.nheads + rope.kvheads;
+      const int pos = rope.positions[m];
+      if (!is_v && rope.inv_freq != nullptr) {
+        float sn, cs;
+        sincosf((float)pos * rope.inv_freq[d >> 1], &sn, &cs);
+        const float r = cs * x0 - sn * x1;
+        x1 = sn * x0 + cs * x1;
+        x0 = r;
+      }
+      const __nv_bfloat162 out = __floats2bfloat162_rn(x0, x1);
+      if (head < rope.nheads) {
+        *reinterpret_cast<__nv_bfloat162*>(rope.q_out + ((size_t)m * rope.nheads + head) * rope.head_dim + d) = out;
+      } else if (rope.write_cache) {
+        const int blk = rope.table[(size_t)rope.slots[rope.token_seq[m]] * rope.table_stride + pos / rope.block_tokens];
+        if (blk < 0) {
+          if (rope.error_flag) atomicExch(rope.error_flag, 2);
+          continue;
+        }
+        const int kvh = is_v ? head - rope.nheads - rope.kvheads : head - rope.nheads;
+        __nv_bfloat16* base = is_v ? rope.v_cache : rope.k_cache;
+        *reinterpret_cast<__nv_bfloat162*>(
+            base + (((size_t)blk * rope.kvheads + kvh) * rope.block_tokens + (pos % rope.block_tokens)) * rope.head_dim + d) = out;
+      }
+    }
   } else {
     constexpr int EL = 4;
     for (int i = threadIdx.x; i < RT * NT * 32 * EL; i += THREADS) {
@@ -202,7 +259,7 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const __nv_bfloa
 
 template <int NT, int RT, int MODE, typename TOut>
 int launch_typed(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int hidden, int act,
-                 cudaStream_t stream) {
+                 cudaStream_t stream, const RopeArgs& rope = RopeArgs{}) {
   constexpr int LOADS = RT * 2 + NT;
   constexpr int D = LOADS <= 2 ? 7 : (LOADS == 3 ? 5 : (LOADS == 4 ? 4 : 3));  // 56 to 72 KB of ring per block
   constexpr size_t smem = (size_t)D * LOADS * THREADS * sizeof(uint4);
@@ -213,11 +270,11 @@ int launch_typed(const void* x, const void* w, const void* bias, void* y, int M,
     if (e != cudaSuccess) return fms_fail("linear_bf16_skinny: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  constexpr int TILE_ROWS = MODE == ROWS16 ? 16 : 8;
+  constexpr int TILE_ROWS = MODE == GLU8 ? 8 : 16;
   const int rows = MODE == GLU8 ? hidden : N;
   const int blocks = (rows + TILE_ROWS * RT - 1) / (TILE_ROWS * RT);
   cudaError_t e = fms_launch(kernel, dim3(blocks), dim3(THREADS), smem, stream, (const __nv_bfloat16*)x,
-                             (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, (TOut*)y, M, N, K, hidden, act);
+                             (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, (TOut*)y, M, N, K, hidden, act, rope);
   if (e != cudaSuccess) return fms_fail("linear_bf16_skinny: launch failed: %s", cudaGetErrorString(e));
   return 0;
 }
@@ -244,6 +301,29 @@ FMS_API int fms_linear_bf16_skinny(const void* x, const void* w, const void* bia
   // very many weight rows: 32 rows a block, which halves the re-reading of x
   if (N < 16384) return launch<1, 1, ROWS16>(x, w, bias, y, out_dtype, M, N, K, 0, 0, stream);
   return launch<1, 2, ROWS16>(x, w, bias, y, out_dtype, M, N, K, 0, 0, stream);
+}
+
+// The fused projection of an attention layer for up to 8 tokens: [q | k | v] = x [M, K] w[(nheads + 2 kvheads) head_dim, K]^T
+// + bias; q and k rotated by each token's position; q -> q_out [M, nheads head_dim], k and v -> the token's place in
+// the block cache (write_cache 0: q only).  A token whose position has no block sets error flag 2 and is skipped.
+FMS_API int fms_qkv_rope_store_bf16_skinny(const void* x, const void* w, const void* bias, void* q_out,
+                                           const float* inv_freq, const int* positions, const int* token_seq,
+                                           const int* slots, void* k_cache, void* v_cache, const int* table,
+                                           int table_stride, int block_tokens, int M, int K, int nheads, int kvheads,
+                                           int head_dim, int write_cache, int* error_flag, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (M > 8) return fms_fail("qkv_rope_store_bf16_skinny: %d rows, at most 8", M);
+  if (K <= 0 || K % 8) return fms_fail("qkv_rope_store_bf16_skinny: K %d must be a positive multiple of 8", K);
+  if (nheads <= 0 || kvheads <= 0 || head_dim <= 0 || head_dim % 2 || block_tokens <= 0)
+    return fms_fail("qkv_rope_store_bf16_skinny: %d heads, %d kv heads, head size %d, blocks of %d", nheads, kvheads,
+                    head_dim, block_tokens);
+  const long rows = (long)(nheads + 2 * kvheads) * head_dim;
+  if (rows > 0x7fffffffL) return fms_fail("qkv_rope_store_bf16_skinny: %ld rows of w", rows);
+  const RopeArgs rope{(__nv_bfloat16*)q_out, inv_freq, positions, token_seq, slots, (__nv_bfloat16*)k_cache,
+                      (__nv_bfloat16*)v_cache, table, table_stride, block_tokens, nheads, kvheads, head_dim, write_cache,
+                      error_flag};
+  if (rows < 16384) return launch_typed<1, 1, QKV_ROPE, __nv_bfloat16>(x, w, bias, nullptr, M, (int)rows, K, 0, 0, stream, rope);
+  return launch_typed<1, 2, QKV_ROPE, __nv_bfloat16>(x, w, bias, nullptr, M, (int)rows, K, 0, 0, stream, rope);
 }
 
 // y [M, hidden] = act(x w_gate^T + b_gate) * (x w_up^T + b_up) with w = [gate; up] of 2 hidden rows.

@@ -32,6 +32,7 @@ _SIGNATURES = {
     "fms_gemm_f32": [_P, _P, _P, _P, _I, _I, _I, _P],
     "fms_linear_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "fms_glu_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "fms_qkv_rope_store_bf16_skinny": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "fms_gemm_bf16_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "fms_glu_bf16_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "fms_argmax": [_P, _P, _I, _I, _P],
@@ -266,6 +267,28 @@ def rope_store(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], batch, view,
           view.table.shape[1], view.block_tokens, n, nheads, kvheads, head_dim, 1 if writes_cache else 0,
           _ptr(error_flag(qkv.device)), _stream())
     return q
+
+
+FUSE_QKV_ROPE = os.environ.get("FMS_B200_FUSE_QKV_ROPE", "1") != "0"
+
+
+def qkv_rope_store(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
+                   batch, view, nheads: int, kvheads: int, head_dim: int, writes_cache: bool = True) -> torch.Tensor:
+    """An attention layer's fused projection and what follows it: qkv = x weight^T (+ bias), q and k rotated by each
+    token's position, k and v written into the cache, the rotated q returned.  For a few bfloat16 rows (a decode
+    step) this is one kernel, the weight-streaming product with the rotation and the cache write in its epilogue;
+    else the product and ``rope_store`` one after the other."""
+    if (FUSE_QKV_ROPE and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_ROWS
+            and weight.shape[1] % 8 == 0 and head_dim % 2 == 0 and (bias is None or bias.dtype == torch.bfloat16)
+            and view.keys.dtype == torch.bfloat16 and weight.shape[0] == (nheads + 2 * kvheads) * head_dim):
+        n = x.shape[0]
+        q = torch.empty((n, nheads * head_dim), dtype=x.dtype, device=x.device)
+        _call("gemm_bf16_skinny", "fms_qkv_rope_store_bf16_skinny", _ptr(x), _ptr(weight), _ptr(bias), _ptr(q),
+              _ptr(inv_freq), _ptr(batch.positions), _ptr(batch.token_seq), _ptr(batch.slots), _ptr(view.keys),
+              _ptr(view.values), _ptr(view.table), view.table.shape[1], view.block_tokens, n, weight.shape[1], nheads,
+              kvheads, head_dim, 1 if writes_cache else 0, _ptr(error_flag(x.device)), _stream())
+        return q
+    return rope_store(linear(x, weight, bias), inv_freq, batch, view, nheads, kvheads, head_dim, writes_cache)
 
 
 def _attention_library(head_dim: int) -> str:

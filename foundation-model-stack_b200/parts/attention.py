@@ -54,10 +54,9 @@ class MultiHeadAttention(Part):
         return KVRequest(self.kvheads, self.head_dim, self.window)
 
     def forward(self, x, batch, cache_view, writes_cache: bool = True):
-        qkv = self.qkv.forward(x)
-        q = ops.rope_store(
-            qkv, self.position.rotary_frequencies(), batch, cache_view, self.nheads, self.kvheads, self.head_dim,
-            writes_cache,
+        q = ops.qkv_rope_store(
+            x, self.qkv.tensor("weight"), self.qkv.tensor("bias"), self.position.rotary_frequencies(), batch, cache_view,
+            self.nheads, self.kvheads, self.head_dim, writes_cache,
         )
         o = ops.attention(q, batch, cache_view, self.nheads, self.kvheads, self.head_dim, self.scale, self.window)
         return self.dense.forward(o)

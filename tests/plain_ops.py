@@ -73,6 +73,10 @@ def rope_store(qkv, inv_freq, batch, view, nheads, kvheads, head_dim, writes_cac
     return q
 
 
+def qkv_rope_store(x, weight, bias, inv_freq, batch, view, nheads, kvheads, head_dim, writes_cache=True):
+    return rope_store(linear(x, weight, bias), inv_freq, batch, view, nheads, kvheads, head_dim, writes_cache)
+
+
 def gather_cache(view, slot, lo, hi):
     """Keys and values [hi - lo, kvheads, head_dim] of positions lo..hi-1 of the sequence in ``slot``."""
     pos = torch.arange(lo, hi, device=view.keys.device)
@@ -137,7 +141,7 @@ def check_error_flag(device):
 
 
 PLAIN = dict(embed=embed, add_rmsnorm=add_rmsnorm, linear=linear, gated_activation=gated_activation, gated_linear=gated_linear,
-             rope_store=rope_store, attention=attention, decode_advance=decode_advance, argmax=argmax, sample=sample, error_flag=error_flag,
+             rope_store=rope_store, qkv_rope_store=qkv_rope_store, attention=attention, decode_advance=decode_advance, argmax=argmax, sample=sample, error_flag=error_flag,
              check_error_flag=check_error_flag)
 
 

@@ -263,6 +263,49 @@ def test_rope_store(ops, dtype, nheads, kvheads, hd):
     assert torch.equal(torch.nan_to_num(view.keys.float()), torch.nan_to_num(before.float()))
 
 
+@pytest.mark.parametrize("nheads,kvheads,hd,lens_before,num_new", [
+    (4, 2, 16, [70, 0, 5], [1, 1, 1]),        # a decode step
+    (3, 1, 32, [0, 63], [3, 2]),              # short prompts and a continuation across a block's edge
+    (5, 5, 48, [130], [8]),                   # eight tokens of one sequence, odd head size
+    (32, 8, 128, [100, 200, 300, 5, 64, 63, 1, 0], [1] * 8),  # the benchmark's head layout, batch 8
+])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_projection_rotation_and_cache_write_in_one_kernel(ops, nheads, kvheads, hd, lens_before, num_new, with_bias):
+    """Up to 8 bfloat16 rows: the weight-streaming product rotates q and k and writes k and v into the cache in its
+    epilogue.  Against the plain product followed by the plain rotation and cache write (which round the product
+    to bfloat16 in between; the fused kernel rotates the float32 sums)."""
+    dtype, k = torch.bfloat16, 8 * 21
+    cache, view, batch = make_cache_case(dtype, nheads, kvheads, hd, lens_before, num_new, 23)
+    g = torch.Generator().manual_seed(24)
+    n, rows = sum(num_new), (nheads + 2 * kvheads) * hd
+    x = torch.randn(n, k, generator=g).to(dtype).cuda()
+    w = (torch.randn(rows, k, generator=g) * 0.08).to(dtype).cuda()
+    b = (torch.randn(rows, generator=g) * 0.3).to(dtype).cuda() if with_bias else None
+    inv = (1.0 / (500000.0 ** (torch.arange(0, hd, 2).float() / hd))).cuda()
+    keys0, values0 = view.keys.clone(), view.values.clone()
+
+    class V:
+        keys, values, table, block_tokens = keys0, values0, view.table, 64
+
+    want_q = P.rope_store(P.linear(x, w, b, torch.float32), inv, batch, V, nheads, kvheads, hd)
+    got_q = ops.qkv_rope_store(x, w, b, inv, batch, view, nheads, kvheads, hd)
+    ops.check_error_flag("cuda")
+    t = dict(atol=3e-2, rtol=2e-2)
+    torch.testing.assert_close(got_q.float(), want_q.float(), **t)
+    torch.testing.assert_close(view.keys.float(), keys0.float(), equal_nan=True, **t)
+    torch.testing.assert_close(view.values.float(), values0.float(), equal_nan=True, **t)
+    # nothing else of the cache was touched: what was NaN (no live position) is NaN still
+    assert torch.equal(torch.isnan(view.keys), torch.isnan(keys0)) and torch.equal(torch.isnan(view.values), torch.isnan(values0))
+    # the same values as the two kernels one after the other, up to the rounding of the product in between
+    two = ops.rope_store(ops.linear(x, w, b), inv, batch, view, nheads, kvheads, hd)
+    torch.testing.assert_close(got_q.float(), two.float(), **t)
+    # without frequencies nothing is rotated; without cache writes the cache stays as it is
+    before = view.keys.clone()
+    q2 = ops.qkv_rope_store(x, w, b, None, batch, view, nheads, kvheads, hd, writes_cache=False)
+    torch.testing.assert_close(q2.float(), P.linear(x, w, b, torch.float32)[:, : nheads * hd].float(), **t)
+    assert torch.equal(torch.nan_to_num(view.keys.float()), torch.nan_to_num(before.float()))
+
+
 ATTN_CASES = [
     # nheads, kvheads, hd, lens_before, num_new, window
     (4, 2, 16, [0, 0, 0], [5, 70, 17], 0),          # prompts from an empty cache
