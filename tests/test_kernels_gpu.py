@@ -485,6 +485,18 @@ def test_kernels_report_what_the_host_should_have_prevented(ops):
         changed = (view.keys != keys0).flatten(1).any(1).nonzero().flatten().tolist()
         assert changed == still_there  # only the blocks that exist were written
 
+    # the same through the product that writes the cache itself (up to 8 bfloat16 rows)
+    cache, view, batch = make_cache_case(torch.bfloat16, 4, 2, 16, [63], [2], 17, poison=False)
+    view.table[int(batch.slots[0]), 1] = -1
+    keys0 = view.keys.clone()
+    x = torch.randn(2, 24).to(torch.bfloat16).cuda()
+    w = torch.randn(8 * 16, 24).to(torch.bfloat16).cuda()
+    ops.qkv_rope_store(x, w, None, None, batch, view, 4, 2, 16)
+    with pytest.raises(KernelError, match="cache block"):
+        ops.check_error_flag("cuda")
+    changed = (view.keys != keys0).flatten(1).any(1).nonzero().flatten().tolist()
+    assert changed == [int(cache.groups[0].table_host[int(batch.slots[0])][0])]  # position 63 was written, 64 was not
+
 
 def test_attention_refuses_other_head_sizes():
     from fms_b200.kernels.build import KernelBuildError, _spec
