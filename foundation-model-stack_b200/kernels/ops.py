@@ -321,9 +321,10 @@ def attention(q: torch.Tensor, batch, view, nheads: int, kvheads: int, head_dim:
         n_splits = (batch.max_len_after + split - 1) // split
         part_o = torch.empty((batch.n_seqs, nheads, n_splits, head_dim), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((batch.n_seqs, nheads, n_splits, 2), dtype=torch.float32, device=q.device)
+        # total_len (what the host knows of the sequences' lengths) chooses between the two bfloat16 decode kernels
         _call(lib, "fms_attention_decode", *common, batch.n_seqs, n_splits, _ptr(part_o), _ptr(part_ml), nheads,
-              kvheads, head_dim, float(scale), int(window), view.keys.shape[0], int(getattr(batch, "total_len", 0)), _ptr(_work_counter(q.device)),
-              _ptr(error_flag(q.device)), _stream())
+              kvheads, head_dim, float(scale), int(window), view.keys.shape[0], int(getattr(batch, "total_len", 0)),
+              _ptr(_work_counter(q.device)), _ptr(error_flag(q.device)), _stream())
         if n_splits > 1 or q.dtype == torch.float32:
             global launches
             launches += 1  # the kernel that merges the splits
