@@ -258,3 +258,16 @@ def test_adapter_registry():
     # the engine's own names load through the "fms" source (fusion only)
     fused = get_adapted("llama", "fms", {"x.ff_sub_layer.wg.weight": torch.ones(2, 3), "x.ff_sub_layer.w1.weight": torch.zeros(2, 3)})
     assert list(fused) == ["x.ff_sub_layer.wg1_fused.weight"] and fused["x.ff_sub_layer.wg1_fused.weight"][0, 0] == 1
+
+
+def test_the_references_serialization_import_path(tiny_folders):
+    """fms.utils.serialization's names (fms/utils/serialization.py:27-160, :292-316, :339-450) under the same path."""
+    from fms_b200.utils.serialization import get_adapted, list_sources, load_state_dict
+
+    assert "hf" in list_sources("llama")
+    sd = load_state_dict(tiny_folders["a"])
+    assert "model.embed_tokens.weight" in sd.keys() and sd.spec("model.norm.weight") == (torch.bfloat16, (64,))
+    assert sd.get("model.norm.weight").shape == (64,)
+    with pytest.raises(FileNotFoundError):
+        load_state_dict("/no/such/checkpoint")
+    assert callable(get_adapted)
