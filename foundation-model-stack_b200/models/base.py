@@ -71,3 +71,35 @@ class Model:
             del e
             self._engine = self.new_engine(max(min_tokens, 64), max(min_slots, 1))
         return self._engine
+
+    # ---- whole sequences in, logits out: the reference's ``model(x)`` ------------------------------
+    def forward(self, x, last_n_tokens: int = 0, use_cache: bool = False, **kwargs):
+        """Float32 logits of whole sequences, nothing kept afterwards (fms/models/llama.py:425-450).
+
+        x: token ids [S], [B, S] (a tensor) or a list of sequences of any lengths.  last_n_tokens: 0 for every
+        position, n for the last n of each sequence, as the reference's parameter of the same name.  Returns
+        [S', V], [B, S', V] or a list of [S'_i, V].  Stepping with a cache is ``new_engine(...).step`` (or
+        ``generate``), not this call: use_cache and the reference's other keywords are refused."""
+        if use_cache or any(v is not None for v in kwargs.values()):
+            raise NotImplementedError("model(x) scores whole sequences; to step with the cache use Engine.step or generate")
+        if isinstance(x, torch.Tensor):
+            if x.dim() not in (1, 2):
+                raise ValueError("x must be [S] or [B, S]")
+            seqs = [x.tolist()] if x.dim() == 1 else [row.tolist() for row in x]
+        else:
+            seqs = [[int(t) for t in s] for s in x]
+        if not seqs or any(len(s) == 0 for s in seqs):
+            raise ValueError("every sequence needs at least one token")
+        want = [list(range(len(s) - last_n_tokens if 0 < last_n_tokens < len(s) else 0, len(s))) for s in seqs]
+        engine = self.engine(min_tokens=sum((len(s) + 63) // 64 * 64 for s in seqs), min_slots=len(seqs))
+        slots = engine.begin(len(seqs))
+        try:
+            logits = engine.step(slots, seqs, want)
+        finally:
+            engine.release(slots)
+        parts = list(torch.split(logits, [len(w) for w in want]))
+        if isinstance(x, torch.Tensor):
+            return parts[0] if x.dim() == 1 else torch.stack(parts)
+        return parts
+
+    __call__ = forward

@@ -208,6 +208,18 @@ def test_greedy_generation_through_the_entry_point(models, oracles, which):
     # one prompt alone gives the same tokens as in the batch
     alone = generate(model, torch.tensor(prompts[1]), max_new_tokens=8, do_sample=False)
     assert alone.tolist() == out[1].tolist()
+    # model(x): logits of whole sequences, as the reference's forward without a cache
+    one = model(torch.tensor(prompts[1]))
+    close(one, oracles[which].logits(prompts[1]), "fp32")
+    two = model(torch.tensor([prompts[1], prompts[1][::-1]]), last_n_tokens=2)
+    assert two.shape == (2, 2, one.shape[-1])
+    close(two[0], oracles[which].logits(prompts[1])[-2:], "fp32")
+    close(two[1], oracles[which].logits(prompts[1][::-1])[-2:], "fp32")
+    ragged = model(prompts)
+    assert [r.shape[0] for r in ragged] == [len(p) for p in prompts]
+    close(ragged[0], oracles[which].logits(prompts[0]), "fp32")
+    with pytest.raises(NotImplementedError):
+        model(torch.tensor(prompts[1]), use_cache=True)
     # the reference's way with unequal prompts, a padded rectangle: padding changes no token
     from fms_b200.utils.generation import pad_input_ids, trim_prefix
 
