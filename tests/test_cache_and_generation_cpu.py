@@ -365,3 +365,25 @@ def test_bench_says_that_it_measures_one_gpu_only():
     assert r.returncode == 2
     lines = [line for line in r.stdout.splitlines() if line.strip()]
     assert len(lines) == 1 and "one GPU" in lines[0]
+
+
+def test_bench_counts_the_bytes_and_flops_of_its_shapes():
+    """The denominators of the roofline figures: what a decode step has to read (every weight once, and the
+    cache of the live tokens) and what a prefill has to compute, for the benchmark's three shapes."""
+    import importlib.util
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    want = {  # GB of weights a step, bytes of cache a token, TFLOP of a 2,048-token prefill
+        "llama-3-8b": (15.01, 131072, 29.69), "llama-2-7b": (13.21, 524288, 27.63), "llama-2-13b": (25.70, 819200, 53.69)}
+    for name, (gb, per_token, tflop) in want.items():
+        bench.choose_model(name)
+        layers = bench.MODEL["nlayers"]
+        assert abs(bench.decode_bytes(layers, 0) / 1e9 - gb) < 0.01
+        assert bench.decode_bytes(layers, 1) - bench.decode_bytes(layers, 0) == per_token
+        assert abs(bench.prefill_flops(layers, 2048) / 1e12 - tflop) < 0.01
+        assert (bench.PROMPT_MIN, bench.PROMPT_MAX) == bench.MODEL["prompts"]
+    bench.choose_model("llama-3-8b")
