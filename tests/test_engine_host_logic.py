@@ -87,3 +87,27 @@ def test_step_refuses_what_does_not_fit(tiny_folders):
         engine.release([slot, other])
         with pytest.raises(ValueError, match="not held"):
             engine.step([slot], [[1]])
+
+
+def test_model_called_on_whole_sequences(tiny_folders):
+    """model(x), the reference's forward without a cache (fms/models/llama.py:425-450): a sequence, a rectangle with
+    last_n_tokens, sequences of unequal lengths; the engine it makes for itself grows when it has to and holds
+    nothing afterwards."""
+    oracle = pl.PlainLlama(tiny_folders["a"])
+    prompts = tiny_prompts("a")
+    with use_plain_ops():
+        model = _model(tiny_folders["a"])
+        one = model(torch.tensor(prompts[0]))
+        torch.testing.assert_close(one.double(), oracle.logits(prompts[0]), atol=2e-5, rtol=1e-4)
+        rect = model(torch.tensor([prompts[1], prompts[1][::-1]]), last_n_tokens=3)
+        assert rect.shape == (2, 3, one.shape[-1])
+        torch.testing.assert_close(rect[1].double(), oracle.logits(prompts[1][::-1])[-3:], atol=2e-5, rtol=1e-4)
+        ragged = model(prompts)  # more sequences and tokens than the first call's engine had room for
+        for got, p in zip(ragged, prompts):
+            torch.testing.assert_close(got.double(), oracle.logits(p), atol=2e-5, rtol=1e-4)
+        engine = model.engine()
+        assert engine.cache.slots.n_held == 0 and all(g.pool.n_held == 0 for g in engine.cache.groups)
+        with pytest.raises(NotImplementedError):
+            model(torch.tensor(prompts[0]), use_cache=True)
+        with pytest.raises(ValueError):
+            model([[]])
