@@ -135,6 +135,9 @@ __global__ void __launch_bounds__((SR_WARPS + 1) * 32, 1)
     const int s = i % SR_STAGES;
     if (!mbar_wait(full + s, (uint32_t)(i / SR_STAGES) & 1u)) {
       if (lane == 0 && error_flag) atomicExch(error_flag, 4);
+      // copies that may still be on their way into this warp's other stages: wait for them, again with a limit,
+      // so that none lands in shared memory that has been given to another block
+      for (int k = 1; k < SR_STAGES; ++k) mbar_wait(full + (i + k) % SR_STAGES, (uint32_t)((i + k) / SR_STAGES) & 1u);
       return;
     }
     const int* d = descs + s * SR_DESC_INTS;
