@@ -216,14 +216,17 @@ class PlainLlama:
         )
         return x + f
 
-    def logits(self, ids: Sequence[int]) -> torch.Tensor:
+    def logits(self, ids: Sequence[int], rows: Optional[Sequence[int]] = None) -> torch.Tensor:
         """Logits at every position of one whole sequence: [S, vocab]
-        (fms/models/llama.py:318-357 and :425-450)."""
+        (fms/models/llama.py:318-357 and :425-450).  With ``rows`` the head is applied at those positions
+        only (the layers still run the whole sequence): [len(rows), vocab]."""
         ids_t = torch.as_tensor(list(ids), dtype=torch.long)
         positions = torch.arange(ids_t.shape[0])
         x = plain_embedding(ids_t, self.w["model.embed_tokens.weight"])
         for i in range(self.c["nlayers"]):
             x = self.block(i, x, positions)
+        if rows is not None:
+            x = x[torch.as_tensor(list(rows), dtype=torch.long)]
         x = plain_rmsnorm(x, self.w["model.norm.weight"], self.c["eps"])
         head = self.w["model.embed_tokens.weight"] if self.c["tied"] else self.w["lm_head.weight"]
         return x @ head.T
