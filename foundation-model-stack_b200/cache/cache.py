@@ -164,8 +164,8 @@ class Cache:
         self.blocks_per_sequence = round_up(self.max_positions, BLOCK_TOKENS) // BLOCK_TOKENS
         self.slots = SlotAllocator(self.max_slots)
         # fixed-size state that every sequence has, whatever the architecture: its length (tokens in the
-        # cache) and the position of its next token (equal for Llama; kept apart for encodings whose
-        # positions are not the token index)
+        # cache) and the position of its next token, which is what a position encoding sees.  They differ
+        # by the position at which the sequence started (``begin(n, first_positions)``), 0 by default.
         self.length = [0] * self.max_slots
         self.position = [0] * self.max_slots
         self.groups: List[Union[KVGroup, StateGroup]] = []
@@ -186,14 +186,17 @@ class Cache:
                 self._group_of_layer[layer] = group
 
     # ---- slots -------------------------------------------------------------------------------
-    def begin(self, n: int) -> List[int]:
-        """Takes n slots for sequences that start together; their lengths are 0 and their state is zero."""
+    def begin(self, n: int, first_positions: Optional[Sequence[int]] = None) -> List[int]:
+        """Takes n slots for sequences that start together; their lengths are 0 and their state is zero.
+        ``first_positions[i]``: the position of sequence i's first token (default 0)."""
         if n > self.slots.n_free:
             raise CacheFull(f"{n} slots wanted, {self.slots.n_free} of {self.max_slots} free")
+        if first_positions is not None and (len(first_positions) != n or any(int(p) < 0 for p in first_positions)):
+            raise ValueError("first_positions: one position >= 0 for each sequence")
         out = [self.slots.alloc() for _ in range(n)]
-        for s in out:
+        for i, s in enumerate(out):
             self.length[s] = 0
-            self.position[s] = 0
+            self.position[s] = int(first_positions[i]) if first_positions is not None else 0
             for g in self.groups:
                 if isinstance(g, StateGroup):
                     g.reset(s)
@@ -225,9 +228,10 @@ class Cache:
                 raise ValueError(f"slot {s} is not held")
             if n <= 0:
                 raise ValueError("every sequence of a step brings at least one token")
-            if self.length[s] + n > self.max_positions:
+            if max(self.length[s], self.position[s]) + n > self.max_positions:
                 raise CacheFull(
-                    f"slot {s}: {self.length[s]} + {n} tokens exceed the model's {self.max_positions} positions"
+                    f"slot {s}: {max(self.length[s], self.position[s])} + {n} tokens exceed the model's "
+                    f"{self.max_positions} positions"
                 )
             before.append(self.length[s])
         plans = []
@@ -250,8 +254,9 @@ class Cache:
         work = []
         for s in slots:
             n = self.length[s]
-            if n + 1 > self.max_positions:
-                raise CacheFull(f"slot {s}: {n} + 1 tokens exceed the model's {self.max_positions} positions")
+            if max(n, self.position[s]) + 1 > self.max_positions:
+                raise CacheFull(f"slot {s}: {max(n, self.position[s])} + 1 tokens exceed the model's "
+                                f"{self.max_positions} positions")
             if n % BLOCK_TOKENS == 0 or any(isinstance(g, KVGroup) and g.request.window for g in self.groups):
                 work.append(s)
         if work:
@@ -261,6 +266,10 @@ class Cache:
         for s, n in zip(slots, num_new):
             self.length[s] += n
             self.position[s] += n
+
+    def offset(self, slot: int) -> int:
+        """The position at which the sequence in ``slot`` started."""
+        return self.position[slot] - self.length[slot]
 
     def layer_view(self, layer: int):
         g = self._group_of_layer.get(layer)

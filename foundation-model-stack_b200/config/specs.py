@@ -68,7 +68,8 @@ class FeedForwardSpec:
 
 @dataclasses.dataclass(frozen=True)
 class BlockSpec:
-    """One layer: its norms, mixer and feed-forward and their arrangement.  ``arrangement == "pre_norm"``:
+    """One layer: its norms, mixer and feed-forward and their arrangement, which names the block class in the
+    registry (``fms_b200.parts.register_block``).  ``arrangement == "pre_norm"``:
     x += mixer(norm1(x)); x += feed_forward(norm2(x)).  The names are those under which the layer's
     parts appear in weight names (``ln``, ``attn``, ``ff_ln``, ``ff_sub_layer`` for Llama)."""
 
@@ -78,6 +79,7 @@ class BlockSpec:
     feed_forward_norm: NormSpec
     arrangement: str = "pre_norm"
     names: Tuple[str, str, str, str] = ("ln", "attn", "ff_ln", "ff_sub_layer")
+    options: Tuple[Tuple[str, Any], ...] = ()  # what another arrangement needs (a residual multiplier, ...)
 
 
 @dataclasses.dataclass(frozen=True)
@@ -105,6 +107,8 @@ class DecoderSpec:
     max_positions: int
     # prefixes of weight names: embedding, layer list, final norm, head
     names: Tuple[str, str, str, str] = ("base_model.embedding", "base_model.layers", "base_model.dec_norm", "head")
+    embedding_scale: float = 1.0  # the embedded rows are multiplied by it as they enter the residual stream
+    logit_scale: float = 1.0  # the logits are multiplied by it
 
     def __post_init__(self):
         n = len(self.layers)

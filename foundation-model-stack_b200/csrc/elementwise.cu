@@ -4,11 +4,11 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------------------------------
-// embedding: out[t, :] = float(table[tokens[t], :])            (reference: fms/models/llama.py:332)
+// embedding: out[t, :] = scale * float(table[tokens[t], :])    (reference: fms/models/llama.py:332; scale 1)
 // ---------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ out,
-                                  int dim, int vocab, int* __restrict__ error_flag) {
+                                  int dim, int vocab, float scale, int* __restrict__ error_flag) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -17,17 +17,17 @@ __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __rest
   if (!ok && threadIdx.x == 0 && error_flag) atomicExch(error_flag, 1);
   const T* src = table + (size_t)(ok ? tok : 0) * dim;
   float* dst = out + (size_t)t * dim;
-  for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = ok ? to_f32(src[d]) : 0.f;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = ok ? scale * to_f32(src[d]) : 0.f;
 }
 
 FMS_API int fms_embed_rows(const void* table, int table_dtype, const int* tokens, float* out, int n_tokens, int dim,
-                           int vocab, int* error_flag, cudaStream_t stream) {
+                           int vocab, float scale, int* error_flag, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (dim <= 0 || vocab <= 0) return fms_fail("embed_rows: dim %d, vocab %d", dim, vocab);
   const int threads = dim >= 1024 ? 256 : 128;
   FMS_DISPATCH_DTYPE(table_dtype, T,
                      fms_launch(embed_rows_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, (const T*)table, tokens,
-                                out, dim, vocab, error_flag));
+                                out, dim, vocab, scale, error_flag));
   return fms_launch_status("embed_rows");
 }
 
@@ -253,12 +253,15 @@ FMS_API int fms_gated_activation(const void* gu, void* out, int dtype, int n_row
 //   qkv[t] = [q heads | k heads | v heads], each head `head_dim` wide     (fms/modules/attention.py:653-657)
 //   q, k: adjacent pairs (2i, 2i+1) rotated by angle = position * inv_freq[i], float32
 //                                                                    (fms/modules/positions.py:438-456)
+//   positions[t]: the token's place in its sequence's cache; position_ids[t]: the position that the rotation sees
+//   (null: the same; they differ for a sequence that does not start at position 0)
 //   rotated q -> q_out[t]; rotated k and v -> the cache block of the token's slot and position
 // grid (token, head), one thread per pair.
 // ---------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float* __restrict__ inv_freq,
-                                  const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                  const int* __restrict__ positions, const int* __restrict__ position_ids,
+                                  const int* __restrict__ token_seq,
                                   const int* __restrict__ slots, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                   const int* __restrict__ table, int table_stride, int block_tokens, int nheads,
                                   int kvheads, int head_dim, int write_cache, int* __restrict__ error_flag) {
@@ -274,7 +277,7 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
   float x0 = to_f32(src[2 * i]), x1 = to_f32(src[2 * i + 1]);
   const bool is_v = head >= nheads + kvheads;
   if (!is_v && inv_freq != nullptr) {
-    const float angle = (float)pos * inv_freq[i];
+    const float angle = (float)(position_ids ? position_ids[t] : pos) * inv_freq[i];
     float s, c;
     sincosf(angle, &s, &c);
     const float r0 = c * x0 - s * x1;
@@ -308,7 +311,8 @@ constexpr int ROPE_VEC_MAX_PAIRS = 1024;  // head_dim / 2 that the table in shar
 
 __global__ void rope_store_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
                                       const float* __restrict__ inv_freq, const int* __restrict__ positions,
-                                      const int* __restrict__ token_seq, const int* __restrict__ slots,
+                                      const int* __restrict__ position_ids, const int* __restrict__ token_seq,
+                                      const int* __restrict__ slots,
                                       __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
                                       const int* __restrict__ table, int table_stride, int block_tokens, int nheads,
                                       int kvheads, int head_dim, int write_cache, int* __restrict__ error_flag) {
@@ -326,9 +330,10 @@ __global__ void rope_store_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __n
     if (blk < 0 && threadIdx.x == 0 && error_flag) atomicExch(error_flag, 2);
   }
   if (inv_freq != nullptr) {
+    const float turned_by = (float)(position_ids ? position_ids[t] : pos);
     for (int i = threadIdx.x; i < head_dim / 2; i += blockDim.x) {
       float sn, cs;
-      sincosf((float)pos * inv_freq[i], &sn, &cs);
+      sincosf(turned_by * inv_freq[i], &sn, &cs);
       sincos_of_pair[i] = make_float2(sn, cs);
     }
     __syncthreads();
@@ -360,7 +365,7 @@ __global__ void rope_store_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __n
 }
 
 FMS_API int fms_rope_store(const void* qkv, int dtype, void* q_out, const float* inv_freq, const int* positions,
-                           const int* token_seq, const int* slots, void* k_cache, void* v_cache, const int* table,
+                           const int* position_ids, const int* token_seq, const int* slots, void* k_cache, void* v_cache, const int* table,
                            int table_stride, int block_tokens, int n_tokens, int nheads, int kvheads, int head_dim,
                            int write_cache, int* error_flag, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
@@ -370,7 +375,7 @@ FMS_API int fms_rope_store(const void* qkv, int dtype, void* q_out, const float*
     const int threads = total >= 256 ? 256 : ((total + 31) / 32) * 32;
     fms_launch(rope_store_vec_kernel, dim3(n_tokens), dim3(threads), (size_t)(head_dim / 2) * sizeof(float2), stream,
                (const __nv_bfloat16*)qkv,
-               (__nv_bfloat16*)q_out, inv_freq, positions, token_seq, slots, (__nv_bfloat16*)k_cache,
+               (__nv_bfloat16*)q_out, inv_freq, positions, position_ids, token_seq, slots, (__nv_bfloat16*)k_cache,
                (__nv_bfloat16*)v_cache, table, table_stride, block_tokens, nheads, kvheads, head_dim, write_cache,
                error_flag);
     return fms_launch_status("rope_store");
@@ -379,15 +384,18 @@ FMS_API int fms_rope_store(const void* qkv, int dtype, void* q_out, const float*
   const int threads = ((head_dim / 2 + 31) / 32) * 32;
   FMS_DISPATCH_DTYPE(dtype, T,
                      fms_launch(rope_store_kernel<T>, grid, dim3(threads), 0, stream, (const T*)qkv, (T*)q_out, inv_freq,
-                                positions, token_seq, slots, (T*)k_cache, (T*)v_cache, table, table_stride, block_tokens,
+                                positions, position_ids, token_seq, slots, (T*)k_cache, (T*)v_cache, table, table_stride,
+                                block_tokens,
                                 nheads, kvheads, head_dim, write_cache, error_flag));
   return fms_launch_status("rope_store");
 }
 
 // ---------------------------------------------------------------------------------------------------
-// start of a decode step: every sequence's new token sits at its current length, which then grows by one
+// start of a decode step: every sequence's new token sits at its current length, which then grows by one; the
+// position its encoding sees is that place plus the offset at which the sequence started (offsets null: none)
 // ---------------------------------------------------------------------------------------------------
-__global__ void decode_advance_kernel(int* __restrict__ positions, int* __restrict__ lengths, int n) {
+__global__ void decode_advance_kernel(int* __restrict__ positions, int* __restrict__ lengths,
+                                      const int* __restrict__ offsets, int* __restrict__ position_ids, int n) {
   pdl_launch_dependents();
   pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -395,11 +403,15 @@ __global__ void decode_advance_kernel(int* __restrict__ positions, int* __restri
     const int len = lengths[i];
     positions[i] = len;
     lengths[i] = len + 1;
+    if (offsets != nullptr) position_ids[i] = len + offsets[i];
   }
 }
 
-FMS_API int fms_decode_advance(int* positions, int* lengths, int n, cudaStream_t stream) {
+FMS_API int fms_decode_advance(int* positions, int* lengths, const int* offsets, int* position_ids, int n,
+                               cudaStream_t stream) {
   if (n <= 0) return 0;
-  fms_launch(decode_advance_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, positions, lengths, n);
+  if ((offsets == nullptr) != (position_ids == nullptr)) return fms_fail("decode_advance: offsets without position_ids");
+  fms_launch(decode_advance_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, positions, lengths, offsets, position_ids,
+             n);
   return fms_launch_status("decode_advance");
 }

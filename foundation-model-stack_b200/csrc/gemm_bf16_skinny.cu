@@ -32,7 +32,8 @@ enum Mode { ROWS16 = 0, QKV_ROPE = 1, GLU8 = 2 };
 struct RopeArgs {
   __nv_bfloat16* q_out;        // [M, nheads * head_dim]
   const float* inv_freq;       // [head_dim / 2], or null: nothing is rotated
-  const int* positions;        // [M]
+  const int* positions;        // [M] each token's place in its sequence's cache
+  const int* position_ids;     // [M] the position the rotation sees, or null: the same
   const int* token_seq;        // [M] index into slots
   const int* slots;
   __nv_bfloat16* k_cache;      // [blocks, kvheads, block_tokens, head_dim]
@@ -222,7 +223,7 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const __nv_bfloa
       const int pos = rope.positions[m];
       if (!is_v && rope.inv_freq != nullptr) {
         float sn, cs;
-        sincosf((float)pos * rope.inv_freq[d >> 1], &sn, &cs);
+        sincosf((float)(rope.position_ids ? rope.position_ids[m] : pos) * rope.inv_freq[d >> 1], &sn, &cs);
         const float r = cs * x0 - sn * x1;
         x1 = sn * x0 + cs * x1;
         x0 = r;
@@ -307,8 +308,8 @@ FMS_API int fms_linear_bf16_skinny(const void* x, const void* w, const void* bia
 // + bias; q and k rotated by each token's position; q -> q_out [M, nheads head_dim], k and v -> the token's place in
 // the block cache (write_cache 0: q only).  A token whose position has no block sets error flag 2 and is skipped.
 FMS_API int fms_qkv_rope_store_bf16_skinny(const void* x, const void* w, const void* bias, void* q_out,
-                                           const float* inv_freq, const int* positions, const int* token_seq,
-                                           const int* slots, void* k_cache, void* v_cache, const int* table,
+                                           const float* inv_freq, const int* positions, const int* position_ids,
+                                           const int* token_seq, const int* slots, void* k_cache, void* v_cache, const int* table,
                                            int table_stride, int block_tokens, int M, int K, int nheads, int kvheads,
                                            int head_dim, int write_cache, int* error_flag, cudaStream_t stream) {
   if (M <= 0) return 0;
@@ -319,7 +320,7 @@ FMS_API int fms_qkv_rope_store_bf16_skinny(const void* x, const void* w, const v
                     head_dim, block_tokens);
   const long rows = (long)(nheads + 2 * kvheads) * head_dim;
   if (rows > 0x7fffffffL) return fms_fail("qkv_rope_store_bf16_skinny: %ld rows of w", rows);
-  const RopeArgs rope{(__nv_bfloat16*)q_out, inv_freq, positions, token_seq, slots, (__nv_bfloat16*)k_cache,
+  const RopeArgs rope{(__nv_bfloat16*)q_out, inv_freq, positions, position_ids, token_seq, slots, (__nv_bfloat16*)k_cache,
                       (__nv_bfloat16*)v_cache, table, table_stride, block_tokens, nheads, kvheads, head_dim, write_cache,
                       error_flag};
   if (rows < 16384) return launch_typed<1, 1, QKV_ROPE, __nv_bfloat16>(x, w, bias, nullptr, M, (int)rows, K, 0, 0, stream, rope);

@@ -27,7 +27,10 @@ class Batch:
         self.total_len = 0  # tokens of all sequences after the step, as far as the host knows (kernels are chosen by it)
         self.num_new: List[int] = []
         self.tokens: Optional[torch.Tensor] = None  # [n_tokens] int32
-        self.positions: Optional[torch.Tensor] = None  # [n_tokens] int32
+        self.positions: Optional[torch.Tensor] = None  # [n_tokens] int32: each token's place in its sequence's cache
+        # [n_tokens] int32: the position each token's encoding sees, where that is not its place in the cache (a
+        # sequence that started at another position than 0); None: the same
+        self.position_ids: Optional[torch.Tensor] = None
         self.token_seq: Optional[torch.Tensor] = None  # [n_tokens] int32, index into the arrays below
         self.first_row: Optional[torch.Tensor] = None  # [n_seqs + 1] int32
         self.slots: Optional[torch.Tensor] = None  # [n_seqs] int32
@@ -38,7 +41,9 @@ class Batch:
 
     @staticmethod
     def from_lists(slots: Sequence[int], len_before: Sequence[int], tokens: Sequence[Sequence[int]],
-                   want: Sequence[Sequence[int]], device) -> "Batch":
+                   want: Sequence[Sequence[int]], device, offsets: Optional[Sequence[int]] = None) -> "Batch":
+        """``offsets[i]``: the position at which sequence i started (its token at place p of the cache has the
+        position p + offsets[i]); None: every sequence started at 0."""
         b = Batch()
         b.n_seqs = len(slots)
         b.num_new = [len(t) for t in tokens]
@@ -59,7 +64,8 @@ class Batch:
                     raise ValueError(f"wanted place {j} outside the {len(t)} tokens of this step")
                 rows.append(base + j)
         len_after = [lb + n for lb, n in zip(len_before, b.num_new)]
-        packed = torch.tensor(flat + pos + seq + first + list(slots) + len_after + rows, dtype=torch.int32)
+        ids = [p + offsets[i] for p, i in zip(pos, seq)] if offsets is not None and any(offsets) else []
+        packed = torch.tensor(flat + pos + seq + first + list(slots) + len_after + ids + rows, dtype=torch.int32)
         packed = packed.to(device)
         n, s = b.n_tokens, b.n_seqs
         o = 0
@@ -69,6 +75,8 @@ class Batch:
         b.first_row = packed[o:o + s + 1]; o += s + 1
         b.slots = packed[o:o + s]; o += s
         b.len_after = packed[o:o + s]; o += s
+        if ids:
+            b.position_ids = packed[o:o + n]; o += n
         b.want_rows = packed[o:]
         b.n_wanted = len(rows)
         b.len_before_host = list(len_before)

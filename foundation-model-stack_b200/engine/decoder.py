@@ -11,8 +11,8 @@ import torch
 from ..config.specs import DecoderSpec
 from ..kernels import ops
 from ..parts.base import Part
-from ..parts.block import Block
-from ..parts.registry import build_norm
+from ..parts import block as _blocks  # noqa: F401  (registers the built-in arrangement)
+from ..parts.registry import build_block, build_norm
 
 
 def _add_path(root: Part, path: str, part: Part) -> Part:
@@ -34,7 +34,7 @@ class Decoder(Part):
         self.embedding = _add_path(self, emb_name, Part())
         self.embedding.declare("weight", (spec.vocab_size, spec.dim), role="matrix")
         layer_list = _add_path(self, layers_name, Part())
-        self.blocks = [layer_list.add(str(i), Block(b)) for i, b in enumerate(spec.layers)]
+        self.blocks = [layer_list.add(str(i), build_block(b)) for i, b in enumerate(spec.layers)]
         self.final_norm = _add_path(self, norm_name, build_norm(spec.final_norm))
         self.head = _add_path(self, head_name, Part())
         if not spec.tie_head:
@@ -49,14 +49,22 @@ class Decoder(Part):
         self.device = torch.device(device)
         super().finalize(self.device, self.dtype)
 
+    def kernel_libraries(self, dtype):
+        head = ["gemm_f32"] if dtype == torch.float32 or self.head_weight().dtype == torch.float32 else \
+            ["gemm_bf16_skinny", "gemm_bf16_tc"]
+        return ["elementwise"] + head + super().kernel_libraries(dtype)
+
     def head_weight(self):
         return self.embedding.tensor("weight") if self.spec.tie_head else self.head.tensor("weight")
 
     def forward(self, batch, cache):
-        residual = ops.embed(self.embedding.tensor("weight"), batch.tokens)
+        residual = ops.embed(self.embedding.tensor("weight"), batch.tokens, self.spec.embedding_scale)
         pending = None
         for call in self.spec.schedule:
             view = cache.layer_view(call.cache_layer)
             pending = self.blocks[call.layer].forward(residual, pending, batch, view, call.writes_cache, self.dtype)
         h = self.final_norm.apply(residual, pending, self.dtype, rows=batch.want_rows)
-        return ops.linear(h, self.head_weight(), None, torch.float32)
+        logits = ops.linear(h, self.head_weight(), None, torch.float32)
+        if self.spec.logit_scale != 1.0:
+            logits.mul_(self.spec.logit_scale)
+        return logits

@@ -12,6 +12,7 @@ and, from its second occurrence on, as one CUDA graph launch instead of some hun
 """
 from __future__ import annotations
 
+import collections
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -40,6 +41,10 @@ class _DecodeBuffers:
         b.first_row = ar
         b.slots = torch.zeros(n, dtype=torch.int32, device=device)
         b.len_after = torch.zeros(n, dtype=torch.int32, device=device)  # between steps: the current lengths
+        # for sequences that did not start at position 0: what the encoding sees (batch.position_ids points at it
+        # while any of the loaded sequences has an offset, else stays None)
+        self.offsets = torch.zeros(n, dtype=torch.int32, device=device)
+        self.position_ids = torch.zeros(n, dtype=torch.int32, device=device)
         b.want_rows = ar[:n].clone()
         self.tokens_host = torch.zeros(n, dtype=torch.int32).pin_memory() if torch.device(device).type == "cuda" \
             else torch.zeros(n, dtype=torch.int32)
@@ -47,15 +52,18 @@ class _DecodeBuffers:
         self.copied = None  # event after the last copy out of tokens_host
         self.loaded: Optional[Tuple[int, ...]] = None  # slots whose state the arrays hold
         self.lengths: List[int] = []  # their lengths, as the device arrays have them
-        self.graphs: Dict[int, object] = {}  # key-split bound -> (graph, logits)
-        self.seen: Dict[int, int] = {}
+        self.seen: Dict[tuple, int] = {}  # a graph's key -> how often a step came with it
 
 
 class Engine:
     """A model's decoder together with a cache of a given size."""
 
     def __init__(self, model, max_tokens: int, max_slots: Optional[int] = None, sampling: bool = True,
-                 use_graphs: bool = True) -> None:
+                 use_graphs: bool = True, max_graphs: int = 16) -> None:
+        """``max_graphs``: the most captured decode steps the engine keeps (one per number of sequences and bound on
+        their lengths).  When one more is captured, the one used longest ago is dropped with its logits buffer, and
+        all captures draw their buffers from one pool; so a batch whose requests end one by one holds at most
+        ``max_graphs`` logits buffers [sequences, vocabulary] and one set of a step's intermediate buffers."""
         if model.decoder is None:
             raise ValueError("the model has no weights yet")
         self.model = model
@@ -69,33 +77,30 @@ class Engine:
         self.cache = Cache(self.decoder.cache_requests(), max_tokens, self.decoder.spec.max_positions,
                            self.decoder.dtype, self.device, max_slots)
         self.use_graphs = use_graphs and self.device.type == "cuda"
+        self.max_graphs = max(1, int(max_graphs))
         self._decode: Dict[int, _DecodeBuffers] = {}
+        # (sequences, bound on their lengths, with position offsets) -> (graph, logits), least recently used first
+        self._graphs: "collections.OrderedDict[tuple, Tuple[object, torch.Tensor]]" = collections.OrderedDict()
+        self._graph_pool = None
+        self.graphs_captured = 0
         self.h2d_bytes = 0  # bytes copied host -> device by steps since the engine was made
         self.graph_launches = 0
         self.kernels_per_graph = 0  # own kernels inside the decode graph captured last
 
     def _compile_what_this_model_needs(self, sampling: bool) -> None:
-        """Compiles, side by side, the kernel libraries this model will call and that are not built yet."""
+        """Compiles, side by side, the kernel libraries this model's parts name and that are not built yet."""
         from ..kernels import build
 
-        names = ["elementwise"]
-        tensors = self.decoder.state_dict().values()
-        if self.decoder.dtype == torch.float32 or any(t.dtype == torch.float32 and t.dim() == 2 for t in tensors):
-            names.append("gemm_f32")
-        if self.decoder.dtype == torch.bfloat16:
-            names += ["gemm_bf16_skinny", "gemm_bf16_tc"]
-        for block in self.decoder.blocks:
-            hd = getattr(block.mixer, "head_dim", None)
-            if hd and getattr(block.mixer, "kvheads", None):
-                names.append(f"attention_hd{hd}")
+        names = list(dict.fromkeys(self.decoder.kernel_libraries(self.decoder.dtype)))
         if sampling:
             names.append("sampling")
         build.compile_many(names)
 
     # ---- sequences ---------------------------------------------------------------------------
-    def begin(self, n: int) -> List[int]:
-        """Slots for n sequences that start together."""
-        return self.cache.begin(n)
+    def begin(self, n: int, first_positions: Optional[Sequence[int]] = None) -> List[int]:
+        """Slots for n sequences that start together.  ``first_positions``: the position of each sequence's first
+        token, where that is not 0 (the position encoding sees it; the cache holds the tokens from its place 0 on)."""
+        return self.cache.begin(n, first_positions)
 
     def release(self, slots: Sequence[int]) -> None:
         self.cache.release(slots)
@@ -121,8 +126,9 @@ class Engine:
             want = [[len(t) - 1] for t in tokens]
         num_new = [len(t) for t in tokens]
         before = self.cache.prepare(slots, num_new)
-        batch = Batch.from_lists(slots, before, tokens, want, self.device)
-        self.h2d_bytes += 4 * (3 * batch.n_tokens + 3 * batch.n_seqs + 1 + batch.n_wanted)
+        batch = Batch.from_lists(slots, before, tokens, want, self.device, [self.cache.offset(s) for s in slots])
+        self.h2d_bytes += 4 * ((3 if batch.position_ids is None else 4) * batch.n_tokens + 3 * batch.n_seqs + 1
+                               + batch.n_wanted)
         logits = self.decoder.forward(batch, self.cache)
         self.cache.commit(slots, num_new)
         return logits
@@ -133,8 +139,8 @@ class Engine:
         (``tokens``) or are already on the device (``tokens_device``, int32 [n], e.g. what the sampler
         wrote).  ``horizon``: the longest any of these sequences will get in this run, if the caller knows
         it; the launch is then sized for it once, instead of growing (and being captured anew) as the
-        sequences grow.  The result is a buffer that the next decode step of as many sequences
-        overwrites: use it, or copy it, before that."""
+        sequences grow.  The result is a buffer that the next decode step (of any number of sequences)
+        may overwrite: use it, or copy it, before that."""
         n = len(slots)
         if len(set(slots)) != n:
             raise ValueError("a slot appears twice in one step")
@@ -150,11 +156,14 @@ class Engine:
         if buf.copied is not None:
             buf.copied.synchronize()  # the last copy out of the pinned array is over
         if buf.loaded != key or buf.lengths != lengths:
-            state = torch.tensor([list(slots), lengths], dtype=torch.int32)
+            offsets = [self.cache.offset(s) for s in slots]
+            state = torch.tensor([list(slots), lengths, offsets], dtype=torch.int32)
             buf.batch.slots.copy_(state[0])
             buf.batch.len_after.copy_(state[1])
+            buf.offsets.copy_(state[2])
+            buf.batch.position_ids = buf.position_ids if any(offsets) else None
             buf.loaded, buf.lengths = key, lengths
-            self.h2d_bytes += 8 * n
+            self.h2d_bytes += 12 * n
         if tokens_device is not None:
             buf.batch.tokens.copy_(tokens_device)
         else:
@@ -166,13 +175,21 @@ class Engine:
                     buf.copied = torch.cuda.Event()
                 buf.copied.record()
         buf.batch.total_len = sum(lengths) + n  # read when a graph is captured: the lengths only grow from here
-        logits = self._run_decode(buf, max(max(lengths) + 1, min(int(horizon), self.cache.max_positions)))
+        try:
+            logits = self._run_decode(buf, max(max(lengths) + 1, min(int(horizon), self.cache.max_positions)))
+        except BaseException:
+            # the device arrays may be a step ahead of the cache now: have the next step bring them anew
+            buf.loaded, buf.lengths = None, []
+            raise
         self.cache.commit(slots, [1] * n)
         buf.lengths = [x + 1 for x in lengths]
         return logits
 
     def _decode_body(self, buf: _DecodeBuffers) -> torch.Tensor:
-        ops.decode_advance(buf.batch.positions, buf.batch.len_after)
+        if buf.batch.position_ids is None:
+            ops.decode_advance(buf.batch.positions, buf.batch.len_after)
+        else:
+            ops.decode_advance(buf.batch.positions, buf.batch.len_after, buf.offsets, buf.position_ids)
         return self.decoder.forward(buf.batch, self.cache)
 
     def _run_decode(self, buf: _DecodeBuffers, longest: int) -> torch.Tensor:
@@ -185,17 +202,25 @@ class Engine:
         buf.batch.max_len_after = max(bound, longest)
         if not self.use_graphs:
             return self._decode_body(buf)
-        entry = buf.graphs.get(bound)
+        key = (buf.n, bound, buf.batch.position_ids is not None)
+        entry = self._graphs.get(key)
         if entry is None:
-            buf.seen[bound] = buf.seen.get(bound, 0) + 1
-            if buf.seen[bound] == 1:
+            buf.seen[key] = buf.seen.get(key, 0) + 1
+            if buf.seen[key] == 1:
                 return self._decode_body(buf)  # first occurrence: plain launches (they also warm everything up)
+            while len(self._graphs) >= self.max_graphs:
+                self._graphs.popitem(last=False)  # the one used longest ago, with its logits buffer
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
             graph = torch.cuda.CUDAGraph()
             before = ops.launches
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph, pool=self._graph_pool):
                 logits = self._decode_body(buf)
             self.kernels_per_graph = ops.launches - before
-            entry = buf.graphs[bound] = (graph, logits)
+            self.graphs_captured += 1
+            entry = self._graphs[key] = (graph, logits)
+        else:
+            self._graphs.move_to_end(key)
         entry[0].replay()
         self.graph_launches += 1
         return entry[1]

@@ -24,15 +24,16 @@ F32, BF16 = 0, 1
 _P, _I, _F, _U64, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_ulonglong, ctypes.c_long
 
 _SIGNATURES = {
-    "fms_embed_rows": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
+    "fms_embed_rows": [_P, _I, _P, _P, _I, _I, _I, _F, _P, _P],
     "fms_add_rmsnorm": [_P, _P, _P, _I, _F, _P, _I, _P, _I, _I, _P],
     "fms_gated_activation": [_P, _P, _I, _I, _I, _I, _P],
-    "fms_rope_store": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
-    "fms_decode_advance": [_P, _P, _I, _P],
+    "fms_rope_store": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "fms_decode_advance": [_P, _P, _P, _P, _I, _P],
     "fms_gemm_f32": [_P, _P, _P, _P, _I, _I, _I, _P],
     "fms_linear_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "fms_glu_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
-    "fms_qkv_rope_store_bf16_skinny": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "fms_qkv_rope_store_bf16_skinny": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P,
+                                       _P],
     "fms_gemm_bf16_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "fms_glu_bf16_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "fms_argmax": [_P, _P, _I, _I, _P],
@@ -134,12 +135,12 @@ def check_error_flag(device) -> None:
 
 
 # ---- embedding ---------------------------------------------------------------------------------------
-def embed(table: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
-    """Float32 rows of ``table`` at ``tokens``: the start of the residual stream."""
+def embed(table: torch.Tensor, tokens: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """Float32 rows of ``table`` at ``tokens``, times ``scale``: the start of the residual stream."""
     n, dim = tokens.shape[0], table.shape[1]
     out = torch.empty((n, dim), dtype=torch.float32, device=table.device)
     _call("elementwise", "fms_embed_rows", _ptr(table), _code(table.dtype), _ptr(tokens), _ptr(out), n, dim,
-          table.shape[0], _ptr(error_flag(table.device)), _stream())
+          table.shape[0], float(scale), _ptr(error_flag(table.device)), _stream())
     return out
 
 
@@ -257,13 +258,16 @@ def gated_activation(gate_up: torch.Tensor, activation: int) -> torch.Tensor:
 def rope_store(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], batch, view, nheads: int, kvheads: int,
                head_dim: int, writes_cache: bool = True) -> torch.Tensor:
     """Rotates q and k of ``qkv`` [tokens, (nheads + 2 kvheads) head_dim] by each token's position, writes k
-    and v into the cache at the token's slot and position, returns the rotated q [tokens, nheads head_dim]."""
+    and v into the cache at the token's slot and place, returns the rotated q [tokens, nheads head_dim].  The
+    rotation sees ``batch.position_ids`` where the batch has them (sequences that did not start at position 0),
+    else the token's place in the cache, ``batch.positions``; ``inv_freq`` None rotates nothing."""
     n = qkv.shape[0]
     if view.keys.dtype != qkv.dtype:
         raise KernelError(f"cache is {view.keys.dtype}, activations are {qkv.dtype}")
     q = torch.empty((n, nheads * head_dim), dtype=qkv.dtype, device=qkv.device)
     _call("elementwise", "fms_rope_store", _ptr(qkv), _code(qkv.dtype), _ptr(q), _ptr(inv_freq), _ptr(batch.positions),
-          _ptr(batch.token_seq), _ptr(batch.slots), _ptr(view.keys), _ptr(view.values), _ptr(view.table),
+          _ptr(getattr(batch, "position_ids", None)), _ptr(batch.token_seq), _ptr(batch.slots), _ptr(view.keys),
+          _ptr(view.values), _ptr(view.table),
           view.table.shape[1], view.block_tokens, n, nheads, kvheads, head_dim, 1 if writes_cache else 0,
           _ptr(error_flag(qkv.device)), _stream())
     return q
@@ -284,8 +288,9 @@ def qkv_rope_store(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
         n = x.shape[0]
         q = torch.empty((n, nheads * head_dim), dtype=x.dtype, device=x.device)
         _call("gemm_bf16_skinny", "fms_qkv_rope_store_bf16_skinny", _ptr(x), _ptr(weight), _ptr(bias), _ptr(q),
-              _ptr(inv_freq), _ptr(batch.positions), _ptr(batch.token_seq), _ptr(batch.slots), _ptr(view.keys),
-              _ptr(view.values), _ptr(view.table), view.table.shape[1], view.block_tokens, n, weight.shape[1], nheads,
+              _ptr(inv_freq), _ptr(batch.positions), _ptr(getattr(batch, "position_ids", None)), _ptr(batch.token_seq),
+              _ptr(batch.slots), _ptr(view.keys), _ptr(view.values), _ptr(view.table), view.table.shape[1],
+              view.block_tokens, n, weight.shape[1], nheads,
               kvheads, head_dim, 1 if writes_cache else 0, _ptr(error_flag(x.device)), _stream())
         return q
     return rope_store(linear(x, weight, bias), inv_freq, batch, view, nheads, kvheads, head_dim, writes_cache)
@@ -342,9 +347,12 @@ def attention_stream_launches(head_dim: int) -> int:
     return int(lib.fms_attn_stream_launches())
 
 
-def decode_advance(positions: torch.Tensor, lengths: torch.Tensor) -> None:
-    """positions[i] = lengths[i]; lengths[i] += 1 — the bookkeeping of a decode step, on the device."""
-    _call("elementwise", "fms_decode_advance", _ptr(positions), _ptr(lengths), positions.shape[0], _stream())
+def decode_advance(positions: torch.Tensor, lengths: torch.Tensor, offsets: Optional[torch.Tensor] = None,
+                   position_ids: Optional[torch.Tensor] = None) -> None:
+    """positions[i] = lengths[i]; lengths[i] += 1 — the bookkeeping of a decode step, on the device.  With
+    ``offsets`` (sequences that did not start at position 0) also position_ids[i] = positions[i] + offsets[i]."""
+    _call("elementwise", "fms_decode_advance", _ptr(positions), _ptr(lengths), _ptr(offsets), _ptr(position_ids),
+          positions.shape[0], _stream())
 
 
 # ---- sampling ----------------------------------------------------------------------------------------

@@ -56,10 +56,11 @@ class Model:
     def state_dict(self):
         return self.decoder.state_dict()
 
-    def new_engine(self, max_tokens: int, max_slots: Optional[int] = None, sampling: bool = True):
+    def new_engine(self, max_tokens: int, max_slots: Optional[int] = None, sampling: bool = True, **engine_options):
+        """``engine_options``: further keyword arguments of ``Engine`` (``use_graphs``, ``max_graphs``)."""
         from ..engine.step import Engine
 
-        return Engine(self, max_tokens=max_tokens, max_slots=max_slots, sampling=sampling)
+        return Engine(self, max_tokens=max_tokens, max_slots=max_slots, sampling=sampling, **engine_options)
 
     def engine(self, min_tokens: int = 0, min_slots: int = 0):
         """The model's own engine, made on first use and made anew when it is too small."""

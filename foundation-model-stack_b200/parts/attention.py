@@ -45,6 +45,9 @@ class MultiHeadAttention(Part):
         self.dense = self.add("dense", Linear(spec.nheads * spec.head_dim, spec.dim, spec.bias))
         # not a child: the encoding has no checkpoint tensors of its own and may be shared
         self.position = build_position(spec.position)
+        if self.position.score_bias() is not None:
+            raise ValueError(f"position encoding {spec.position.kind!r} adds to the attention scores; the attention "
+                             "kernels of this mixer take no such term")
 
     def finalize(self, device, dtype) -> None:
         super().finalize(device, dtype)
@@ -54,12 +57,14 @@ class MultiHeadAttention(Part):
         return KVRequest(self.kvheads, self.head_dim, self.window)
 
     def forward(self, x, batch, cache_view, writes_cache: bool = True):
-        q = ops.qkv_rope_store(
-            x, self.qkv.tensor("weight"), self.qkv.tensor("bias"), self.position.rotary_frequencies(), batch, cache_view,
-            self.nheads, self.kvheads, self.head_dim, writes_cache,
-        )
+        # the position part applies the projection, encodes q and k and writes k and v into the cache
+        q = self.position.project(x, self.qkv, batch, cache_view, self.nheads, self.kvheads, self.head_dim, writes_cache)
         o = ops.attention(q, batch, cache_view, self.nheads, self.kvheads, self.head_dim, self.scale, self.window)
         return self.dense.forward(o)
+
+    def kernel_libraries(self, dtype):
+        return (super().kernel_libraries(dtype) + self.position.kernel_libraries(dtype)
+                + ["elementwise", f"attention_hd{self.head_dim}"])
 
 
 register_mixer("attention", MultiHeadAttention)

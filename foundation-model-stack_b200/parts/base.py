@@ -8,7 +8,7 @@ integer table.
 from __future__ import annotations
 
 import dataclasses
-from typing import Dict, Iterator, Optional, Tuple
+from typing import Dict, Iterator, List, Optional, Tuple
 
 import torch
 
@@ -75,3 +75,12 @@ class Part:
         """Called once after all tensors are set: build derived tables on the device."""
         for _, c in self._children.items():
             c.finalize(device, dtype)
+
+    def kernel_libraries(self, dtype: torch.dtype) -> List[str]:
+        """Names of the kernel libraries (``fms_b200.kernels.build``) that this part and the parts below it call
+        when the model computes in ``dtype``; the engine compiles them before the first step.  A part that calls
+        kernels of its own adds their libraries' names to what this returns."""
+        out: List[str] = []
+        for _, c in self._children.items():
+            out += c.kernel_libraries(dtype)
+        return out

@@ -33,5 +33,8 @@ class GatedLinearUnit(Part):
         h = ops.gated_linear(x, self.gate_up.tensor("weight"), self.gate_up.tensor("bias"), self.activation)
         return self.down.forward(h)
 
+    def kernel_libraries(self, dtype):
+        return super().kernel_libraries(dtype) + ["elementwise"]
+
 
 register_feed_forward("glu", GatedLinearUnit)

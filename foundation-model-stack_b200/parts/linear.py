@@ -2,6 +2,8 @@
 (the reference's ``get_linear`` default, fms/modules/linear.py:119-156)."""
 from __future__ import annotations
 
+import torch
+
 from ..kernels import ops
 from .base import Part
 
@@ -17,3 +19,9 @@ class Linear(Part):
 
     def forward(self, x, out_dtype=None):
         return ops.linear(x, self.tensor("weight"), self.tensor("bias"), out_dtype)
+
+    def kernel_libraries(self, dtype):
+        w = self.tensor("weight")
+        if dtype == torch.float32 or (w is not None and w.dtype == torch.float32):
+            return ["gemm_f32"]
+        return ["gemm_bf16_skinny", "gemm_bf16_tc"]

@@ -29,5 +29,8 @@ class RMSNorm(Part):
     def apply(self, residual, delta, out_dtype, rows=None):
         return ops.add_rmsnorm(residual, delta, self.tensor("weight"), self.eps, out_dtype, rows)
 
+    def kernel_libraries(self, dtype):
+        return ["elementwise"]
+
 
 register_norm("rmsnorm", RMSNorm)

@@ -32,4 +32,4 @@ def tiny_folders(tmp_path_factory):
     from tiny_models import write_tiny
 
     root = tmp_path_factory.mktemp("tiny_models")
-    return {w: write_tiny(str(root / w), w) for w in ("a", "b", "c")}
+    return {w: write_tiny(str(root / w), w) for w in ("a", "b", "c", "d", "e")}

@@ -58,15 +58,30 @@ def main(reference_root: str):
     from fms.models import get_model
     from safetensors.torch import save_file
 
-    from tiny_models import TINY, tiny_prompts, tiny_tensors, write_tiny
+    from tiny_models import TINY, tiny_prompts, tiny_tensors_of, write_tiny
 
     out = {}
-    for which in ("a", "b", "c"):
-        cfg, seed, gain_dtype = TINY[which]
+    for which in sorted(TINY):
         folder = write_tiny(tempfile.mkdtemp(), which)
-        model = get_model("hf_pretrained", model_path=folder, data_type=torch.float32, device_type="cpu")
+        cfg = TINY[which][0]
+        if cfg.get("rope_scaling"):
+            # With transformers 5 the reference's "hf_pretrained" route finds config.json's rope_scaling folded into
+            # rope_parameters, where it does not look for it (fms/models/hf/config_utils/param_builders.py:17-34),
+            # and builds the model without the rescaling.  Its other route takes the configuration as keyword
+            # arguments, the rescaling among them.
+            model = get_model(
+                "llama", "micro", model_path=folder, source="hf", data_type=torch.float32, device_type="cpu",
+                src_vocab_size=cfg["vocab_size"], emb_dim=cfg["hidden_size"], nheads=cfg["num_attention_heads"],
+                kvheads=cfg["num_key_value_heads"], nlayers=cfg["num_hidden_layers"],
+                hidden_grow_factor=cfg["intermediate_size"] / cfg["hidden_size"], multiple_of=1,
+                norm_eps=cfg["rms_norm_eps"], max_expected_seq_len=cfg["max_position_embeddings"],
+                attn_bias=cfg["attention_bias"], mlp_bias=cfg["mlp_bias"], tie_heads=cfg["tie_word_embeddings"],
+                rope_theta=cfg["rope_theta"], rope_scaling=cfg["rope_scaling"])
+            assert type(model.base_model.rot_emb.rope_scaling).__name__ == "RopeLlama3ScalingImpl"
+        else:
+            model = get_model("hf_pretrained", model_path=folder, data_type=torch.float32, device_type="cpu")
         model.eval()
-        tensors = tiny_tensors(cfg, seed, gain_dtype)
+        tensors = tiny_tensors_of(which)
         out[f"{which}.weight_abs_sum"] = torch.stack(
             [t.float().abs().sum() for _, t in sorted(tensors.items())]
         ).sum().reshape(1).double()

@@ -216,12 +216,13 @@ class PlainLlama:
         )
         return x + f
 
-    def logits(self, ids: Sequence[int], rows: Optional[Sequence[int]] = None) -> torch.Tensor:
+    def logits(self, ids: Sequence[int], rows: Optional[Sequence[int]] = None, first_position: int = 0) -> torch.Tensor:
         """Logits at every position of one whole sequence: [S, vocab]
         (fms/models/llama.py:318-357 and :425-450).  With ``rows`` the head is applied at those positions
-        only (the layers still run the whole sequence): [len(rows), vocab]."""
+        only (the layers still run the whole sequence): [len(rows), vocab].  ``first_position``: the position
+        of the first token (the reference's position_ids, fms/models/llama.py:337-343; 0 by default)."""
         ids_t = torch.as_tensor(list(ids), dtype=torch.long)
-        positions = torch.arange(ids_t.shape[0])
+        positions = torch.arange(ids_t.shape[0]) + int(first_position)
         x = plain_embedding(ids_t, self.w["model.embed_tokens.weight"])
         for i in range(self.c["nlayers"]):
             x = self.block(i, x, positions)

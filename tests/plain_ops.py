@@ -14,8 +14,8 @@ import torch
 from plain_llama import plain_uniform
 
 
-def embed(table, tokens):
-    return table[tokens.long()].float()
+def embed(table, tokens, scale=1.0):
+    return table[tokens.long()].float() * scale
 
 
 def add_rmsnorm(residual, delta, gain, eps, out_dtype, rows=None):
@@ -54,9 +54,10 @@ def gated_linear(x, weight, bias, activation):
 def rope_store(qkv, inv_freq, batch, view, nheads, kvheads, head_dim, writes_cache=True):
     n = qkv.shape[0]
     x = qkv.float().view(n, nheads + 2 * kvheads, head_dim)
-    pos = batch.positions.long()
+    pos = batch.positions.long()  # the place in the cache
+    ids = getattr(batch, "position_ids", None)  # what the rotation sees, where that differs
     if inv_freq is not None:
-        ang = torch.outer(pos.float(), inv_freq.float().cpu().to(qkv.device))
+        ang = torch.outer((pos if ids is None else ids.long()).float(), inv_freq.float().cpu().to(qkv.device))
         cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
         rot = x[:, : nheads + kvheads]
         x0, x1 = rot[..., 0::2], rot[..., 1::2]
@@ -107,8 +108,10 @@ def attention(q, batch, view, nheads, kvheads, head_dim, scale, window):
     return out
 
 
-def decode_advance(positions, lengths):
+def decode_advance(positions, lengths, offsets=None, position_ids=None):
     positions.copy_(lengths)
+    if offsets is not None:
+        position_ids.copy_(lengths + offsets)
     lengths += 1
 
 

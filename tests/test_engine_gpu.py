@@ -62,7 +62,7 @@ def long_requests(which, n=5, seed=0):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("which", ["a", "b", "c"])
+@pytest.mark.parametrize("which", ["a", "b", "c", "d", "e"])
 def test_each_request_alone_and_whole(models, oracles, which, dtype):
     engine = models(which, dtype).new_engine(max_tokens=1024)
     for req in tiny_prompts(which) + long_requests(which, 4):
@@ -74,7 +74,7 @@ def test_each_request_alone_and_whole(models, oracles, which, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("which", ["a", "b", "c"])
+@pytest.mark.parametrize("which", ["a", "b", "c", "d", "e"])
 def test_last_32_tokens_one_by_one(models, oracles, which, dtype):
     engine = models(which, dtype).new_engine(max_tokens=1024)
     for req in long_requests(which, 6):
@@ -92,7 +92,7 @@ def test_last_32_tokens_one_by_one(models, oracles, which, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("which", ["a", "b", "c"])
+@pytest.mark.parametrize("which", ["a", "b", "c", "d", "e"])
 def test_unequal_batches_one_after_another_with_reuse(models, oracles, which, dtype):
     """Three batches on a cache that holds only one of them: every slot and block is used again.  Freed
     blocks are filled with NaN, so anything stale that is read shows."""
@@ -133,12 +133,14 @@ def test_unequal_batches_one_after_another_with_reuse(models, oracles, which, dt
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_long_decoding(models, oracles, dtype):
-    """A short prompt, then hundreds of tokens one by one: across block edges and decode splits."""
+@pytest.mark.parametrize("which", ["c", "d"])
+def test_long_decoding(models, oracles, which, dtype):
+    """A short prompt, then hundreds of tokens one by one: across block edges and decode splits ("d": with
+    attention that a few keys carry)."""
     g = torch.Generator().manual_seed(60)
-    req = torch.randint(0, TINY["c"][0]["vocab_size"], (600,), generator=g).tolist()
-    want = oracles["c"].logits(req)
-    engine = models("c", dtype).new_engine(max_tokens=640)
+    req = torch.randint(0, TINY[which][0]["vocab_size"], (600,), generator=g).tolist()
+    want = oracles[which].logits(req)
+    engine = models(which, dtype).new_engine(max_tokens=640)
     (slot,) = engine.begin(1)
     parts = [engine.step([slot], [req[:3]], [[0, 1, 2]])]
     for t in range(3, len(req)):
@@ -165,7 +167,7 @@ def test_first_tokens_of_a_sequence(models, oracles, which, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("which", ["b", "c"])
+@pytest.mark.parametrize("which", ["b", "c", "d", "e"])
 def test_prompts_cut_into_steps_of_several_tokens(models, oracles, which, dtype):
     """Two requests whose tokens come in pieces of unequal sizes (several tokens onto what is already cached,
     across the edges of cache blocks, one request resting while the other goes on): the same logits as whole.
@@ -260,6 +262,76 @@ def test_bfloat16_greedy_generation(models, oracles):
         close(got, want, "bf16")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_steps_that_ask_for_no_logits(models, oracles, dtype):
+    """A prompt that comes in three pieces of which only the last asks for logits, beside a request that asks at every
+    place; then a step in which nobody asks for anything (an empty result), then single tokens again."""
+    engine = models("d", dtype).new_engine(max_tokens=1024)
+    a, b = long_requests("d", 5)[1:3]  # 300 and 65 tokens
+    want_a, want_b = oracles["d"].logits(a), oracles["d"].logits(b)
+    slots = engine.begin(2)
+    lg = engine.step(slots, [a[:100], b[:20]], [[], list(range(20))])
+    assert lg.shape[0] == 20
+    got_b = [lg]
+    lg = engine.step(slots, [a[100:170], b[20:21]], [[], [0]])  # one of the two brings a single token
+    got_b.append(lg)
+    nothing = engine.step(slots, [a[170:250], b[21:40]], [[], []])
+    assert tuple(nothing.shape) == (0, want_a.shape[1])
+    lg = engine.step(slots, [a[250:298], b[40:]], [[47], list(range(25))])
+    got_a = [lg[:1]]
+    got_b.append(lg[1:])
+    for t in (298, 299):
+        got_a.append(engine.step([slots[0]], [[a[t]]]))
+    engine.release(slots)
+    engine.check()
+    close(torch.cat(got_a), want_a[297:], dtype)
+    close(torch.cat(got_b), torch.cat([want_b[:21], want_b[40:]]), dtype)
+
+
+def test_a_batch_whose_requests_end_one_by_one_keeps_few_graphs(models, oracles):
+    """Thirty-two requests that start together and end one at a time: decode steps of 32, 31, ... 1 sequences, each
+    size for several steps, so each is captured.  The engine keeps at most ``max_graphs`` captures (and their logits
+    buffers), all drawing from one pool: the logits stay right and a second pass over the same schedule holds no more
+    memory than the first."""
+    model = models("d", "bf16")
+    engine = model.new_engine(max_tokens=64 * 2 * 32, max_slots=32, max_graphs=4)
+    g = torch.Generator().manual_seed(90)
+    reqs = [torch.randint(0, TINY["d"][0]["vocab_size"], (20 + 3 * i,), generator=g).tolist() for i in range(32)]
+    want = [oracles["d"].logits(r) for r in reqs]
+    prompt = 12
+
+    def run():
+        slots = engine.begin(32)
+        got = [[] for _ in reqs]
+        lg = engine.step(slots, [r[:prompt] for r in reqs])
+        for i in range(32):
+            got[i].append(lg[i:i + 1])
+        at = [prompt] * 32
+        live = list(range(32))
+        while live:
+            lg = engine.step([slots[i] for i in live], [[reqs[i][at[i]]] for i in live])
+            for j, i in enumerate(live):
+                got[i].append(lg[j:j + 1])
+                at[i] += 1
+            for i in [i for i in live if at[i] == len(reqs[i])]:
+                engine.release([slots[i]])
+                live.remove(i)
+        for i in range(32):
+            close(torch.cat(got[i]), want[i][prompt - 1:], "bf16")
+
+    run()
+    torch.cuda.synchronize()
+    first = torch.cuda.memory_allocated()
+    captured = engine.graphs_captured
+    assert captured >= 30 and len(engine._graphs) <= 4
+    run()
+    torch.cuda.synchronize()
+    assert engine.graphs_captured > captured  # dropped captures are made again when their size comes back
+    assert len(engine._graphs) <= 4
+    assert torch.cuda.memory_allocated() <= first + (1 << 20)
+    engine.check()
+
+
 def _trace_lines(reqs, prefill):
     """Steps of one batch: prompts together, then one token each; shorter requests end earlier."""
     lines, step = [], 0
@@ -306,6 +378,29 @@ def test_trace_run_program(tiny_folders, oracles, tmp_path, dtype):
         assert o == data.shape[0]
     for i, r in enumerate(reqs):
         close(torch.cat(got[i]), oracles["b"].logits(r), "fp32" if dtype == "float32" else "bf16")
+
+
+def test_trace_run_with_steps_that_want_nothing(tiny_folders, oracles, tmp_path):
+    """A prompt cut into three steps of which only the last asks for logits (no file for the first two), and a
+    step with an empty ``entries`` list."""
+    import numpy as np
+
+    req = long_requests("d", 5)[1]
+    want = oracles["d"].logits(req)
+    vocab = TINY["d"][0]["vocab_size"]
+    lines = [{"step": 0, "entries": [{"id": "p", "tokens": req[:128], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "p", "tokens": req[128:130]}], "end": []},
+             {"step": 2, "entries": [], "end": []},
+             {"step": 3, "entries": [{"id": "p", "tokens": req[130:], "want": [0, len(req) - 131]}], "end": ["p"]}]
+    proc = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", tiny_folders["d"], "--dtype", "float32", "--out",
+         str(tmp_path), "--max-tokens", "320"], input="\n".join(json.dumps(l) for l in lines) + "\n", capture_output=True,
+        text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split() == ["done", "0", "done", "1", "done", "2", "done", "3"]
+    assert sorted(os.listdir(tmp_path)) == ["3.f32"]
+    got = torch.from_numpy(np.fromfile(tmp_path / "3.f32", dtype="<f4").reshape(-1, vocab).copy())
+    close(got, want[[130, len(req) - 1]], "fp32")
 
 
 def test_trace_run_answers_each_step_before_the_next_is_written(tiny_folders, oracles, tmp_path):
@@ -381,130 +476,128 @@ def test_further_configurations_against_the_plain_implementation(tmp_path, name,
     close(torch.stack(rows, 1).reshape(-1, cfg["vocab_size"]), want, dtype)
 
 
-def test_head_size_128_model_bfloat16_against_float32(tmp_path):
-    """A model with the head size, group size and widths (in small) of the benchmark's: prompts long enough for
-    the tcgen05 product (1,024 rows and more in one step), decode through the weight-streaming product and the CUDA graph.
-    The float32 path — itself checked against the plain implementation on the tiny models — is the yardstick."""
-    from fms_b200.models import get_model
-    from fms_b200.models.llama import LLaMA, LLaMAConfig
-    from fms_b200.weights import write_random_model
+def _peaked_model(tmp_path, qk_std, **sizes):
+    """A model folder of the given sizes whose q and k projections are drawn wide enough for attention scores with a
+    standard deviation between 1.5 and 2, and its oracle."""
+    from tiny_models import llama_config, tiny_tensors, write_folder
 
-    arch = LLaMA(LLaMAConfig(src_vocab_size=4099, emb_dim=1024, nheads=8, kvheads=2, nlayers=2, hidden_dim=2816,
-                             max_expected_seq_len=2048, rope_theta=500000.0))
-    folder = write_random_model(str(tmp_path / "m"), arch.config_json(), arch.checkpoint_layout(), seed=5)
+    cfg = llama_config(**sizes)
+    folder = write_folder(str(tmp_path / "m"), cfg, tiny_tensors(cfg, 5, torch.float32, qk_std=qk_std))
+    return folder, pl.PlainLlama(folder)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_head_size_128_model(tmp_path, dtype):
+    """A model with the head size, group size and widths (in small) of the benchmark's: prompts long enough for
+    the tcgen05 product (1,024 rows and more in one step) and the tcgen05 attention, decode through the
+    weight-streaming product and the CUDA graph."""
+    from fms_b200.models import get_model
+
+    folder, oracle = _peaked_model(tmp_path, 0.04, vocab=4099, hidden=1024, intermediate=2816, layers=2, heads=8, kvheads=2,
+                                   theta=5e5, context=2048)
     g = torch.Generator().manual_seed(70)
     reqs = [torch.randint(0, 4099, (k,), generator=g).tolist() for k in (900, 300, 41)]
-    out = {}
-    for dtype in ("fp32", "bf16"):
-        engine = get_model("hf_pretrained", model_path=folder, device_type="cuda", data_type=dtype).new_engine(2048)
-        slots = engine.begin(3)
-        cut = [len(r) - 5 for r in reqs]
-        rows = [engine.step(slots, [r[:c] for r, c in zip(reqs, cut)], [[0, c // 2, c - 1] for c in cut]).float().cpu()]
-        for t in range(5):
-            rows.append(engine.step(slots, [[r[c + t]] for r, c in zip(reqs, cut)]).float().cpu())
-        engine.release(slots)
-        engine.check()
-        out[dtype] = torch.cat(rows)
-    close(out["bf16"], out["fp32"], "bf16")
-    assert (out["bf16"].argmax(-1) == out["fp32"].argmax(-1)).float().mean() > 0.9
+    engine = get_model("hf_pretrained", model_path=folder, device_type="cuda", data_type=dtype).new_engine(2048)
+    slots = engine.begin(3)
+    cut = [len(r) - 5 for r in reqs]
+    places = [[0, c // 2, c - 1] for c in cut]
+    first = engine.step(slots, [r[:c] for r, c in zip(reqs, cut)], places)
+    rows = [engine.step(slots, [[r[c + t]] for r, c in zip(reqs, cut)]) for t in range(5)]
+    engine.release(slots)
+    engine.check()
+    for i, (r, c) in enumerate(zip(reqs, cut)):
+        got = torch.cat([first[3 * i:3 * i + 3]] + [x[i:i + 1] for x in rows])
+        close(got, oracle.logits(r, rows=places[i] + list(range(c, len(r)))), dtype)
 
 
-def test_many_short_requests_in_one_batch_bfloat16_against_float32(tmp_path):
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_many_short_requests_in_one_batch(tmp_path, dtype):
     """Forty requests of 1 to 120 tokens in one batch (prompts in one step of more than a thousand rows, whose
-    attention tiles span many sequences; then decode steps of forty rows, which take the library product), on the
-    model shape of the test above; the float32 path is the yardstick."""
+    attention tiles span many sequences; then decode steps of forty rows), on the model shape of the test above."""
     from fms_b200.models import get_model
-    from fms_b200.models.llama import LLaMA, LLaMAConfig
-    from fms_b200.weights import write_random_model
 
-    arch = LLaMA(LLaMAConfig(src_vocab_size=4099, emb_dim=1024, nheads=8, kvheads=2, nlayers=2, hidden_dim=2816,
-                             max_expected_seq_len=2048, rope_theta=500000.0))
-    folder = write_random_model(str(tmp_path / "m"), arch.config_json(), arch.checkpoint_layout(), seed=6)
+    folder, oracle = _peaked_model(tmp_path, 0.04, vocab=4099, hidden=1024, intermediate=2816, layers=2, heads=8, kvheads=2,
+                                   theta=5e5, context=2048)
     g = torch.Generator().manual_seed(71)
     lens = [1, 2, 63, 64, 65, 120] + [int(v) for v in torch.randint(1, 121, (34,), generator=g)]
     reqs = [torch.randint(0, 4099, (k + 3,), generator=g).tolist() for k in lens]
     assert sum(lens) > 1024
-    out = {}
-    for dtype in ("fp32", "bf16"):
-        engine = get_model("hf_pretrained", model_path=folder, device_type="cuda", data_type=dtype).new_engine(64 * 120)
-        slots = engine.begin(len(reqs))
-        rows = [engine.step(slots, [r[:k] for r, k in zip(reqs, lens)], [[k - 1] for k in lens]).float().cpu()]
-        for t in range(3):
-            rows.append(engine.step(slots, [[r[k + t]] for r, k in zip(reqs, lens)]).float().cpu())
-        engine.release(slots)
-        engine.check()
-        out[dtype] = torch.cat(rows)
-    close(out["bf16"], out["fp32"], "bf16")
-    assert (out["bf16"].argmax(-1) == out["fp32"].argmax(-1)).float().mean() > 0.9
+    engine = get_model("hf_pretrained", model_path=folder, device_type="cuda", data_type=dtype).new_engine(64 * 120)
+    slots = engine.begin(len(reqs))
+    rows = [engine.step(slots, [r[:k] for r, k in zip(reqs, lens)], [[k - 1] for k in lens])]
+    for t in range(3):
+        rows.append(engine.step(slots, [[r[k + t]] for r, k in zip(reqs, lens)]))
+    engine.release(slots)
+    engine.check()
+    got = torch.stack(rows, 1)
+    for i, (r, k) in enumerate(zip(reqs, lens)):
+        close(got[i], oracle.logits(r, rows=list(range(k - 1, k + 3))), dtype)
 
 
-def test_decode_of_many_long_sequences_bfloat16_against_float32(tmp_path):
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decode_of_many_long_sequences(tmp_path, dtype):
     """Sixty-four requests of 700 to 1,000 tokens: enough keys and values for decode attention to take its
-    streaming kernel (persistent warps fed by TMA), first by plain launches, then inside the captured graph.  The
-    float32 path is the yardstick."""
+    streaming kernel (persistent warps fed by TMA), first by plain launches, then inside the captured graph."""
     from fms_b200.kernels import ops
     from fms_b200.models import get_model
-    from fms_b200.models.llama import LLaMA, LLaMAConfig
-    from fms_b200.weights import write_random_model
 
-    arch = LLaMA(LLaMAConfig(src_vocab_size=1031, emb_dim=512, nheads=8, kvheads=4, nlayers=2, hidden_dim=1024,
-                             max_expected_seq_len=2048, rope_theta=500000.0))
-    folder = write_random_model(str(tmp_path / "m"), arch.config_json(), arch.checkpoint_layout(), seed=6)
+    folder, oracle = _peaked_model(tmp_path, 0.06, vocab=1031, hidden=512, intermediate=1024, layers=2, heads=8, kvheads=4,
+                                   theta=5e5, context=2048)
     g = torch.Generator().manual_seed(71)
     reqs = [torch.randint(0, 1031, (int(k),), generator=g).tolist() for k in torch.randint(700, 1000, (64,), generator=g)]
     steps = 4
-    out = {}
-    for dtype in ("fp32", "bf16"):
-        engine = get_model("hf_pretrained", model_path=folder, device_type="cuda", data_type=dtype).new_engine(64 * 1024)
-        before = ops.attention_stream_launches(64)
-        slots = engine.begin(len(reqs))
-        rows = [engine.step(slots, [r[:-steps] for r in reqs]).float().cpu()]
-        for t in range(steps, 0, -1):
-            rows.append(engine.step(slots, [[r[-t]] for r in reqs]).float().cpu())
-        engine.release(slots)
-        engine.check()
-        out[dtype] = torch.stack(rows, 1).reshape(-1, 1031)
-        # 2 layers: the first decode step launches them plainly, the second captures them; replays launch nothing new
-        assert ops.attention_stream_launches(64) - before == (4 if dtype == "bf16" else 0)
-    close(out["bf16"], out["fp32"], "bf16")
-    assert (out["bf16"].argmax(-1) == out["fp32"].argmax(-1)).float().mean() > 0.9
+    engine = get_model("hf_pretrained", model_path=folder, device_type="cuda", data_type=dtype).new_engine(64 * 1024)
+    before = ops.attention_stream_launches(64)
+    slots = engine.begin(len(reqs))
+    rows = [engine.step(slots, [r[:-steps] for r in reqs])]
+    for t in range(steps, 0, -1):
+        rows.append(engine.step(slots, [[r[-t]] for r in reqs]))
+    engine.release(slots)
+    engine.check()
+    # 2 layers: the first decode step launches them plainly, the second captures them; replays launch nothing new
+    assert ops.attention_stream_launches(64) - before == (4 if dtype == "bf16" else 0)
+    got = torch.stack(rows, 1)
+    for i, r in enumerate(reqs):
+        close(got[i], oracle.logits(r, rows=list(range(len(r) - steps - 1, len(r)))), dtype)
 
 
-def test_window_attention_through_the_engine(tmp_path):
-    """A decoder whose mixers keep a window of 40 keys: the cache gives blocks back as they leave the window, and
-    the logits equal the plain implementation's with the same window, whole and token by token."""
+def windowed_model(folder, dtype, window):
+    """Llama's layers with a window on every mixer: a test's variation, not a model of anyone's."""
     import dataclasses
 
     from fms_b200.models import get_model
     from fms_b200.models.llama import LLaMA
-    from tiny_models import TINY, write_tiny
+    from fms_b200.weights import FileSource
 
-    class WindowedLLaMA(LLaMA):  # Llama's layers with a window on every mixer: a test's variation, not a model
+    class WindowedLLaMA(LLaMA):
         def decoder_spec(self):
             spec = super().decoder_spec()
-            layers = tuple(dataclasses.replace(b, mixer=dataclasses.replace(b.mixer, window=40)) for b in spec.layers)
+            layers = tuple(dataclasses.replace(b, mixer=dataclasses.replace(b.mixer, window=window)) for b in spec.layers)
             return dataclasses.replace(spec, layers=layers)
 
-    folder = write_tiny(str(tmp_path / "c"), "c")
-    plain = pl.PlainLlama(folder)
+    base = get_model("hf_pretrained", model_path=folder, device_type="cuda", data_type=dtype)
+    model = WindowedLLaMA(base.config)
+    model.load(FileSource(folder), "hf", "cuda", base.dtype)
+    return model
+
+
+def plain_windowed_logits(plain, ids, window):
+    x = pl.plain_embedding(torch.as_tensor(ids), plain.w["model.embed_tokens.weight"])
+    for i in range(plain.c["nlayers"]):
+        x = plain.block(i, x, torch.arange(len(ids)), window=window)
+    x = pl.plain_rmsnorm(x, plain.w["model.norm.weight"], plain.c["eps"])
+    return x @ plain.w["lm_head.weight"].T
+
+
+@pytest.mark.parametrize("which", ["c", "d"])
+def test_window_attention_through_the_engine(tiny_folders, oracles, which):
+    """A decoder whose mixers keep a window of 40 keys: the cache gives blocks back as they leave the window, and
+    the logits equal the plain implementation's with the same window, whole and token by token."""
     g = torch.Generator().manual_seed(80)
-    req = torch.randint(0, TINY["c"][0]["vocab_size"], (300,), generator=g).tolist()
-
-    def plain_logits(ids):
-        ids_t = torch.as_tensor(ids)
-        x = pl.plain_embedding(ids_t, plain.w["model.embed_tokens.weight"])
-        for i in range(plain.c["nlayers"]):
-            x = plain.block(i, x, torch.arange(len(ids)), window=40)
-        x = pl.plain_rmsnorm(x, plain.w["model.norm.weight"], plain.c["eps"])
-        return x @ plain.w["lm_head.weight"].T
-
-    want = plain_logits(req)
+    req = torch.randint(0, TINY[which][0]["vocab_size"], (300,), generator=g).tolist()
+    want = plain_windowed_logits(oracles[which], req, 40)
     for dtype in ("fp32", "bf16"):
-        base = get_model("hf_pretrained", model_path=folder, device_type="cuda", data_type=dtype)
-        model = WindowedLLaMA(base.config)
-        from fms_b200.weights import FileSource
-
-        model.load(FileSource(folder), "hf", "cuda", base.dtype)
+        model = windowed_model(tiny_folders[which], dtype, 40)
         engine = model.new_engine(max_tokens=64 * 4, max_slots=1)  # 4 blocks: the sequence of 300 needs 5 without a window
         (slot,) = engine.begin(1)
         parts = [engine.step([slot], [req[:130]], [list(range(130))])]
@@ -515,6 +608,94 @@ def test_window_attention_through_the_engine(tmp_path):
         engine.release([slot])
         engine.check()
         close(torch.cat(parts), want, dtype)
+
+
+@pytest.fixture(scope="module")
+def planted(tmp_path_factory):
+    from tiny_models import TINY_D, planted_tensors, write_folder
+
+    folder = write_folder(str(tmp_path_factory.mktemp("planted")), TINY_D, planted_tensors())
+    return folder, pl.PlainLlama(folder)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_one_key_that_carries_the_whole_attention(planted, dtype):
+    """Five requests in one batch, in each a key that gets all the attention of certain queries: at position 0,
+    on both sides of a cache block's edge (63, 64) and of a decode split's edge (255, 256).  The queries stand right
+    behind the key, further on in the prompt, and among the last 32 tokens, which are fed one by one; the shorter
+    requests end earlier.  A key that is dropped, read from a wrong place or counted twice changes these rows
+    altogether."""
+    from fms_b200.models import get_model
+    from tiny_models import PLANT_KEYS, planted_request
+
+    folder, oracle = planted
+    places = [0, 63, 64, 255, 256]
+    lengths = [300, 345, 322, 310, 333]
+    reqs = [planted_request(n, at, PLANT_KEYS[i], [at + 1, n - 50, n - 20, n - 1], 40 + i)
+            for i, (n, at) in enumerate(zip(lengths, places))]
+    want = [oracle.logits(r) for r in reqs]
+    # the rows that rest on the planted key differ from what they would be without it by far more than any tolerance
+    for r, w, at in zip(reqs, want, places):
+        other = list(r)
+        other[at] = 1
+        assert (oracle.logits(other)[-1] - w[-1]).abs().max() > 0.2 * w[-1].abs().max()
+    engine = get_model("hf_pretrained", model_path=folder, device_type="cuda", data_type=dtype).new_engine(
+        max_tokens=sum((n + 63) // 64 * 64 for n in lengths), max_slots=5)
+    slots = engine.begin(5)
+    cut = [n - 32 for n in lengths]
+    got = [[] for _ in reqs]
+    lg = engine.step(slots, [r[:c] for r, c in zip(reqs, cut)], [list(range(c)) for c in cut])
+    o = 0
+    for i, c in enumerate(cut):
+        got[i].append(lg[o:o + c])
+        o += c
+    for t in range(32):
+        lg = engine.step(slots, [[r[c + t]] for r, c in zip(reqs, cut)])
+        for i in range(5):
+            got[i].append(lg[i:i + 1])
+    engine.release(slots)
+    engine.check()
+    for i in range(5):
+        close(torch.cat(got[i]), want[i], dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_key_at_the_edge_of_the_window(planted, dtype):
+    """With a window of 40 the query at position p sees the keys p-39..p.  A key that carries all the attention is
+    the oldest one in the window of one query token and just outside the window of the next; both stand in the
+    prompt in one request and among the tokens fed one by one in another."""
+    from tiny_models import PLANT_KEYS, planted_request
+
+    folder, oracle = planted
+    window = 40
+    # (length, key at, queries at): the key leaves the window between the two queries
+    cases = [(200, 100, [139, 140]), (200, 150, [189, 190]), (130, 63, [102, 103]), (150, 64, [103, 104])]
+    reqs = [planted_request(n, at, PLANT_KEYS[i], q, 60 + i) for i, (n, at, q) in enumerate(cases)]
+    want = [plain_windowed_logits(oracle, r, window) for r in reqs]
+    for w, (_, _, q) in zip(want, cases):  # seeing the key or not makes all the difference
+        assert (w[q[0]] - w[q[1]]).abs().max() > 0.2 * w[q[0]].abs().max()
+    engine = windowed_model(folder, dtype, window).new_engine(max_tokens=64 * 16, max_slots=4)
+    slots = engine.begin(4)
+    cut = [160, 160, 90, 90]  # the queries of the first request lie in the prompt, the others' among the single tokens
+    got = [[] for _ in reqs]
+    lg = engine.step(slots, [r[:c] for r, c in zip(reqs, cut)], [list(range(c)) for c in cut])
+    o = 0
+    for i, c in enumerate(cut):
+        got[i].append(lg[o:o + c])
+        o += c
+    at = list(cut)
+    live = [0, 1, 2, 3]
+    while live:
+        lg = engine.step([slots[i] for i in live], [[reqs[i][at[i]]] for i in live])
+        for j, i in enumerate(live):
+            got[i].append(lg[j:j + 1])
+            at[i] += 1
+        for i in [i for i in live if at[i] == len(reqs[i])]:
+            engine.release([slots[i]])
+            live.remove(i)
+    engine.check()
+    for i in range(4):
+        close(torch.cat(got[i]), want[i], dtype)
 
 
 def test_command_line(tiny_folders):

@@ -71,7 +71,9 @@ def test_rotary_part_frequencies():
         part.finalize(torch.device("cuda"), torch.float32)
         torch.testing.assert_close(part.rotary_frequencies().cpu(), pl.plain_rope_inv_freq(64, theta, scaling), rtol=1e-6,
                                    atol=0)
-    assert build_position(PositionSpec("none")).rotary_frequencies() is None
+    from fms_b200.parts import PositionEncoding
+
+    assert type(build_position(PositionSpec("none"))) is PositionEncoding  # the base: encodes nothing
     with pytest.raises(ValueError):
         build_position(PositionSpec("rope", head_dim=64, scaling=(("rope_type", "yarn"),)))
 
@@ -116,17 +118,35 @@ def test_attention_part_alone(dtype, nheads, kvheads, hd, window):
         close(torch.cat(outs), want, dtype)
 
 
-def test_toy_position_encoding_is_registered_and_used_by_the_mixer():
-    """Another position encoding, defined here: rotation of pairs with frequencies that fall linearly instead of
-    geometrically.  It is registered under a name of its own and chosen by the mixer's spec; the attention part and
-    its kernels take it without a change."""
+def _run_mixer_in_three_steps(mixer, x, dtype, first_position=0):
     from fms_b200.cache import Cache
-    from fms_b200.config import MixerSpec, PositionSpec
-    from fms_b200.parts import Part, build_mixer, register_position, registered
+    from fms_b200.engine.batch import Batch
 
-    class LinearFrequencies(Part):
+    cache = Cache([mixer.cache_request()], max_tokens=256, max_positions=512, dtype=dtype, device="cuda")
+    (slot,) = cache.begin(1, [first_position])
+    outs, at = [], 0
+    for k_new in (60, 1, x.shape[0] - 61):
+        cache.prepare([slot], [k_new])
+        batch = Batch.from_lists([slot], [at], [[0] * k_new], [[]], "cuda", [cache.offset(slot)])
+        outs.append(mixer.forward(x[at:at + k_new].to(dtype).cuda().contiguous(), batch, cache.layer_view(0), True))
+        cache.commit([slot], [k_new])
+        at += k_new
+    return torch.cat(outs)
+
+
+def wave(positions, head_dim):
+    """[n, head_dim] float64: what the toy encoding ``toy_added_wave`` adds to every q and k head at a position."""
+    d = torch.arange(head_dim, dtype=torch.float64, device=positions.device)
+    return 0.3 * torch.sin(positions.double()[:, None] * 0.05 * (d[None, :] + 1.0))
+
+
+def register_toy_encodings():
+    from fms_b200.kernels import ops
+    from fms_b200.parts import PositionEncoding, register_position, registered
+
+    class LinearFrequencies(PositionEncoding):
         def __init__(self, spec):
-            super().__init__()
+            super().__init__(spec)
             self.half, self.top = spec.head_dim // 2, spec.theta
             self._f = None
 
@@ -136,36 +156,90 @@ def test_toy_position_encoding_is_registered_and_used_by_the_mixer():
         def finalize(self, device, dtype):
             self._f = self.frequencies().to(device).contiguous()
 
-        def rotary_frequencies(self):
-            return self._f
+        def project(self, x, linear, batch, cache_view, nheads, kvheads, head_dim, writes_cache=True):
+            return ops.qkv_rope_store(x, linear.tensor("weight"), linear.tensor("bias"), self._f, batch, cache_view, nheads,
+                                      kvheads, head_dim, writes_cache)
+
+    class AddedWave(PositionEncoding):
+        def project(self, x, linear, batch, cache_view, nheads, kvheads, head_dim, writes_cache=True):
+            qkv = ops.linear(x, linear.tensor("weight"), linear.tensor("bias"))
+            pos = batch.positions if batch.position_ids is None else batch.position_ids
+            rows = qkv.float().view(qkv.shape[0], nheads + 2 * kvheads, head_dim)  # no host synchronisation: capturable
+            rows[:, : nheads + kvheads] += wave(pos, head_dim).float()[:, None, :]
+            qkv = rows.view(qkv.shape).to(qkv.dtype)
+            return ops.rope_store(qkv, None, batch, cache_view, nheads, kvheads, head_dim, writes_cache)  # stores as it is
 
     if "toy_linear_frequencies" not in registered("position"):
         register_position("toy_linear_frequencies", LinearFrequencies)
+        register_position("toy_added_wave", AddedWave)
+
+
+def test_toy_position_encodings_are_registered_and_used_by_the_mixer():
+    """Two other position encodings, defined here, registered under names of their own and chosen by the mixer's
+    spec; the attention part and its kernels take them without a change.  The first rotates pairs with frequencies
+    that fall linearly instead of geometrically (it keeps the rotary kernels).  The second is no rotation at all: it
+    adds a vector that depends on the position to every head of q and k (written with torch operations: a test's
+    toy), and leaves the write into the cache to the library's kernel.  Its result depends on the positions
+    themselves, not on their differences: the case that starts at position 17 shows that the encoding sees 17 + i."""
+    from fms_b200.config import MixerSpec, PositionSpec
+    from fms_b200.parts import build_mixer
+
+    register_toy_encodings()
     nheads, kvheads, hd, n, dtype = 4, 2, 32, 90, torch.float32
-    spec = MixerSpec("attention", dim=nheads * hd, nheads=nheads, kvheads=kvheads, head_dim=hd,
-                     position=PositionSpec("toy_linear_frequencies", head_dim=hd, theta=0.3))
-    mixer = build_mixer(spec)
-    assert type(mixer.position).__name__ == "LinearFrequencies"
-    w = fill(mixer, dtype, 12, scale=0.08)
     x = torch.randn(n, nheads * hd, generator=torch.Generator().manual_seed(13))
-    inv = mixer.position.frequencies().double()
-    qkv = x.double() @ w["in_proj.qkv_fused.weight"].T
-    q, k, v = qkv.split([nheads * hd, kvheads * hd, kvheads * hd], -1)
-    pos = torch.arange(n)
-    a = pl.plain_attention(pl.plain_rope(q.view(n, nheads, hd), pos, inv), pl.plain_rope(k.view(n, kvheads, hd), pos, inv),
-                           v.view(n, kvheads, hd)).reshape(n, -1)
-    want = a @ w["dense.weight"].T
-    cache = Cache([mixer.cache_request()], max_tokens=256, max_positions=256, dtype=dtype, device="cuda")
-    (slot,) = cache.begin(1)
-    outs, at = [], 0
-    for k_new in (60, 1, 29):
-        batch = one_sequence_batch(k_new, at, cache, slot)
-        outs.append(mixer.forward(x[at:at + k_new].cuda().contiguous(), batch, cache.layer_view(0), True))
-        cache.commit([slot], [k_new])
-        at += k_new
-    close(torch.cat(outs), want, dtype)
-    # the toy's frequencies are not the ordinary ones, so the agreement above is not an accident
-    assert not torch.allclose(inv.float(), pl.plain_rope_inv_freq(hd, 10000.0).float())
+    for kind, first in (("toy_linear_frequencies", 0), ("toy_added_wave", 0), ("toy_added_wave", 17)):
+        spec = MixerSpec("attention", dim=nheads * hd, nheads=nheads, kvheads=kvheads, head_dim=hd,
+                         position=PositionSpec(kind, head_dim=hd, theta=0.3))
+        mixer = build_mixer(spec)
+        assert type(mixer.position).__name__ == {"toy_linear_frequencies": "LinearFrequencies", "toy_added_wave": "AddedWave"}[kind]
+        w = fill(mixer, dtype, 12, scale=0.08)
+        qkv = x.double() @ w["in_proj.qkv_fused.weight"].T
+        q, k, v = qkv.split([nheads * hd, kvheads * hd, kvheads * hd], -1)
+        pos = torch.arange(n) + first
+        if kind == "toy_linear_frequencies":
+            inv = mixer.position.frequencies().double()
+            q, k = pl.plain_rope(q.view(n, nheads, hd), pos, inv), pl.plain_rope(k.view(n, kvheads, hd), pos, inv)
+            # the toy's frequencies are not the ordinary ones, so the agreement below is not an accident
+            assert not torch.allclose(inv.float(), pl.plain_rope_inv_freq(hd, 10000.0).float())
+        else:
+            q, k = q.view(n, nheads, hd) + wave(pos, hd)[:, None], k.view(n, kvheads, hd) + wave(pos, hd)[:, None]
+        want = pl.plain_attention(q, k, v.view(n, kvheads, hd)).reshape(n, -1) @ w["dense.weight"].T
+        close(_run_mixer_in_three_steps(mixer, x, dtype, first), want, dtype)
+        if first:  # and from position 0 the rows would have been others
+            q0, k0 = q - wave(pos, hd)[:, None] + wave(pos - first, hd)[:, None], k - wave(pos, hd)[:, None] + wave(pos - first, hd)[:, None]
+            other = pl.plain_attention(q0, k0, v.view(n, kvheads, hd)).reshape(n, -1) @ w["dense.weight"].T
+            assert (other - want).abs().max() > 100 * 2e-5
+
+
+def test_an_encoding_that_adds_to_the_scores_is_refused_by_the_built_in_mixer():
+    from fms_b200.config import MixerSpec, PositionSpec
+    from fms_b200.parts import PositionEncoding, build_mixer, register_position, registered
+
+    class Slopes(PositionEncoding):
+        def score_bias(self):
+            return torch.ones(4)
+
+    if "toy_slopes" not in registered("position"):
+        register_position("toy_slopes", Slopes)
+    with pytest.raises(ValueError, match="adds to the attention scores"):
+        build_mixer(MixerSpec("attention", dim=64, nheads=4, kvheads=2, head_dim=16, position=PositionSpec("toy_slopes")))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rotary_attention_of_a_sequence_that_starts_at_another_position(dtype):
+    """The rotation sees position 300 + i while the cache holds the tokens from its place 0 on.  (Rotary scores
+    depend on differences of positions only, so this shows no more than that q and k are turned by the same
+    positions and stored at the right places; the toy encoding above shows the positions themselves.)"""
+    from fms_b200.config import MixerSpec, PositionSpec
+    from fms_b200.parts import build_mixer
+
+    nheads, kvheads, hd, n, theta = 4, 2, 32, 90, 10000.0
+    mixer = build_mixer(MixerSpec("attention", dim=nheads * hd, nheads=nheads, kvheads=kvheads, head_dim=hd,
+                                  position=PositionSpec("rope", head_dim=hd, theta=theta)))
+    w = fill(mixer, dtype, 21, scale=0.2)
+    x = torch.randn(n, nheads * hd, generator=torch.Generator().manual_seed(22)).to(dtype)
+    want = plain_mixer(w, x.double(), nheads, kvheads, hd, theta, 0, torch.arange(n) + 300)
+    close(_run_mixer_in_three_steps(mixer, x, dtype, 300), want, dtype)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -356,3 +430,116 @@ def test_toy_mixer_with_state_and_routed_feed_forward_are_registered_built_and_s
     for i in range(3):
         close(torch.cat(got[i]), want[i], torch.float32)
     assert engine.graph_launches > 0
+
+
+# ---------------------------------------------------------------------------------------------------
+# another arrangement of a layer, scales at both ends of the decoder, sequences that start at other positions
+# ---------------------------------------------------------------------------------------------------
+def register_toy_arrangement():
+    from fms_b200.parts import Part, build_feed_forward, build_mixer, build_norm, register_block, registered
+
+    class ParallelBlock(Part):
+        """x += r * (mixer(norm(x)) + feed_forward(norm(x))): one norm, both sublayers beside one another, and a
+        multiplier r on what they add (``BlockSpec.options``)."""
+
+        def __init__(self, spec):
+            super().__init__()
+            self.norm = self.add("norm", build_norm(spec.mixer_norm))
+            self.mixer = self.add("mixer", build_mixer(spec.mixer))
+            self.feed_forward = self.add("ff", build_feed_forward(spec.feed_forward))
+            self.multiplier = dict(spec.options)["residual_multiplier"]
+
+        def cache_request(self):
+            return self.mixer.cache_request()
+
+        def forward(self, residual, pending, batch, cache_view, writes_cache, dtype):
+            h = self.norm.apply(residual, pending, dtype)
+            both = self.mixer.forward(h, batch, cache_view, writes_cache).float() + self.feed_forward.forward(h).float()
+            return (both * self.multiplier).to(dtype)
+
+    if "toy_parallel" not in registered("block"):
+        register_block("toy_parallel", ParallelBlock)
+
+
+def parallel_toy_model(dtype, seed=9):
+    from fms_b200.config import BlockSpec, DecoderSpec, FeedForwardSpec, LayerCall, MixerSpec, NormSpec, PositionSpec
+    from fms_b200.engine.decoder import Decoder
+    from fms_b200.models.base import Model
+    from fms_b200.weights import RandomSource, TensorLayout
+
+    register_toy_encodings()
+    register_toy_arrangement()
+    dim, vocab = 64, 89
+    norm = NormSpec("rmsnorm", dim, 1e-5)
+    block = BlockSpec(MixerSpec("attention", dim=dim, nheads=4, kvheads=2, head_dim=16,
+                                position=PositionSpec("toy_added_wave", head_dim=16)),
+                      FeedForwardSpec("glu", dim=dim, hidden=80), norm, norm, arrangement="toy_parallel",
+                      options=(("residual_multiplier", 0.7),))
+    spec = DecoderSpec(vocab_size=vocab, dim=dim, layers=(block, block), schedule=(LayerCall(0), LayerCall(1)),
+                       final_norm=norm, tie_head=False, max_positions=512, embedding_scale=3.0, logit_scale=0.25)
+
+    class ParallelToy(Model):
+        architecture = "toy_parallel_architecture_of_a_test"
+        default_source = "native"
+
+        def decoder_spec(self):
+            return spec
+
+    layout = [TensorLayout(n, d.shape, "gain" if d.role == "vector" else "matrix")
+              for n, _, _, d in Decoder(spec, dtype).named_decls()]
+    model = ParallelToy(config=None)
+    model.load(RandomSource(layout, seed, dtype=torch.bfloat16, device="cpu", std=0.1), "native", "cuda", dtype)
+    return model
+
+
+def plain_parallel_toy(model, ids, first_position):
+    w = {k: v.double().cpu() for k, v in model.state_dict().items()}
+    n = len(ids)
+    pos = torch.arange(n) + first_position
+    x = 3.0 * w["base_model.embedding.weight"][torch.tensor(ids)]
+    for layer in (0, 1):
+        p = f"base_model.layers.{layer}."
+        h = pl.plain_rmsnorm(x, w[p + "norm.weight"], 1e-5)
+        q, k, v = (h @ w[p + "mixer.in_proj.qkv_fused.weight"].T).split([64, 32, 32], -1)
+        q, k = q.view(n, 4, 16) + wave(pos, 16)[:, None], k.view(n, 2, 16) + wave(pos, 16)[:, None]
+        a = pl.plain_attention(q, k, v.view(n, 2, 16)).reshape(n, -1) @ w[p + "mixer.dense.weight"].T
+        gu = w[p + "ff.wg1_fused.weight"]
+        x = x + 0.7 * (a + pl.plain_swiglu_ffn(h, gu[:80], gu[80:], w[p + "ff.w2.weight"]))
+    x = pl.plain_rmsnorm(x, w["base_model.dec_norm.weight"], 1e-5)
+    return 0.25 * (x @ w["head.weight"].T)
+
+
+def test_another_arrangement_scales_and_sequences_that_start_at_other_positions():
+    """A decoder defined here: both layers in a parallel arrangement registered by this test (one norm, mixer and
+    feed-forward beside one another, a residual multiplier), a position encoding that shows absolute positions, a
+    scale on the embedding and one on the logits.  Three sequences start at positions 0, 5 and 130; prompts in one
+    step, then one token each (the decode arrays and the captured graph carry the positions too)."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    model = parallel_toy_model(torch.float32)
+    engine = model.new_engine(max_tokens=512, max_slots=3)
+    g = torch.Generator().manual_seed(8)
+    reqs = [torch.randint(0, 89, (k,), generator=g).tolist() for k in (40, 9, 70)]
+    firsts = [0, 5, 130]
+    want = [plain_parallel_toy(model, r, f) for r, f in zip(reqs, firsts)]
+    assert (plain_parallel_toy(model, reqs[2], 0) - want[2]).abs().max() > 1e-2  # the start does matter
+    cut = [len(r) - 6 for r in reqs]
+    slots = engine.begin(3, first_positions=firsts)
+    got = [[] for _ in reqs]
+    lg = engine.step(slots, [r[:c] for r, c in zip(reqs, cut)], [list(range(c)) for c in cut])
+    o = 0
+    for i, c in enumerate(cut):
+        got[i].append(lg[o:o + c])
+        o += c
+    for t in range(6):
+        lg = engine.step(slots, [[r[c + t]] for r, c in zip(reqs, cut)])
+        for i in range(3):
+            got[i].append(lg[i:i + 1])
+    engine.release(slots)
+    engine.check()
+    assert engine.graph_launches > 0
+    for i in range(3):
+        close(torch.cat(got[i]), want[i], torch.float32)
+    # the same slots again, from position 0: nothing of the offsets is left
+    slots = engine.begin(1)
+    close(engine.step(slots, [reqs[2]], [list(range(70))]), plain_parallel_toy(model, reqs[2], 0), torch.float32)
+    engine.release(slots)

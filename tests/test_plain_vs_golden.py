@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import plain_llama as pl
-from tiny_models import TINY, tiny_prompts, tiny_tensors
+from tiny_models import TINY, tiny_prompts, tiny_tensors_of
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_logits.safetensors")
 
@@ -41,15 +41,14 @@ def test_pad_input_ids_returns_what_the_reference_returns():
         assert torch.isinf(extra["mask"][~zero]).all() and (extra["mask"][~zero] < 0).all()
 
 
-@pytest.mark.parametrize("which", ["a", "b", "c"])
+@pytest.mark.parametrize("which", sorted(TINY))
 def test_weights_are_the_ones_the_golden_was_made_with(golden, which):
-    cfg, seed, gain_dtype = TINY[which]
-    tensors = tiny_tensors(cfg, seed, gain_dtype)
+    tensors = tiny_tensors_of(which)
     total = torch.stack([t.float().abs().sum() for _, t in sorted(tensors.items())]).sum().double()
     assert abs(total.item() - golden[f"{which}.weight_abs_sum"].item()) < 1e-6 * total.item()
 
 
-@pytest.mark.parametrize("which", ["a", "b", "c"])
+@pytest.mark.parametrize("which", sorted(TINY))
 def test_plain_logits_equal_reference(golden, tiny_folders, which):
     model = pl.PlainLlama(tiny_folders[which], dtype=torch.float64)
     for n, prompt in enumerate(tiny_prompts(which)):
