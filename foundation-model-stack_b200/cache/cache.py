@@ -87,17 +87,24 @@ class KVGroup:
         missing = [i for i in range(first_needed, last_needed + 1) if row[i] < 0]
         return stale, missing
 
-    def apply(self, slot: int, stale, missing) -> None:
-        row = self.table_host[slot]
+    def give_back(self, slot: int, stale) -> None:
         if stale:
+            row = self.table_host[slot]
             self.pool.free([int(row[i]) for i in stale])
             for i in stale:
                 row[i] = -1
+            self._dirty.add(slot)
+
+    def take(self, slot: int, missing) -> None:
         if missing:
+            row = self.table_host[slot]
             for i, b in zip(missing, self.pool.alloc(len(missing))):
                 row[i] = b
-        if stale or missing:
             self._dirty.add(slot)
+
+    def apply(self, slot: int, stale, missing) -> None:
+        self.give_back(slot, stale)
+        self.take(slot, missing)
 
     def release(self, slot: int) -> None:
         held = self.held_blocks(slot)
@@ -243,8 +250,11 @@ class Cache:
                     raise CacheFull(f"{want} blocks wanted, {g.pool.n_free} of {g.pool.n_blocks} free")
                 plans.append((g, plan))
         for g, plan in plans:
-            for s, (stale, missing) in zip(slots, plan):
-                g.apply(s, stale, missing)
+            # all that has left a window first, then what is needed: the check above counted on both
+            for s, (stale, _) in zip(slots, plan):
+                g.give_back(s, stale)
+            for s, (_, missing) in zip(slots, plan):
+                g.take(s, missing)
             g.sync()
         return before
 

@@ -325,7 +325,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, float* __r
 
 template <typename T>
 __global__ void attn_combine_kernel(AttnArgs a, const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    int n_splits, int* __restrict__ reset = nullptr) {
+                                    int n_splits, int* __restrict__ reset = nullptr, int* __restrict__ error_flag = nullptr) {
   pdl_launch_dependents();
   pdl_wait();
   // the kernel before this one is done: its work counter (if it has one) is put back for the next launch
@@ -334,7 +334,14 @@ __global__ void attn_combine_kernel(AttnArgs a, const float* __restrict__ part_o
   const int len = a.len_after[seq];
   const int pos = len - 1;
   const int kstart = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-  const int s_lo = kstart / SPLIT, s_hi = pos / SPLIT;
+  int s_lo = kstart / SPLIT, s_hi = pos / SPLIT;
+  if (s_hi >= n_splits) {
+    // a sequence longer than the launch's splits cover (the caller's n_splits is too small): nothing beyond the
+    // scratch is read, the keys past the last split are left out, and the flag says so where there is one
+    if (error_flag != nullptr && threadIdx.x == 0) atomicExch(error_flag, 8);
+    s_hi = n_splits - 1;
+    s_lo = min(s_lo, s_hi);
+  }
   const float* ml = part_ml + ((size_t)seq * a.nheads + head) * n_splits * 2;
   const float* po = part_o + ((size_t)seq * a.nheads + head) * n_splits * HD;
   float m = -INFINITY;
@@ -415,7 +422,7 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
     fms_launch(attn_decode_kernel<float>, dim3(n_seqs, a.kvheads * chunks, n_splits), dim3(128), 0, stream, a, part_o,
                part_ml, n_splits);
     fms_launch(attn_combine_kernel<float>, dim3(n_seqs, a.nheads), dim3(HD >= 128 ? 128 : 64), 0, stream, a,
-               (const float*)part_o, (const float*)part_ml, n_splits, (int*)nullptr);
+               (const float*)part_o, (const float*)part_ml, n_splits, (int*)nullptr, error_flag);
   } else if (dtype == FMS_BF16) {
     // Few (sequence, kv head) pairs: four warps share a split, each with one block of 64 keys in flight, which
     // is quickest when the GPU is not full.  Many: one warp per block with a small footprint, so that several
@@ -444,7 +451,7 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
       fms_launch(attn_decode_stream_kernel, dim3(blocks), dim3((SR_WARPS + 1) * 32), SR_SMEM, stream, map_k, map_v, a,
                  part_o, part_ml, n_seqs, n_splits, work_counter, error_flag);
       fms_launch(attn_combine_kernel<__nv_bfloat16>, dim3(n_seqs, a.nheads), dim3(HD >= 128 ? 128 : 64), 0, stream, a,
-                 (const float*)part_o, (const float*)part_ml, n_splits, work_counter);
+                 (const float*)part_o, (const float*)part_ml, n_splits, work_counter, error_flag);
       return fms_launch_status(what);
     }
 #endif
@@ -463,7 +470,7 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
                n_splits, nw == 4 ? pool_blocks : 0);
     if (n_splits > 1)  // with one split the kernel above has written the result itself
       fms_launch(attn_combine_kernel<__nv_bfloat16>, dim3(n_seqs, a.nheads), dim3(HD >= 128 ? 128 : 64), 0, stream, a,
-                 (const float*)part_o, (const float*)part_ml, n_splits, (int*)nullptr);
+                 (const float*)part_o, (const float*)part_ml, n_splits, (int*)nullptr, error_flag);
   } else {
     return fms_fail("%s: unsupported dtype code %d", what, dtype);
   }
@@ -547,6 +554,8 @@ FMS_API int fms_attention_prefill(const void* q, void* out, int dtype, const voi
 // off).  total_len: cached tokens of all sequences together as far as the host knows (0: unknown), by which the
 // kernel is chosen.  work_counter: one int that is 0 between launches, from which the streaming kernel's warps draw their
 // units; error_flag: where a kernel records that a wait ran out (either null: the streaming kernel is not used).
+// n_splits * 256 must cover every len_after (they live on the device, so the host cannot check it): a longer sequence
+// loses its keys beyond that, sets error flag 8 where there is a flag, and reads nothing outside the scratch.
 FMS_API int fms_attention_decode(const void* q, void* out, int dtype, const void* keys, const void* values,
                                  const int* table, int table_stride, int block_tokens, const int* slots,
                                  const int* first_row, const int* len_after, int n_seqs, int n_splits, float* part_o,

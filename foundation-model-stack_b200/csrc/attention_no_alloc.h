@@ -18,10 +18,17 @@
 //     n_seqs * nheads * n_splits * (head_dim + 2) * 4 bytes
 // (e.g. 8 sequences x 32 heads x 8 splits of 256 keys x 130 floats = 1.0 MiB); a larger call is refused
 // with an error and nothing is launched.  Every GPU on which the library's kernels get loaded holds the
-// 8 MiB until the process exits, whether or not this entry point is ever called.
+// 8 MiB until the process exits, whether or not this entry point is ever called.  The attention source is built
+// once per head size (libfms_attention_hd64, _hd128, ...), and each of these libraries carries an array of its
+// own: a process that loads three of them holds 24 MiB per GPU.
+//
+// Precondition.  n_splits * 256 must be at least every sequence's length after the step (len_after lives on the
+// device, so this function cannot check it).  This entry point has no error word on the device: a longer sequence
+// silently loses its keys beyond n_splits * 256.  Nothing outside the array is read or written in that case.
 //
 // Set-up.  The array's name is a host-side handle, not a device address.  The first call on each device
-// (with that device current) asks the runtime for the address with cudaGetSymbolAddress, checks the
+// (with that device current: the address is taken for the current device, not for the device of `stream`, so
+// make the stream's device current before every call) asks the runtime for the address with cudaGetSymbolAddress, checks the
 // result and remembers it per device; later calls on that device reuse it.  Make that first call before
 // any stream capture begins.  The function calls no cudaMalloc, cudaFree or other allocating routine.
 //

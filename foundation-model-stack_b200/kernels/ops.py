@@ -131,7 +131,9 @@ def check_error_flag(device) -> None:
         flag.zero_()
         raise KernelError({1: "a token id outside the vocabulary reached the embedding",
                            2: "a token's position has no cache block",
-                           4: "a kernel gave up waiting for a copy or for the tensor cores"}.get(v, f"device error flag {v}"))
+                           4: "a kernel gave up waiting for a copy or for the tensor cores",
+                           8: "decode attention was launched with fewer key splits than a sequence's length needs",
+                           16: "a kernel's bounds check met an index outside its array"}.get(v, f"device error flag {v}"))
 
 
 # ---- embedding ---------------------------------------------------------------------------------------

@@ -56,8 +56,6 @@ _DTYPES = {
 
 
 def _dtype(data_type) -> torch.dtype:
-    if data_type is None:
-        return torch.bfloat16
     if data_type not in _DTYPES:
         raise ValueError(f"data_type {data_type!r} is not supported: bf16 and fp32 are")
     return _DTYPES[data_type]
@@ -74,14 +72,19 @@ def read_config_json(model_path: str) -> dict:
 def get_model(architecture: str, variant: Optional[str] = None, model_path: Optional[str] = None,
               source: Optional[str] = None, device_type: str = "cuda", data_type: Union[str, torch.dtype, None] = None,
               distributed_strategy: Optional[str] = None, checkpoint_sharding: Optional[str] = None, group=None,
-              seed: int = 0, **kwargs) -> Model:
+              seed: int = 0, init: str = "baseline", **kwargs) -> Model:
     """Builds a model and fills its weights.
 
     architecture: a registered name, or "hf_pretrained" to take it from ``model_path``'s config.json.
     variant: a registered configuration; None with a ``model_path`` folder means its config.json.
     model_path: folder (or file, or glob) of safetensors; None means random weights from ``seed``.
     source: the checkpoint's naming ("hf" by default; "fms" for the engine's own names).
-    data_type: "bf16" (default) or "fp32": the compute dtype; float32 uses no reduced-precision product.
+    data_type: "bf16" or "fp32": the compute dtype; float32 uses no reduced-precision product.  None: the dtype
+        in which the checkpoint stores its matrices (fms/utils/serialization.py:679-687), which must be one of
+        the two, else an error asks for ``data_type``; bfloat16 for random weights.
+    init: how random weights are drawn: "baseline" (matrices and embedding ~ N(0, 0.02), gains 1 + U(-0.1, 0.1)) or
+        "fms" (the reference's ``reset_parameters``: fms/models/llama.py:231-235, :387-393;
+        fms/modules/attention.py:689-692; fms/modules/feedforward.py:269-283; gains 1).
     distributed_strategy, checkpoint_sharding, group: the reference's parameters for several devices
         (fms/models/__init__.py:298-308); this library runs on one GPU and refuses anything but None.
     kwargs: overrides of configuration fields, as in the reference.
@@ -115,14 +118,17 @@ def get_model(architecture: str, variant: Optional[str] = None, model_path: Opti
                            f'`models.list_variants("{architecture}")` for available variants.')
         model = _models[architecture][variant](**kwargs)
 
-    dtype = _dtype(data_type)
+    from ..weights.loader import checkpoint_dtype
+
     device = torch.device(device_type)
     if model_path is not None:
         src = FileSource(model_path)
+        dtype = checkpoint_dtype(src) if data_type is None else _dtype(data_type)
     else:
         # random weights straight on the device, through the same adapter and checks as a file
-        src = RandomSource(model.checkpoint_layout(), seed, dtype=torch.bfloat16, device=device)
+        src = RandomSource(model.checkpoint_layout(), seed, dtype=torch.bfloat16, device=device, init=init)
         source = model.default_source
+        dtype = torch.bfloat16 if data_type is None else _dtype(data_type)
     return model.load(src, source, device, dtype)
 
 

@@ -165,7 +165,7 @@ class LLaMA(Model):
         """The tensors of an HF Llama checkpoint of this configuration."""
         c = self.config
         d, hd, h, kv, f = c.emb_dim, c.head_dim, c.nheads, c.n_kvheads, c.ffn_hidden
-        out = [TensorLayout("model.embed_tokens.weight", (c.src_vocab_size, d), "matrix")]
+        out = [TensorLayout("model.embed_tokens.weight", (c.src_vocab_size, d), "embedding")]
         for i in range(c.nlayers):
             p = f"model.layers.{i}."
             out += [
@@ -187,7 +187,7 @@ class LLaMA(Model):
                         for n, r in (("gate", f), ("up", f), ("down", d))]
         out.append(TensorLayout("model.norm.weight", (d,), "gain"))
         if not c.tie_heads:
-            out.append(TensorLayout("lm_head.weight", (c.src_vocab_size, d), "matrix"))
+            out.append(TensorLayout("lm_head.weight", (c.src_vocab_size, d), "head"))
         return out
 
 
@@ -288,7 +288,8 @@ def _fuse(tensors: Dict[str, torch.Tensor], parts: List[str], fused: str, **_) -
         names = [name[: m.start()] + p + "." + m.group(1) for p in parts]
         if all(n in out for n in names):
             pieces = [out.pop(n) for n in names]
-            out[name[: m.start()] + fused + "." + m.group(1)] = torch.cat(pieces, dim=0)
+            widest = max((p.dtype for p in pieces), key=lambda dt: torch.finfo(dt).bits if dt.is_floating_point else 0)
+            out[name[: m.start()] + fused + "." + m.group(1)] = torch.cat([p.to(widest) for p in pieces], dim=0)
     return out
 
 

@@ -36,6 +36,17 @@ def register_adapter(architecture: str, source: str, step_names: List[str]) -> N
     sources[source] = list(step_names)
 
 
+def extend_adapter(architecture: str, source: str, adapter_steps: List[str]) -> None:
+    """Appends registered steps to the adapter of a source that exists already
+    (fms/utils/serialization.py:104-148).  The other sources of the architecture stay as they are."""
+    if source not in _adapters.get(architecture, {}):
+        raise KeyError(f"Source {source} must already be registered for architecture {architecture}")
+    for s in adapter_steps:
+        if s not in _steps.get(architecture, {}):
+            raise KeyError(f"adapter step {s} is not registered for architecture {architecture}")
+    _adapters[architecture][source] = _adapters[architecture][source] + list(adapter_steps)
+
+
 def list_sources(architecture: str) -> List[str]:
     return list(_adapters.get(architecture, {}))
 

@@ -7,6 +7,7 @@ checks as one read from disk.
 from __future__ import annotations
 
 import hashlib
+import math
 from typing import Dict, List, Sequence, Tuple
 
 import torch
@@ -40,7 +41,9 @@ class TensorLayout:
     def __init__(self, name: str, shape: Sequence[int], init: str) -> None:
         self.name = name
         self.shape = tuple(shape)
-        self.init = init  # "matrix": N(0, std)   "gain": 1 + U(-0.1, 0.1)   "zeros"
+        # "matrix", "embedding", "head": N(0, std)   "gain": 1 + U(-0.1, 0.1)   "zeros"; the reference's own
+        # initialisation (RandomSource(init="fms")) tells the three kinds of matrices apart
+        self.init = init
 
 
 class RandomSource:
@@ -49,7 +52,14 @@ class RandomSource:
     which tensors are asked for.  The same seed gives the same values on the same kind of device."""
 
     def __init__(self, layout: Sequence[TensorLayout], seed: int, dtype: torch.dtype = torch.bfloat16,
-                 device="cpu", std: float = 0.02, gain_dtype: torch.dtype = None) -> None:
+                 device="cpu", std: float = 0.02, gain_dtype: torch.dtype = None, init: str = "baseline") -> None:
+        """``init="fms"``: as the reference initialises a fresh model — linear layers trunc_normal(0, 0.02) cut at
+        +-2 (fms/modules/attention.py:689-692, fms/modules/feedforward.py:269-283), the embedding
+        trunc_normal(std = width^-0.5) (fms/models/llama.py:231-235), the head N(0, (width * vocabulary)^-0.25)
+        (fms/models/llama.py:387-393), gains 1 (fms/modules/layernorm.py:50-54)."""
+        if init not in ("baseline", "fms"):
+            raise ValueError(f'init {init!r}: "baseline" or "fms"')
+        self.init = init
         self.layout = {t.name: t for t in layout}
         self.seed = int(seed)
         self.dtype = dtype
@@ -69,10 +79,19 @@ class RandomSource:
         digest = hashlib.sha256(f"{self.seed}:{name}".encode()).digest()
         g = torch.Generator(device=self.device)
         g.manual_seed(int.from_bytes(digest[:8], "little") & 0x7FFFFFFFFFFFFFFF)
-        if t.init == "matrix":
-            x = torch.empty(t.shape, dtype=torch.float32, device=self.device).normal_(0.0, self.std, generator=g)
+        if t.init in ("matrix", "embedding", "head"):
+            x = torch.empty(t.shape, dtype=torch.float32, device=self.device)
+            if self.init == "fms" and t.init == "head":
+                x.normal_(0.0, 1.0 / math.sqrt(math.sqrt(t.shape[0] * t.shape[1])), generator=g)
+            elif self.init == "fms":
+                std = t.shape[1] ** -0.5 if t.init == "embedding" else 0.02
+                torch.nn.init.trunc_normal_(x, mean=0.0, std=std, a=-2.0, b=2.0, generator=g)
+            else:
+                x.normal_(0.0, self.std, generator=g)
             return x.to(self.dtype)
         if t.init == "gain":
+            if self.init == "fms":
+                return torch.ones(t.shape, dtype=self.gain_dtype, device=self.device)
             x = torch.empty(t.shape, dtype=torch.float32, device=self.device).uniform_(-0.1, 0.1, generator=g)
             return (1.0 + x).to(self.gain_dtype)
         if t.init == "zeros":

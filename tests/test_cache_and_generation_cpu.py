@@ -387,3 +387,47 @@ def test_bench_counts_the_bytes_and_flops_of_its_shapes():
         assert abs(bench.prefill_flops(layers, 2048) / 1e12 - tflop) < 0.01
         assert (bench.PROMPT_MIN, bench.PROMPT_MAX) == bench.MODEL["prompts"]
     bench.choose_model("llama-3-8b")
+
+
+def test_a_window_group_with_a_full_pool_takes_a_step_that_frees_as_much_as_it_needs():
+    """Two sequences in a pool without a free block: the step needs a new block for each, and gives one back for each
+    (it has left the window).  Everything that is given back is given back before anything is taken."""
+    from fms_b200.cache import Cache, CacheFull, KVRequest
+
+    cache = Cache([KVRequest(1, 16, window=64)], max_tokens=64 * 4, max_positions=1024, dtype=torch.float32, device="cpu",
+                  max_slots=2)
+    a, b = cache.begin(2)
+    cache.prepare([a, b], [128, 128])
+    cache.commit([a, b], [128, 128])
+    pool = cache.groups[0].pool
+    assert pool.n_free == 0
+    # position 128 sees keys 65..128: block 0 (0..63) has left the window, block 2 is needed
+    cache.prepare([a, b], [1, 1])
+    cache.commit([a, b], [1, 1])
+    assert pool.n_free == 0 and all(len(cache.groups[0].held_blocks(s)) == 2 for s in (a, b))
+    # a step that does not fit raises before anything is taken or given back
+    held = [cache.groups[0].held_blocks(s) for s in (a, b)]
+    with pytest.raises(CacheFull):
+        cache.prepare([a, b], [64, 64])  # keeps blocks 1.. of each (the first query still sees them) and needs one more each
+    assert [cache.groups[0].held_blocks(s) for s in (a, b)] == held and pool.n_free == 0
+    cache.release([a, b])
+    assert pool.n_held == 0
+
+
+def test_sequences_that_start_at_other_positions_keep_length_and_position_apart():
+    from fms_b200.cache import Cache, CacheFull, KVRequest
+
+    cache = Cache([KVRequest(1, 16)], max_tokens=256, max_positions=100, dtype=torch.float32, device="cpu")
+    a, b = cache.begin(2, [0, 40])
+    cache.prepare([a, b], [10, 10])
+    cache.commit([a, b], [10, 10])
+    assert (cache.length[a], cache.position[a], cache.offset(a)) == (10, 10, 0)
+    assert (cache.length[b], cache.position[b], cache.offset(b)) == (10, 50, 40)
+    with pytest.raises(CacheFull, match="positions"):
+        cache.prepare([b], [51])  # position 50 + 51 exceeds the model's 100 positions although the cache has room
+    cache.prepare([b], [50])
+    cache.release([a, b])
+    (c,) = cache.begin(1)
+    assert cache.offset(c) == 0  # nothing of the old offset is left in a slot that is used again
+    with pytest.raises(ValueError):
+        cache.begin(1, [-1])

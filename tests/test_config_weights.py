@@ -271,3 +271,71 @@ def test_the_references_serialization_import_path(tiny_folders):
     with pytest.raises(FileNotFoundError):
         load_state_dict("/no/such/checkpoint")
     assert callable(get_adapted)
+
+
+def test_extend_adapter():
+    """fms/utils/serialization.py:104-148: steps appended to a source that exists; the others stay."""
+    from fms_b200.utils.serialization import extend_adapter, get_adapted, list_sources, register_adapter, register_adapter_step
+
+    register_adapter_step("toy_arch2", "double", lambda t, **kw: {k + k: v for k, v in t.items()})
+    register_adapter_step("toy_arch2", "upper", lambda t, **kw: {k.upper(): v for k, v in t.items()})
+    register_adapter("toy_arch2", "src", ["double"])
+    register_adapter("toy_arch2", "other", ["upper"])
+    extend_adapter("toy_arch2", "src", ["upper"])
+    assert list(get_adapted("toy_arch2", "src", {"a": torch.zeros(1)})) == ["AA"]
+    assert list(get_adapted("toy_arch2", "other", {"a": torch.zeros(1)})) == ["A"]  # untouched, still there
+    assert set(list_sources("toy_arch2")) == {"src", "other"}
+    with pytest.raises(KeyError, match="must already be registered"):
+        extend_adapter("toy_arch2", "no_such_source", ["upper"])
+    with pytest.raises(KeyError, match="is not registered"):
+        extend_adapter("toy_arch2", "src", ["no_such_step"])
+
+
+def test_compute_dtype_without_data_type_is_the_checkpoints(tmp_path):
+    """The matrix of fms tests/models/test_getmodel_datatype.py:17-85 for this library's two dtypes: no data_type means
+    the dtype the checkpoint's matrices are stored in (fms/utils/serialization.py:679-687), a data_type is obeyed, and
+    a checkpoint in float16 (or mixed) asks for one instead of being cast in silence."""
+    from fms_b200.models import get_model
+
+    base = tiny_tensors(TINY_A, 0, torch.float32)  # gains in float32, matrices in bfloat16
+
+    def folder(name, cast):
+        return write_folder(str(tmp_path / name), TINY_A, {k: (cast(k, v)) for k, v in base.items()})
+
+    as_bf16 = folder("bf16", lambda k, v: v)
+    as_fp32 = folder("fp32", lambda k, v: v.float())
+    as_fp16 = folder("fp16", lambda k, v: v.half())
+    mixed = folder("mixed", lambda k, v: v.float() if "o_proj" in k else v)
+
+    def dtypes(model):
+        sd = model.state_dict()
+        return model.dtype, sd["base_model.layers.0.attn.dense.weight"].dtype, sd["base_model.dec_norm.weight"].dtype
+
+    bf, f32 = torch.bfloat16, torch.float32
+    assert dtypes(get_model("hf_pretrained", model_path=as_bf16, device_type="cpu")) == (bf, bf, f32)
+    assert dtypes(get_model("hf_pretrained", model_path=as_fp32, device_type="cpu")) == (f32, f32, f32)
+    assert dtypes(get_model("hf_pretrained", model_path=as_bf16, device_type="cpu", data_type="fp32")) == (f32, f32, f32)
+    assert dtypes(get_model("hf_pretrained", model_path=as_fp16, device_type="cpu", data_type="bf16")) == (bf, bf, bf)
+    assert dtypes(get_model("hf_pretrained", model_path=as_fp16, device_type="cpu", data_type="fp32")) == (f32, f32, f32)
+    # a tensor stored in 32-bit stays so inside a bfloat16 model
+    assert dtypes(get_model("hf_pretrained", model_path=mixed, device_type="cpu", data_type="bf16")) == (bf, f32, f32)
+    for path in (as_fp16, mixed):
+        with pytest.raises(ValueError, match="pass data_type"):
+            get_model("hf_pretrained", model_path=path, device_type="cpu")
+    # random weights: bfloat16 unless told otherwise
+    assert get_model("llama", "tiny-a", device_type="cpu").dtype == bf
+    assert get_model("llama", "tiny-a", device_type="cpu", data_type=torch.float32).dtype == f32
+
+
+def test_the_references_own_initialisation():
+    from fms_b200.models import get_model
+
+    m = get_model("llama", "micro", device_type="cpu", data_type="fp32", init="fms", nlayers=1, seed=2)
+    sd = m.state_dict()
+    d, v = 192, 256
+    assert torch.equal(sd["base_model.dec_norm.weight"], torch.ones(d))
+    assert abs(sd["base_model.layers.0.attn.dense.weight"].std().item() - 0.02) < 0.002
+    assert abs(sd["base_model.embedding.weight"].std().item() - d ** -0.5) < 0.1 * d ** -0.5
+    assert abs(sd["head.weight"].std().item() - (d * v) ** -0.25) < 0.1 * (d * v) ** -0.25
+    with pytest.raises(ValueError):
+        get_model("llama", "micro", device_type="cpu", init="no_such_init")

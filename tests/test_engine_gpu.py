@@ -476,6 +476,36 @@ def test_further_configurations_against_the_plain_implementation(tmp_path, name,
     close(torch.stack(rows, 1).reshape(-1, cfg["vocab_size"]), want, dtype)
 
 
+def test_matrices_stored_in_32_bit_inside_a_bfloat16_model(tmp_path):
+    """A checkpoint whose output projections, down projections and head are stored in float32 (with values that
+    bfloat16 cannot hold), loaded with data_type="bf16": those matrices stay float32 and take the float32 product,
+    everything else runs as in any bfloat16 model.  Prompts in one step, then single tokens."""
+    from fms_b200.models import get_model
+    from tiny_models import TINY_D, tiny_tensors_of, write_folder
+
+    t = tiny_tensors_of("d")
+    g = torch.Generator().manual_seed(5)
+    for k in list(t):
+        if "o_proj" in k or "down_proj" in k or k == "lm_head.weight":
+            t[k] = t[k].float() * (1.0 + 0.003 * torch.rand(t[k].shape, generator=g))  # many mantissa bits
+    folder = write_folder(str(tmp_path / "m"), TINY_D, t)
+    oracle = pl.PlainLlama(folder)
+    model = get_model("hf_pretrained", model_path=folder, device_type="cuda", data_type="bf16")
+    sd = model.state_dict()
+    assert sd["head.weight"].dtype == torch.float32 and sd["base_model.layers.1.attn.dense.weight"].dtype == torch.float32
+    assert sd["base_model.layers.1.attn.in_proj.qkv_fused.weight"].dtype == torch.bfloat16
+    reqs = long_requests("d", 4)
+    engine = model.new_engine(max_tokens=2048)
+    slots = engine.begin(len(reqs))
+    cut = [max(1, len(r) - 4) for r in reqs]
+    first = engine.step(slots, [r[:c] for r, c in zip(reqs, cut)])
+    rows = [engine.step(slots, [[r[c + i]] for r, c in zip(reqs, cut)]) for i in range(4)]
+    engine.release(slots)
+    engine.check()
+    for i, (r, c) in enumerate(zip(reqs, cut)):
+        close(torch.cat([first[i:i + 1]] + [x[i:i + 1] for x in rows]), oracle.logits(r)[c - 1:], "bf16")
+
+
 def _peaked_model(tmp_path, qk_std, **sizes):
     """A model folder of the given sizes whose q and k projections are drawn wide enough for attention scores with a
     standard deviation between 1.5 and 2, and its oracle."""

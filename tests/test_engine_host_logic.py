@@ -111,3 +111,20 @@ def test_model_called_on_whole_sequences(tiny_folders):
             model(torch.tensor(prompts[0]), use_cache=True)
         with pytest.raises(ValueError):
             model([[]])
+
+
+def test_a_sequence_that_starts_at_another_position(tiny_folders):
+    """Tiny E has the llama3 rescaling, so not even the rotation is a plain function of position differences in float32
+    rounding; the logits must be the plain implementation's with the same first position, prompt and single tokens."""
+    oracle = pl.PlainLlama(tiny_folders["e"])
+    prompt = tiny_prompts("e")[1]
+    with use_plain_ops():
+        engine = _model(tiny_folders["e"]).new_engine(max_tokens=256)
+        slots = engine.begin(2, first_positions=[0, 77])
+        got = [engine.step(slots, [prompt[:30], prompt[:30]], [list(range(30))] * 2)]
+        for t in range(30, len(prompt)):
+            got.append(engine.step(slots, [[prompt[t]], [prompt[t]]]))
+        engine.release(slots)
+    rows = torch.cat([got[0].view(2, 30, -1)] + [g.view(2, 1, -1) for g in got[1:]], 1).double()
+    torch.testing.assert_close(rows[0], oracle.logits(prompt), atol=2e-5, rtol=1e-4)
+    torch.testing.assert_close(rows[1], oracle.logits(prompt, first_position=77), atol=2e-5, rtol=1e-4)

@@ -13,6 +13,8 @@ import math
 import pytest
 import torch
 
+import plain_ops as P
+
 pytestmark = pytest.mark.gpu
 
 _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
@@ -59,6 +61,8 @@ def test_no_alloc_entry_point_equals_the_ordinary_one_twice_in_a_row(dtype):
         tol = dict(atol=2e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
         torch.testing.assert_close(out.float(), want.float(), **tol)
         assert torch.equal(out, want)  # the same kernels in the same order: the same bits
+        # and against the plain restatement, so that this test stands without the ordinary entry point
+        torch.testing.assert_close(out.float(), P.attention(q, batch, view, nheads, kvheads, hd, scale, 0).float(), **tol)
 
 
 def test_no_alloc_entry_point_refuses_what_exceeds_its_scratch():
