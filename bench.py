@@ -1,16 +1,25 @@
 """Decode and prefill throughput of the Llama-3-8B shape on one B200, random weights, bfloat16.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers L] [--model NAME]
+                    [--dtype bf16|fp32] [--points default|main|long]
 
 Prints ONE JSON line.  ``value``: decoded tokens a second at batch 8 (prompt lengths uniform in
-[128, 2048]), K decode steps timed on the device with CUDA events after W warm-up steps; a step is one
-decode step, the next token chosen greedily on the device.  ``e2e``: the same through the Python entry
-point ``generate`` with host token lists in and out (a pinned host-to-device copy of every step's tokens
-and a device-to-host read of every step's result inside the timed region).  ``prefill``: one prompt of
-2,048 tokens.  ``roofline``: the bytes a decode step has to read (every weight it uses once, and the
-cache of the live requests) over its time, against the measured copy bandwidth.  ``points``: decode at
-batch 1 and 64.  Weights (15 GB a step) are larger than L2, so no flush is needed between steps.
+[128, 2048]); after W warm-up steps, ``regions`` (5) regions of K decode steps each are timed on the device
+with CUDA events and the median region counts; a step is one decode step, the next token chosen greedily on
+the device.  ``e2e``: the same through the Python entry point ``generate`` with host token lists in and out (a
+pinned host-to-device copy of every step's tokens and a device-to-host read of every step's result inside the
+timed region), again the median of 5 regions of K steps.  ``prefill``: one prompt of 2,048 tokens.
+``roofline``: the bytes a decode step has to read (every weight it uses once, and the cache of the live
+requests) over its time, against the measured copy bandwidth.  ``points``: tokens a second of decode at batch
+1, 16, 32 and 64, of decode at batch 8 with 7,000 to 8,000 cached tokens a request, of prefills of 512 and 8,192
+tokens, and of the benchmark's further configurations (decode at batch 8 and a prefill of 2,048 tokens for the
+Llama-2-7B and Llama-2-13B shapes, decode at batch 8 in float32); ``points_frac``: each point's fraction of its
+roofline (copy bandwidth for decode, the dtype's arithmetic peak for prefill).  Weights (15 GB a step) are
+larger than L2, so no flush is needed between steps.
 
+``--dtype fp32`` measures the true 32-bit path (FFMA products, float32 cache) in the same line format.
+``--points main`` leaves the further configurations out; ``--points long`` adds decode at batch 64 with
+7,000 to 8,000 cached tokens a request (a prefill of half a million tokens comes before it).
 ``--only decode_b<N>`` or ``--only prefill`` prints that part alone (for profilers); ``--only gemm_rows``,
 ``attention_prefill`` and ``attention_decode`` time single kernels at the model's layer sizes over a range of rows,
 tokens or contexts, one JSON line a size.  The default warm-up of 24 steps covers the 80 ms or so that the GPU's
@@ -51,6 +60,11 @@ def choose_model(name):
     global MODEL, PROMPT_MIN, PROMPT_MAX
     MODEL = MODELS[name]
     PROMPT_MIN, PROMPT_MAX = MODEL["prompts"]
+
+
+# float32 on the CUDA cores: 148 multiprocessors x 128 lanes x 2 flops x 1.965 GHz (nominal; nobody measured it here)
+FP32_TFLOPS_NOMINAL = 148 * 128 * 2 * 1.965e9 / 1e12
+REGIONS = 5  # timed regions of --steps steps each; the median counts
 
 
 def peaks():
@@ -116,13 +130,13 @@ def random_prompts(lengths, vocab, seed=0):
     return [[int(t) for t in rng.integers(0, vocab, size=n)] for n in lengths]
 
 
-def decode_bytes(nlayers, batch_context_tokens, m=None):
+def decode_bytes(nlayers, batch_context_tokens, m=None, itemsize=2):
     """Bytes one decode step has to read: every weight it uses once, and the cache of the live requests."""
     m = m or MODEL
     d, hd, h, kv, f, v = m["emb_dim"], m["head_dim"], m["nheads"], m["kvheads"], m["ffn_hidden"], m["vocab"]
-    per_layer = ((h + 2 * kv) * hd * d + h * hd * d + 2 * f * d + f * d + 2 * d) * 2
-    weights = nlayers * per_layer + d * 2 + v * d * 2
-    cache = batch_context_tokens * nlayers * 2 * kv * hd * 2
+    per_layer = ((h + 2 * kv) * hd * d + h * hd * d + 2 * f * d + f * d + 2 * d) * itemsize
+    weights = nlayers * per_layer + d * itemsize + v * d * itemsize
+    cache = batch_context_tokens * nlayers * 2 * kv * hd * itemsize
     return weights + cache
 
 
@@ -207,63 +221,90 @@ def run_kernels(args):
     ops.check_error_flag("cuda")
 
 
-def run_ours(args):
-    import torch
+class Measured:
+    """One model on the device with an engine, and the measurements taken on it."""
 
-    from fms_b200.kernels import ops
-    from fms_b200.models import get_model
-    from fms_b200.utils.generation import generate
+    def __init__(self, model_info, dtype, nlayers, room, max_prompt, slots=64, long_requests=0):
+        """``room``: decode steps a request goes through; ``long_requests``: how many requests of up to the model's
+        whole context the cache has to hold beside ``slots`` requests of ``max_prompt`` tokens."""
+        import torch
 
-    pk = peaks()
-    nlayers = args.layers or MODEL["nlayers"]
-    model = get_model("llama", MODEL["variant"], device_type="cuda", data_type="bf16", seed=0, nlayers=nlayers)
-    cfg = model.config
-    assert (cfg.emb_dim, cfg.nheads, cfg.n_kvheads, cfg.ffn_hidden, cfg.src_vocab_size, cfg.max_expected_seq_len) == (
-        MODEL["emb_dim"], MODEL["nheads"], MODEL["kvheads"], MODEL["ffn_hidden"], MODEL["vocab"], MODEL["context"])
-    room = args.warmup + args.steps + 8
-    engine = model.new_engine(max_tokens=64 * (PROMPT_MAX + 2 * room + 128), max_slots=64)
+        from fms_b200.models import get_model
 
-    def device_decode(batch, steps, warmup):
-        """(tokens a second, ms a step, mean context, own kernels launched) of `steps` decode steps."""
-        lengths = prompt_lengths(batch)
-        prompts = random_prompts(lengths, MODEL["vocab"])
+        self.m, self.dtype, self.nlayers = model_info, dtype, nlayers
+        self.itemsize = 2 if dtype == "bf16" else 4
+        self.model = get_model("llama", model_info["variant"], device_type="cuda", data_type=dtype, seed=0, nlayers=nlayers)
+        cfg = self.model.config
+        assert (cfg.emb_dim, cfg.nheads, cfg.n_kvheads, cfg.ffn_hidden, cfg.src_vocab_size, cfg.max_expected_seq_len) == (
+            model_info["emb_dim"], model_info["nheads"], model_info["kvheads"], model_info["ffn_hidden"], model_info["vocab"],
+            model_info["context"])
+        self.engine = self.model.new_engine(max_tokens=max(slots * (max_prompt + 2 * room + 128),
+                                                           long_requests * model_info["context"]), max_slots=slots)
+        self.torch = torch
+
+    def close(self):
+        self.engine = self.model = None
+        self.torch.cuda.empty_cache()
+
+    def device_decode(self, batch, steps, warmup, lengths=None, regions=REGIONS):
+        """(tokens a second, ms a step, mean context, own kernels launched, ms a step of every region): after the
+        prompts and ``warmup`` decode steps, ``regions`` regions of ``steps`` decode steps, each between two CUDA events;
+        the median region counts."""
+        from fms_b200.kernels import ops
+
+        torch, engine = self.torch, self.engine
+        lengths = lengths or prompt_lengths(batch)
+        prompts = random_prompts(lengths, self.m["vocab"])
         slots = engine.begin(batch)
         try:
-            horizon = max(lengths) + max(3, warmup) + steps + 1
-            logits = engine.step(slots, prompts)
+            warmup = max(3, warmup)
+            horizon = max(lengths) + warmup + regions * steps + 1
+            if sum(lengths) > 100_000:  # many long prompts: eight requests a step
+                for i in range(0, batch, 8):
+                    last = engine.step(slots[i:i + 8], prompts[i:i + 8])
+                    logits = last if i == 0 else torch.cat([logits, last])
+            else:
+                logits = engine.step(slots, prompts)
             tokens = ops.argmax(logits)
-            for _ in range(max(3, warmup)):
+            for _ in range(warmup):
                 tokens = ops.argmax(engine.decode(slots, tokens_device=tokens, horizon=horizon))
             torch.cuda.synchronize()
-            context = sum(engine.length(s) for s in slots) + batch * (steps + 1) / 2.0
+            context = sum(engine.length(s) for s in slots) + batch * (regions * steps + 1) / 2.0
             launches0, graphs0 = ops.launches, engine.graph_launches
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-            for _ in range(steps):
-                tokens = ops.argmax(engine.decode(slots, tokens_device=tokens, horizon=horizon))
-            end.record()
+            events = [torch.cuda.Event(enable_timing=True) for _ in range(regions + 1)]
+            events[0].record()
+            for r in range(regions):
+                for _ in range(steps):
+                    tokens = ops.argmax(engine.decode(slots, tokens_device=tokens, horizon=horizon))
+                events[r + 1].record()
             torch.cuda.synchronize()
-            ms = start.elapsed_time(end)
-            launched = (ops.launches - launches0) + (engine.graph_launches - graphs0) * engine.kernels_per_graph
+            per_region = [events[r].elapsed_time(events[r + 1]) / steps for r in range(regions)]
+            ms = statistics.median(per_region)
+            launched = ((ops.launches - launches0) + (engine.graph_launches - graphs0) * engine.kernels_per_graph) // regions
             engine.check()
         finally:
             engine.release(slots)
-        return batch * steps / (ms / 1e3), ms / steps, context, launched
+        return batch / (ms / 1e3), ms, context, launched, per_region
 
-    def host_decode(batch, steps, warmup):
+    def host_decode(self, batch, steps, warmup, regions=REGIONS):
         """The same through generate(): host token lists in, host tokens out, every step."""
-        lengths = prompt_lengths(batch)
-        prompts = [torch.tensor(p) for p in random_prompts(lengths, MODEL["vocab"])]
-        h2d0 = engine.h2d_bytes
-        _, times = generate(engine, prompts, max_new_tokens=1 + max(3, warmup) + steps, do_sample=False,
-                            timing="per-token")
-        timed = times[-steps:]
-        h2d_decode = 4 * batch  # each decode step copies its tokens from a pinned host array
-        assert engine.h2d_bytes - h2d0 >= h2d_decode * steps
-        return batch * steps / sum(timed), h2d_decode, 4 * batch
+        from fms_b200.utils.generation import generate
 
-    def prefill(tokens, repeats=5):
-        prompt = random_prompts([tokens], MODEL["vocab"], seed=7)
+        torch, engine = self.torch, self.engine
+        lengths = prompt_lengths(batch)
+        prompts = [torch.tensor(p) for p in random_prompts(lengths, self.m["vocab"])]
+        h2d0 = engine.h2d_bytes
+        _, times = generate(engine, prompts, max_new_tokens=1 + max(3, warmup) + regions * steps, do_sample=False,
+                            timing="per-token")
+        timed = times[-regions * steps:]
+        per_region = [sum(timed[r * steps:(r + 1) * steps]) for r in range(regions)]
+        h2d_decode = 4 * batch  # each decode step copies its tokens from a pinned host array
+        assert engine.h2d_bytes - h2d0 >= h2d_decode * regions * steps
+        return batch * steps / statistics.median(per_region), h2d_decode, 4 * batch
+
+    def prefill(self, tokens, repeats=5):
+        torch, engine = self.torch, self.engine
+        prompt = random_prompts([tokens], self.m["vocab"], seed=7)
         ms = []
         for i in range(3 + repeats):  # three warm-up runs, then the timed ones
             (slot,) = engine.begin(1)
@@ -277,47 +318,100 @@ def run_ours(args):
                 ms.append(start.elapsed_time(end))
         return statistics.median(ms)
 
+    def decode_frac(self, ms_step, context, pk):
+        return decode_bytes(self.nlayers, context, self.m, self.itemsize) / (ms_step / 1e3) / 1e9 / pk["hbm_gbs"]
+
+    def prefill_frac(self, ms, tokens, pk):
+        peak = pk["bf16_tflops"] if self.dtype == "bf16" else FP32_TFLOPS_NOMINAL
+        return prefill_flops(self.nlayers, tokens, self.m) / (ms / 1e3) / (peak * 1e12)
+
+
+def run_ours(args):
+    import numpy as np
+
+    pk = peaks()
+    dtype = args.dtype
+    nlayers = args.layers or MODEL["nlayers"]
+    room = max(3, args.warmup) + REGIONS * args.steps + 8
+    long_context = args.points != "main" and not args.only and MODEL["context"] >= 8192
+    run = Measured(MODEL, dtype, nlayers, room, PROMPT_MAX, slots=64,
+                   long_requests=(64 if args.points == "long" else 8) if long_context else 0)
+
     if args.only:  # a short run of one part, for profilers: prints that part's figures only
         if args.only == "prefill":
-            print(json.dumps({"only": "prefill", "ms": round(prefill(PREFILL_TOKENS, repeats=args.steps), 3)}))
+            print(json.dumps({"only": "prefill", "ms": round(run.prefill(PREFILL_TOKENS, repeats=args.steps), 3)}))
         else:
             batch = int(args.only.split("_b")[1])
-            v, ms, _, _ = device_decode(batch, args.steps, args.warmup)
+            v, ms, _, _, _ = run.device_decode(batch, args.steps, args.warmup, regions=1)
             print(json.dumps({"only": args.only, "value": round(v, 1), "ms_per_step": round(ms, 4)}))
         return
     sampler = ClockSampler()
     sampler.start()
-    value, ms_step, context, launched = device_decode(BATCH, args.steps, args.warmup)
-    e2e, h2d, d2h = host_decode(BATCH, args.steps, args.warmup)
+    value, ms_step, context, launched, per_region = run.device_decode(BATCH, args.steps, args.warmup)
+    e2e, h2d, d2h = run.host_decode(BATCH, args.steps, args.warmup)
     sampler.stop()
-    side = max(8, args.steps // 4)
-    b1 = device_decode(1, side, args.warmup)[0]
-    b64 = device_decode(64, side, args.warmup)[0]
-    pf_ms = prefill(PREFILL_TOKENS)
-    pf_flops = prefill_flops(nlayers, PREFILL_TOKENS)
-    gbs = decode_bytes(nlayers, context) / (ms_step / 1e3) / 1e9
+    points, fracs = {}, {}
+
+    def decode_point(name, r, batch, steps, lengths=None, regions=3):
+        v, ms, ctx, _, _ = r.device_decode(batch, steps, args.warmup, lengths, regions)
+        points[name], fracs[name] = round(v, 1), round(r.decode_frac(ms, ctx, pk), 4)
+
+    def prefill_point(name, r, tokens, repeats=3):
+        ms = r.prefill(tokens, repeats)
+        points[name], fracs[name] = round(tokens / (ms / 1e3), 1), round(r.prefill_frac(ms, tokens, pk), 4)
+
+    side = max(32, args.steps // 2)
+    for b in (1, 16, 32, 64):
+        decode_point(f"decode_b{b}", run, b, side)
+    pf_ms = run.prefill(PREFILL_TOKENS)
+    prefill_point("prefill_512", run, 512)
+    if long_context:
+        rng = np.random.default_rng(5)
+        prefill_point("prefill_8192", run, 8192)
+        decode_point("decode_b8_ctx8192", run, 8, side, [int(x) for x in rng.integers(7000, 8000 - 3 * side - 32, size=8)])
+        if args.points == "long":
+            decode_point("decode_b64_ctx8192", run, 64, side, [int(x) for x in rng.integers(7000, 8000 - 3 * side - 32, size=64)])
+    gbs = decode_bytes(nlayers, context, MODEL, run.itemsize) / (ms_step / 1e3) / 1e9
+    pf_frac = run.prefill_frac(pf_ms, PREFILL_TOKENS, pk)
+    run.close()
+    if args.points != "main" and args.model == "llama-3-8b" and not args.layers:
+        # the benchmark's further configurations, each on a model of its own: decode at batch 8 and one prefill
+        others = [("l2_7b", MODELS["llama-2-7b"], "bf16"), ("l2_13b", MODELS["llama-2-13b"], "bf16")]
+        others.append(("fp32", MODELS["llama-3-8b"], "fp32") if dtype == "bf16" else ("bf16", MODELS["llama-3-8b"], "bf16"))
+        for tag, info, dt in others:
+            lo, hi = info["prompts"]
+            rng = np.random.default_rng(8)
+            lengths = [int(x) for x in rng.integers(lo, hi + 1, size=BATCH)]
+            steps = side if dt == "bf16" else 8
+            other = Measured(info, dt, info["nlayers"], max(3, args.warmup) + 3 * steps + 8, PROMPT_MAX, slots=BATCH)
+            decode_point(f"{tag}_decode_b8", other, BATCH, steps, lengths)
+            prefill_point(f"{tag}_prefill_2048", other, PREFILL_TOKENS, 3 if dt == "bf16" else 1)
+            other.close()
     out = {
         "metric": f"decode tok/s at batch 8 ({MODEL['label']} shape, random weights)", "value": round(value, 1),
         "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "dtype": dtype, "data": "synthetic", "impl": "ours",
         "config": {
             "model": MODEL["name"], "layers": nlayers, "layers_of_model": MODEL["nlayers"], "emb_dim": MODEL["emb_dim"],
             "nheads": MODEL["nheads"], "kvheads": MODEL["kvheads"], "head_dim": MODEL["head_dim"],
             "ffn_hidden": MODEL["ffn_hidden"], "vocab": MODEL["vocab"], "context": MODEL["context"],
             "global_batch": BATCH, "seq_len": f"prompts uniform in [{PROMPT_MIN},{PROMPT_MAX}]",
             "mean_context": round(context / BATCH, 1), "prefill_tokens": PREFILL_TOKENS, "parallelism": "1 gpu",
-            "weights": "random N(0,0.02), seed 0", "l2": f"weights read per step ({decode_bytes(nlayers, 0) / 1e9:.0f} GB) exceed L2; no flush",
-            "cache_block_tokens": 64, "peaks": pk["source"],
+            "weights": "random N(0,0.02), seed 0",
+            "l2": f"weights read per step ({decode_bytes(nlayers, 0, MODEL, run.itemsize) / 1e9:.0f} GB) exceed L2; no flush",
+            "timed": f"median of {REGIONS} regions of {args.steps} steps", "cache_block_tokens": 64,
+            "peaks": pk["source"] + ("" if dtype == "bf16" else f"; fp32 arithmetic {FP32_TFLOPS_NOMINAL:.1f} TFLOP/s nominal"),
         },
         "clocks": sampler.summary(),
         "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": int(launched),
         "prefill": {"value": round(PREFILL_TOKENS / (pf_ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3),
-                    "frac": round(pf_flops / (pf_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
+                    "frac": round(pf_frac, 4)},
         "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(gbs / pk["hbm_gbs"], 4)},
-        "points": {"decode_b1": round(b1, 1), "decode_b64": round(b64, 1)},
+        "regions": {"count": REGIONS, "ms_per_step": [round(x, 4) for x in per_region]},
+        "points": points, "points_frac": fracs,
     }
     print(json.dumps(out))
 
@@ -370,7 +464,7 @@ def run_reference(args):
     sampler.start()
     value, ms_step, e2e, context = decode(BATCH, args.steps)
     sampler.stop()
-    side = max(8, args.steps // 4)
+    side = max(32, args.steps // 2)
     b1 = decode(1, side)[0]
     b64 = decode(64, side)[0]
     ids = torch.tensor(random_prompts([PREFILL_TOKENS], MODEL["vocab"], seed=7), dtype=torch.long, device="cuda")
@@ -416,6 +510,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     ap.add_argument("--model", choices=sorted(MODELS), default="llama-3-8b",
                     help="the shape to measure; the default is the benchmark's, the others are its further configurations")
+    ap.add_argument("--dtype", choices=["bf16", "fp32"], default="bf16", help="fp32: the true 32-bit path")
+    ap.add_argument("--points", choices=["default", "main", "long"], default="default",
+                    help="main: without the further configurations; long: also decode at batch 64 with 8k contexts")
     args = ap.parse_args()
     choose_model(args.model)
     if args.gpus != 1:
