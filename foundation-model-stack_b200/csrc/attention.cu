@@ -55,7 +55,18 @@ struct AttnArgs {
   int nheads, kvheads;
   float scale;
   int window;
+  int table_rows;   // slots the table has rows for, and blocks in the cache: extents that only the bounds-checked
+  int pool_blocks;  // build looks at (0: not known)
 };
+
+// The cache block that holds key block kb of the sequence in `slot`; negative: none (a block given back behind a
+// window, or, in the bounds-checked build, an index outside the table or the cache, which is recorded).
+__device__ __forceinline__ int block_of(const AttnArgs& a, int slot, int kb) {
+  if (!FMS_IN(slot, a.table_rows) || !FMS_IN(kb, a.table_stride)) return -1;
+  const int blk = a.table[(size_t)slot * a.table_stride + kb];
+  if (blk >= 0 && !FMS_IN(blk, a.pool_blocks)) return -1;
+  return blk;
+}
 
 // ---------------------------------------------------------------------------------------------------
 // prefill: grid (query tiles, heads), 128 threads; thread (r = tid / 8, c = tid % 8) owns row r of the
@@ -101,7 +112,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a, const int
   for (int j = 0; j < HD / 8; ++j) acc[j] = 0.f;
 
   for (int kb = kb_lo; kb <= kb_hi; ++kb) {
-    const int blk = a.table[(size_t)slot * a.table_stride + kb];
+    const int blk = block_of(a, slot, kb);
     if (blk < 0) continue;  // uniform over the block: a block that left the window
     __syncthreads();
     const T* kbase = kc + ((size_t)blk * a.kvheads + kvh) * BLK * HD;
@@ -228,7 +239,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, float* __r
   const int warp = tid >> 5, lane = tid & 31;
 
   for (int kb = k_lo / BLK; kb * BLK < k_hi; ++kb) {
-    const int blk = a.table[(size_t)slot * a.table_stride + kb];
+    const int blk = block_of(a, slot, kb);
     if (blk < 0) continue;  // cannot happen for positions inside the window; skip rather than read
     const T* kbase = kc + ((size_t)blk * a.kvheads + kvh) * BLK * HD;
     const T* vbase = vc + ((size_t)blk * a.kvheads + kvh) * BLK * HD;
@@ -313,13 +324,16 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, float* __r
 #pragma unroll
     for (int k = 0; k < RP; ++k) sum += red[k][g][d];
     const int head = kvh * group + g0 + g;
-    part_o[(((size_t)seq * a.nheads + head) * n_splits + split) * HD + d] = sum;
+    const size_t at = ((size_t)seq * a.nheads + head) * n_splits + split;
+    if (FMS_IN(at, (size_t)gridDim.x * a.nheads * n_splits)) part_o[at * HD + d] = sum;
   }
   if (tid < ng) {
     const int head = kvh * group + g0 + tid;
-    float* ml = part_ml + (((size_t)seq * a.nheads + head) * n_splits + split) * 2;
-    ml[0] = sm[tid];
-    ml[1] = sl[tid];
+    const size_t at = ((size_t)seq * a.nheads + head) * n_splits + split;
+    if (FMS_IN(at, (size_t)gridDim.x * a.nheads * n_splits)) {
+      part_ml[at * 2] = sm[tid];
+      part_ml[at * 2 + 1] = sl[tid];
+    }
   }
 }
 
@@ -496,10 +510,11 @@ FMS_API int fms_attention_prefill(const void* q, void* out, int dtype, const voi
                                   const int* table, int table_stride, int block_tokens, const int* slots,
                                   const int* first_row, const int* len_after, const int* tiles, int n_tiles,
                                   int nheads, int kvheads, int head_dim, float scale, int window, int pool_blocks,
-                                  int* error_flag, cudaStream_t stream) {
+                                  int table_rows, int* error_flag, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (check_args("attention_prefill", nheads, kvheads, head_dim, block_tokens)) return 1;
-  AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window};
+  AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window,
+             table_rows, pool_blocks};
   if (nheads > 65535) return fms_fail("attention_prefill: %d heads", nheads);
   if (!(scale > 0.f)) return fms_fail("attention_prefill: the scale of the scores is %g; it must be positive", (double)scale);
 #if FMS_ATTENTION_TC
@@ -551,7 +566,7 @@ FMS_API int fms_attention_prefill(const void* q, void* out, int dtype, const voi
 
 // part_o: float [seqs, nheads, n_splits, HD]; part_ml: float [seqs, nheads, n_splits, 2]; both scratch.
 // pool_blocks: blocks in the cache (bounds the early L2 hints and the streaming kernel's tensor maps; 0 turns both
-// off).  total_len: cached tokens of all sequences together as far as the host knows (0: unknown), by which the
+// off).  table_rows: slots the table has rows for (looked at by the bounds-checked build only; 0: not known).  total_len: cached tokens of all sequences together as far as the host knows (0: unknown), by which the
 // kernel is chosen.  work_counter: one int that is 0 between launches, from which the streaming kernel's warps draw their
 // units; error_flag: where a kernel records that a wait ran out (either null: the streaming kernel is not used).
 // n_splits * 256 must cover every len_after (they live on the device, so the host cannot check it): a longer sequence
@@ -560,11 +575,13 @@ FMS_API int fms_attention_decode(const void* q, void* out, int dtype, const void
                                  const int* table, int table_stride, int block_tokens, const int* slots,
                                  const int* first_row, const int* len_after, int n_seqs, int n_splits, float* part_o,
                                  float* part_ml, int nheads, int kvheads, int head_dim, float scale, int window,
-                                 int pool_blocks, long total_len, int* work_counter, int* error_flag, cudaStream_t stream) {
+                                 int pool_blocks, int table_rows, long total_len, int* work_counter, int* error_flag,
+                                 cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (check_args("attention_decode", nheads, kvheads, head_dim, block_tokens)) return 1;
   if (!(scale > 0.f)) return fms_fail("attention_decode: the scale of the scores is %g; it must be positive", (double)scale);
-  AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window};
+  AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window,
+             table_rows, pool_blocks};
   return launch_decode("attention_decode", a, dtype, n_seqs, n_splits, part_o, part_ml, pool_blocks, total_len, work_counter, error_flag, stream);
 }
 
@@ -623,6 +640,6 @@ FMS_API int fms_attention_decode_no_alloc(const void* q, void* out, int dtype, c
   if (scratch == nullptr) return 1;
   float* part_o = scratch;                  // [seqs, nheads, n_splits, HD]
   float* part_ml = scratch + entries * HD;  // [seqs, nheads, n_splits, 2]
-  AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window};
+  AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window, 0, 0};
   return launch_decode("attention_decode_no_alloc", a, dtype, n_seqs, n_splits, part_o, part_ml, 0, 0, nullptr, nullptr, stream);
 }

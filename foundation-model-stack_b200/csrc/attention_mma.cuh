@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
 
   bool first_block = true;
   for (int kb = k_lo / BLK + warp; kb * BLK < k_hi; kb += NW) {
-    const int blk = a.table[(size_t)slot * a.table_stride + kb];
+    const int blk = block_of(a, slot, kb);
     if (blk < 0) continue;
     const __nv_bfloat16* ksrc = kc + ((size_t)blk * a.kvheads + kvh) * BLK * HD;
     __syncwarp();  // the buffer is free: every lane is past the previous block
@@ -356,9 +356,9 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
 #pragma unroll
         for (int w = 0; w < NW; ++w)
           sum += reinterpret_cast<const float*>(smem_raw + (size_t)w * BLK * ROWB)[r * HD + d] * f[w];
-        part_o[at * HD + d] = sum;
+        if (FMS_IN(at, (size_t)gridDim.x * a.nheads * n_splits)) part_o[at * HD + d] = sum;
       }
-      if (tid % TPH == 0) {
+      if (tid % TPH == 0 && FMS_IN(at, (size_t)gridDim.x * a.nheads * n_splits)) {
         part_ml[at * 2] = mm * (1.f / LOG2E);  // back to natural units, which attn_combine_kernel expects
         part_ml[at * 2 + 1] = lsum;
       }
@@ -438,7 +438,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32, HD <= 128 ? 3 : 1) attn_prefill
   auto issue = [&](int i) {  // copies block kb_lo + i into stage i % 2 (all threads take part)
     if (i < nblocks) {
       const int kb = kb_lo + i;
-      const int blk = a.table[(size_t)slot * a.table_stride + kb];
+      const int blk = block_of(a, slot, kb);
       unsigned char* kbuf = smem_raw + (size_t)(i & 1) * STAGE;
       unsigned char* vbuf = kbuf + BLK * ROWB;
       const __nv_bfloat16* ksrc = kc + ((size_t)max(blk, 0) * a.kvheads + kvh) * BLK * HD;

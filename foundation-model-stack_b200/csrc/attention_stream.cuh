@@ -76,7 +76,7 @@ __global__ void __launch_bounds__((SR_WARPS + 1) * 32, 1)
       while (true) {
         if (open && kb * BLK < k_hi) {
           kb_here = kb++;
-          blk = a.table[(size_t)slot * a.table_stride + kb_here];
+          blk = block_of(a, slot, kb_here);
           if (blk < 0) continue;  // given back behind a window
           first_here = first;
           first = false;
@@ -253,6 +253,7 @@ __global__ void __launch_bounds__((SR_WARPS + 1) * 32, 1)
         const int r = 2 * c + e;  // head within the chunk
         if (r < ng) {
           const size_t at = ((size_t)seq * a.nheads + kvh * group + g0 + r) * n_splits + split;
+          if (!FMS_IN(at, (size_t)n_seqs * a.nheads * n_splits)) continue;
 #pragma unroll
           for (int j = 0; j < HD / 16; ++j) {
             part_o[at * HD + 16 * j + g] = o[j][e];

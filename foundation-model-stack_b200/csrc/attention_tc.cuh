@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
     if (elect_one()) {
       for (int i = 0; i < nblocks && !*failed; ++i) {
         const int s = i % TC_STAGES;
-        const int blk = a.table[(size_t)slot * a.table_stride + kb_lo + i];
+        const int blk = block_of(a, slot, kb_lo + i);
         unsigned char* kdst = kv + (size_t)s * 2 * TC_KV_TILE;
         unsigned char* vdst = kdst + TC_KV_TILE;
         const int row = (max(blk, 0) * a.kvheads + kvh) * BLK;  // first row of the block in the [positions, HD] view
@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
       const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
       l += psum;
       // the values of a block that the sequence fills only partly: rows beyond its length become zeros
-      const int blk = a.table[(size_t)slot * a.table_stride + kb];
+      const int blk = block_of(a, slot, kb);
       if (kb * BLK + BLK > len || blk < 0) {
         ok = __all_sync(0xffffffffu, wait_or_abort(&v_full[s], (i / TC_STAGES) & 1, failed));
         if (!ok) break;

@@ -33,6 +33,40 @@ static inline int fms_launch_status(const char* what) {
 
 FMS_API const char* fms_last_error() { return g_fms_error; }
 
+// ---- bounds-checked build ---------------------------------------------------------------------------
+// Compiled with -DFMS_DEBUG_BOUNDS (environment variable FMS_B200_DEBUG_BOUNDS=1 when the library is built),
+// FMS_IN(index, extent) is false for an index outside [0, extent) and records the first such index of the process
+// (source line, index, extent) in a word of the library that fms_debug_bounds() reads and clears; the access is
+// then skipped, nothing traps and the context stays usable.  An extent <= 0 means "not known here": only a
+// negative index is caught.  Without the flag FMS_IN is the constant true and costs nothing.  This stands in for
+// a memory checker on machines where none can be run.
+#ifdef FMS_DEBUG_BOUNDS
+__device__ int g_fms_bounds[4] = {0, 0, 0, 0};  // violations, then line, index and extent of the first
+__device__ __forceinline__ bool fms_index_ok(long long i, long long n, int line) {
+  if (i >= 0 && (n <= 0 || i < n)) return true;
+  if (atomicAdd(&g_fms_bounds[0], 1) == 0) {
+    g_fms_bounds[1] = line;
+    g_fms_bounds[2] = (int)(i > 0x7fffffffLL ? 0x7fffffffLL : (i < -0x7fffffffLL ? -0x7fffffffLL : i));
+    g_fms_bounds[3] = (int)(n > 0x7fffffffLL ? 0x7fffffffLL : n);
+  }
+  return false;
+}
+#define FMS_IN(i, n) fms_index_ok((long long)(i), (long long)(n), __LINE__)
+// out[0..3]: violations since the last call, line, index, extent of the first.  Synchronises the device.
+FMS_API int fms_debug_bounds(int* out) {
+  int zero[4] = {0, 0, 0, 0};
+  if (cudaMemcpyFromSymbol(out, g_fms_bounds, sizeof(zero)) != cudaSuccess) return fms_fail("debug_bounds: read failed");
+  if (out[0] != 0 && cudaMemcpyToSymbol(g_fms_bounds, zero, sizeof(zero)) != cudaSuccess) return fms_fail("debug_bounds: reset failed");
+  return 0;
+}
+#else
+#define FMS_IN(i, n) true
+FMS_API int fms_debug_bounds(int* out) {  // not a checked build
+  (void)out;
+  return -1;
+}
+#endif
+
 // ---- conversions ------------------------------------------------------------------------------------
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -40,12 +40,13 @@ FMS_API int fms_embed_rows(const void* table, int table_dtype, const int* tokens
 template <typename T, typename TG>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                    const TG* __restrict__ gain, float eps, T* __restrict__ out,
-                                   const int* __restrict__ rows, int dim) {
+                                   const int* __restrict__ rows, int dim, int residual_rows) {
   __shared__ float scratch[33];
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
+  if (!FMS_IN(src, residual_rows)) return;  // the whole block alike
   float* res = residual + (size_t)src * dim;
   const T* del = delta ? delta + (size_t)src * dim : nullptr;
   float ss = 0.f;
@@ -99,7 +100,7 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, const float* v) {
 template <typename T, typename TG, int NCHUNK>
 __global__ void add_rmsnorm_regs_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                         const TG* __restrict__ gain, float eps, T* __restrict__ out,
-                                        const int* __restrict__ rows, int dim) {
+                                        const int* __restrict__ rows, int dim, int residual_rows) {
   __shared__ float scratch[33];
   pdl_launch_dependents();
   const int r = blockIdx.x;
@@ -112,6 +113,7 @@ __global__ void add_rmsnorm_regs_kernel(float* __restrict__ residual, const T* _
   }
   pdl_wait();
   const int src = rows ? rows[r] : r;
+  if (!FMS_IN(src, residual_rows)) return;  // the whole block alike
   float* res = residual + (size_t)src * dim;
   const T* del = delta ? delta + (size_t)src * dim : nullptr;
 #pragma unroll
@@ -150,8 +152,10 @@ __global__ void add_rmsnorm_regs_kernel(float* __restrict__ residual, const T* _
   }
 }
 
+// residual_rows: rows of the residual stream (and of delta), which the entries of `rows` index; used by the
+// bounds-checked build only (0: not known)
 FMS_API int fms_add_rmsnorm(float* residual, const void* delta, const void* gain, int gain_dtype, float eps, void* out,
-                            int dtype, const int* rows, int n_rows, int dim, cudaStream_t stream) {
+                            int dtype, const int* rows, int n_rows, int dim, int residual_rows, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (dim <= 0) return fms_fail("add_rmsnorm: dim %d", dim);
   if (dim % 4 == 0 && dim <= 4 * 4 * 1024) {
@@ -163,20 +167,20 @@ FMS_API int fms_add_rmsnorm(float* residual, const void* delta, const void* gain
     FMS_DISPATCH_DTYPE(dtype, T, FMS_DISPATCH_DTYPE(gain_dtype, TG, {
       if (nchunk <= 1)
         fms_launch(add_rmsnorm_regs_kernel<T, TG, 1>, dim3(n_rows), dim3(threads), 0, stream, residual, (const T*)delta,
-                   (const TG*)gain, eps, (T*)out, rows, dim);
+                   (const TG*)gain, eps, (T*)out, rows, dim, residual_rows);
       else if (nchunk <= 2)
         fms_launch(add_rmsnorm_regs_kernel<T, TG, 2>, dim3(n_rows), dim3(threads), 0, stream, residual, (const T*)delta,
-                   (const TG*)gain, eps, (T*)out, rows, dim);
+                   (const TG*)gain, eps, (T*)out, rows, dim, residual_rows);
       else
         fms_launch(add_rmsnorm_regs_kernel<T, TG, 4>, dim3(n_rows), dim3(threads), 0, stream, residual, (const T*)delta,
-                   (const TG*)gain, eps, (T*)out, rows, dim);
+                   (const TG*)gain, eps, (T*)out, rows, dim, residual_rows);
     }));
     return fms_launch_status("add_rmsnorm");
   }
   const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
   FMS_DISPATCH_DTYPE(dtype, T, FMS_DISPATCH_DTYPE(gain_dtype, TG,
                      fms_launch(add_rmsnorm_kernel<T, TG>, dim3(n_rows), dim3(threads), 0, stream, residual,
-                                (const T*)delta, (const TG*)gain, eps, (T*)out, rows, dim)));
+                                (const T*)delta, (const TG*)gain, eps, (T*)out, rows, dim, residual_rows)));
   return fms_launch_status("add_rmsnorm");
 }
 
@@ -264,7 +268,8 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
                                   const int* __restrict__ token_seq,
                                   const int* __restrict__ slots, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                   const int* __restrict__ table, int table_stride, int block_tokens, int nheads,
-                                  int kvheads, int head_dim, int write_cache, int* __restrict__ error_flag) {
+                                  int kvheads, int head_dim, int write_cache, int* __restrict__ error_flag, int n_seqs,
+                                  int table_rows, int pool_blocks) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -292,12 +297,16 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
     return;
   }
   if (!write_cache) return;
-  const int slot = slots[token_seq[t]];
+  const int seq = token_seq[t];
+  if (!FMS_IN(seq, n_seqs)) return;
+  const int slot = slots[seq];
+  if (!FMS_IN(slot, table_rows) || !FMS_IN(pos / block_tokens, table_stride)) return;
   const int blk = table[(size_t)slot * table_stride + pos / block_tokens];
   if (blk < 0) {
     if (i == 0 && error_flag) atomicExch(error_flag, 2);
     return;
   }
+  if (!FMS_IN(blk, pool_blocks)) return;
   const int kvh = is_v ? head - nheads - kvheads : head - nheads;
   T* base = is_v ? v_cache : k_cache;
   T* dst = base + (((size_t)blk * kvheads + kvh) * block_tokens + (pos % block_tokens)) * head_dim;
@@ -315,7 +324,8 @@ __global__ void rope_store_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __n
                                       const int* __restrict__ slots,
                                       __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
                                       const int* __restrict__ table, int table_stride, int block_tokens, int nheads,
-                                      int kvheads, int head_dim, int write_cache, int* __restrict__ error_flag) {
+                                      int kvheads, int head_dim, int write_cache, int* __restrict__ error_flag,
+                                      int n_seqs, int table_rows, int pool_blocks) {
   extern __shared__ float2 sincos_of_pair[];  // [head_dim / 2]: (sin, cos)
   pdl_launch_dependents();
   pdl_wait();
@@ -326,8 +336,15 @@ __global__ void rope_store_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __n
   const size_t width = (size_t)(nheads + 2 * kvheads) * head_dim;
   int blk = 0;
   if (write_cache) {
-    blk = table[(size_t)slots[token_seq[t]] * table_stride + pos / block_tokens];
-    if (blk < 0 && threadIdx.x == 0 && error_flag) atomicExch(error_flag, 2);
+    const int seq = token_seq[t];
+    const int slot = FMS_IN(seq, n_seqs) ? slots[seq] : -1;
+    if (slot >= 0 && FMS_IN(slot, table_rows) && FMS_IN(pos / block_tokens, table_stride)) {
+      blk = table[(size_t)slot * table_stride + pos / block_tokens];
+      if (blk < 0 && threadIdx.x == 0 && error_flag) atomicExch(error_flag, 2);
+      if (blk >= 0 && !FMS_IN(blk, pool_blocks)) blk = -1;
+    } else {
+      blk = -1;
+    }
   }
   if (inv_freq != nullptr) {
     const float turned_by = (float)(position_ids ? position_ids[t] : pos);
@@ -367,7 +384,9 @@ __global__ void rope_store_vec_kernel(const __nv_bfloat16* __restrict__ qkv, __n
 FMS_API int fms_rope_store(const void* qkv, int dtype, void* q_out, const float* inv_freq, const int* positions,
                            const int* position_ids, const int* token_seq, const int* slots, void* k_cache, void* v_cache, const int* table,
                            int table_stride, int block_tokens, int n_tokens, int nheads, int kvheads, int head_dim,
-                           int write_cache, int* error_flag, cudaStream_t stream) {
+                           int write_cache, int* error_flag, int n_seqs, int table_rows, int pool_blocks,
+                           cudaStream_t stream) {
+  // n_seqs, table_rows, pool_blocks: extents of slots, of the table and of the cache, for the bounds-checked build (0: not known)
   if (n_tokens <= 0) return 0;
   if (head_dim <= 0 || head_dim % 2 || head_dim > 2048) return fms_fail("rope_store: head_dim %d", head_dim);
   if (dtype == FMS_BF16 && head_dim % 8 == 0 && n_tokens >= 64 && head_dim / 2 <= ROPE_VEC_MAX_PAIRS) {
@@ -377,7 +396,7 @@ FMS_API int fms_rope_store(const void* qkv, int dtype, void* q_out, const float*
                (const __nv_bfloat16*)qkv,
                (__nv_bfloat16*)q_out, inv_freq, positions, position_ids, token_seq, slots, (__nv_bfloat16*)k_cache,
                (__nv_bfloat16*)v_cache, table, table_stride, block_tokens, nheads, kvheads, head_dim, write_cache,
-               error_flag);
+               error_flag, n_seqs, table_rows, pool_blocks);
     return fms_launch_status("rope_store");
   }
   dim3 grid(n_tokens, nheads + 2 * kvheads);
@@ -386,7 +405,7 @@ FMS_API int fms_rope_store(const void* qkv, int dtype, void* q_out, const float*
                      fms_launch(rope_store_kernel<T>, grid, dim3(threads), 0, stream, (const T*)qkv, (T*)q_out, inv_freq,
                                 positions, position_ids, token_seq, slots, (T*)k_cache, (T*)v_cache, table, table_stride,
                                 block_tokens,
-                                nheads, kvheads, head_dim, write_cache, error_flag));
+                                nheads, kvheads, head_dim, write_cache, error_flag, n_seqs, table_rows, pool_blocks));
   return fms_launch_status("rope_store");
 }
 

@@ -41,6 +41,7 @@ struct RopeArgs {
   const int* table;            // [slots, table_stride]
   int table_stride, block_tokens, nheads, kvheads, head_dim, write_cache;
   int* error_flag;
+  int n_seqs, table_rows, pool_blocks;  // extents of slots, of the table and of the cache, for the bounds-checked build
 };
 
 __device__ __forceinline__ void mma_bf16(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -201,7 +202,7 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const __nv_bfloa
           gate += __bfloat162float(bias[row]);
           up += __bfloat162float(bias[hidden + row]);
         }
-        y[(size_t)m * hidden + row] = from_f32<TOut>(activate(gate, act) * up);
+        if (FMS_IN((size_t)m * hidden + row, (size_t)M * hidden)) y[(size_t)m * hidden + row] = from_f32<TOut>(activate(gate, act) * up);
       }
     }
   } else if (MODE == QKV_ROPE) {
@@ -232,11 +233,16 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const __nv_bfloa
       if (head < rope.nheads) {
         *reinterpret_cast<__nv_bfloat162*>(rope.q_out + ((size_t)m * rope.nheads + head) * rope.head_dim + d) = out;
       } else if (rope.write_cache) {
-        const int blk = rope.table[(size_t)rope.slots[rope.token_seq[m]] * rope.table_stride + pos / rope.block_tokens];
+        const int seq = rope.token_seq[m];
+        if (!FMS_IN(seq, rope.n_seqs)) continue;
+        const int slot = rope.slots[seq];
+        if (!FMS_IN(slot, rope.table_rows) || !FMS_IN(pos / rope.block_tokens, rope.table_stride)) continue;
+        const int blk = rope.table[(size_t)slot * rope.table_stride + pos / rope.block_tokens];
         if (blk < 0) {
           if (rope.error_flag) atomicExch(rope.error_flag, 2);
           continue;
         }
+        if (!FMS_IN(blk, rope.pool_blocks)) continue;
         const int kvh = is_v ? head - rope.nheads - rope.kvheads : head - rope.nheads;
         __nv_bfloat16* base = is_v ? rope.v_cache : rope.k_cache;
         *reinterpret_cast<__nv_bfloat162*>(
@@ -252,7 +258,7 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const __nv_bfloa
       if (row < N && m < M) {
         float v = red[0][t][j][l][e];
         if (bias) v += __bfloat162float(bias[row]);
-        y[(size_t)m * N + row] = from_f32<TOut>(v);
+        if (FMS_IN((size_t)m * N + row, (size_t)M * N)) y[(size_t)m * N + row] = from_f32<TOut>(v);
       }
     }
   }
@@ -311,7 +317,8 @@ FMS_API int fms_qkv_rope_store_bf16_skinny(const void* x, const void* w, const v
                                            const float* inv_freq, const int* positions, const int* position_ids,
                                            const int* token_seq, const int* slots, void* k_cache, void* v_cache, const int* table,
                                            int table_stride, int block_tokens, int M, int K, int nheads, int kvheads,
-                                           int head_dim, int write_cache, int* error_flag, cudaStream_t stream) {
+                                           int head_dim, int write_cache, int* error_flag, int n_seqs, int table_rows,
+                                           int pool_blocks, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (M > 8) return fms_fail("qkv_rope_store_bf16_skinny: %d rows, at most 8", M);
   if (K <= 0 || K % 8) return fms_fail("qkv_rope_store_bf16_skinny: K %d must be a positive multiple of 8", K);
@@ -322,7 +329,7 @@ FMS_API int fms_qkv_rope_store_bf16_skinny(const void* x, const void* w, const v
   if (rows > 0x7fffffffL) return fms_fail("qkv_rope_store_bf16_skinny: %ld rows of w", rows);
   const RopeArgs rope{(__nv_bfloat16*)q_out, inv_freq, positions, position_ids, token_seq, slots, (__nv_bfloat16*)k_cache,
                       (__nv_bfloat16*)v_cache, table, table_stride, block_tokens, nheads, kvheads, head_dim, write_cache,
-                      error_flag};
+                      error_flag, n_seqs, table_rows, pool_blocks};
   if (rows < 16384) return launch_typed<1, 1, QKV_ROPE, __nv_bfloat16>(x, w, bias, nullptr, M, (int)rows, K, 0, 0, stream, rope);
   return launch_typed<1, 2, QKV_ROPE, __nv_bfloat16>(x, w, bias, nullptr, M, (int)rows, K, 0, 0, stream, rope);
 }

@@ -80,7 +80,8 @@ __device__ __forceinline__ void store_rows(const Epilogue& ep, uint32_t taddr, i
       for (int jj = 0; jj < 16; ++jj)
         if (col0 + jj < ncols) v[jj] += __bfloat162float(bias[col0 + jj]);
     }
-    if (row >= M) continue;
+    if (row >= M || col0 >= ncols) continue;  // nothing of these 16 columns lies inside y
+    if (!FMS_IN((size_t)row * ncols + col0, (size_t)M * ncols)) continue;
     if (ep.out_f32) {
       float* o = (float*)ep.out + (size_t)row * ncols + col0;
 #pragma unroll

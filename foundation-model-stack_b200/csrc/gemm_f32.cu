@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__
 #pragma unroll
     for (int j = 0; j < TN; ++j) {
       const int gn = n0 + tn + j;
-      if (gn < N) y[(size_t)gm * N + gn] = acc[i][j] + (bias ? bias[gn] : 0.f);
+      if (gn < N && FMS_IN((size_t)gm * N + gn, (size_t)M * N)) y[(size_t)gm * N + gn] = acc[i][j] + (bias ? bias[gn] : 0.f);
     }
   }
 }
@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(FEW_THREADS) gemm_f32_few_rows_kernel(const fl
     const float b = bias ? bias[n] : 0.f;
 #pragma unroll
     for (int m = 0; m < FEW_ROWS; ++m)
-      if (m < M) y[(size_t)m * N + n] = acc[m] + b;
+      if (m < M && FMS_IN((size_t)m * N + n, (size_t)M * N)) y[(size_t)m * N + n] = acc[m] + b;
   }
 }
 }  // namespace

@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
-    if (lane == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;  // a row of NaN or -inf only: token 0
+    if (lane == 0 && FMS_IN(bi == 0x7fffffff ? 0 : bi, vocab)) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;  // a row of NaN or -inf only: token 0
   }
 }
 
@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
       base_sum = __shfl_sync(0xffffffffu, cum, 31);
     }
     if (chosen < 0) chosen = last_kept >= 0 ? last_kept : 0;
-    if (lane == 0) out[blockIdx.x] = chosen;
+    if (lane == 0 && FMS_IN(chosen, vocab)) out[blockIdx.x] = chosen;
   }
 }
 }  // namespace

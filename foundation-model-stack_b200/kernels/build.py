@@ -24,6 +24,12 @@ from typing import Dict, List, Optional, Tuple
 CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-shared"]
+# FMS_B200_DEBUG_BOUNDS=1: the libraries are built with index checks (csrc/common.cuh, FMS_IN) that record the first
+# index outside its array instead of making the access; ops.check_error_flag then raises with its source line.  The
+# flag is part of a library's name, so checked and unchecked builds lie side by side.
+DEBUG_BOUNDS = os.environ.get("FMS_B200_DEBUG_BOUNDS", "0") not in ("", "0")
+if DEBUG_BOUNDS:
+    BASE_FLAGS = BASE_FLAGS + ["-DFMS_DEBUG_BOUNDS"]
 
 # library name -> (source file, extra flags)
 PLAIN_LIBRARIES = {
@@ -34,6 +40,7 @@ PLAIN_LIBRARIES = {
     "sampling": ("sampling.cu", []),
 }
 
+_TAG = "_checked" if DEBUG_BOUNDS else ""
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 _dir_lock = threading.Lock()
@@ -104,13 +111,13 @@ def _digest(source: str, flags: List[str]) -> str:
 
 def library_path(name: str) -> str:
     source, flags = _spec(name)
-    return os.path.join(build_dir(), f"libfms_{name}_{_digest(source, flags)}.so")
+    return os.path.join(build_dir(), f"libfms_{name}{_TAG}_{_digest(source, flags)}.so")
 
 
 def find_built(name: str) -> Optional[str]:
     """The library if it is already compiled — in the package's own folder or the per-user one."""
     source, flags = _spec(name)
-    fname = f"libfms_{name}_{_digest(source, flags)}.so"
+    fname = f"libfms_{name}{_TAG}_{_digest(source, flags)}.so"
     for d in (os.environ.get("FMS_B200_BUILD_DIR"), os.path.join(CSRC, "_build"),
               os.path.join(tempfile.gettempdir(), f"fms_b200_build_{os.getuid()}")):
         if d and os.path.isfile(os.path.join(d, fname)):
@@ -140,7 +147,8 @@ def compile_library(name: str, verbose: bool = True) -> str:
         raise KernelBuildError(f"nvcc failed on {source}:\n{' '.join(cmd)}\n{output}")
     os.replace(tmp, out)
     for stale in os.listdir(os.path.dirname(out)):  # earlier builds of this library, from other sources or flags
-        if stale.startswith(f"libfms_{name}_") and stale.endswith(".so") and stale != os.path.basename(out):
+        if (stale.startswith(f"libfms_{name}{_TAG}_") and stale.endswith(".so") and stale != os.path.basename(out)
+                and len(stale) == len(os.path.basename(out))):
             try:
                 os.remove(os.path.join(os.path.dirname(out), stale))
             except OSError:
@@ -182,6 +190,26 @@ def load_library(name: str) -> ctypes.CDLL:
         lib.fms_last_error.restype = ctypes.c_char_p
         _loaded[name] = lib
         return lib
+
+
+def loaded_libraries() -> Dict[str, ctypes.CDLL]:
+    with _lock:
+        return dict(_loaded)
+
+
+def bounds_violations() -> List[str]:
+    """In a bounds-checked build: for every loaded library that met an index outside its array since the last call,
+    one line with the source line, the index and the extent of the first (reading clears it).  Synchronises."""
+    out = []
+    if not DEBUG_BOUNDS:
+        return out
+    for name, lib in loaded_libraries().items():
+        word = (ctypes.c_int * 4)()
+        if lib.fms_debug_bounds(word) == 0 and word[0]:
+            source = _spec(name)[0]
+            out.append(f"{name}: {word[0]} accesses outside their arrays were skipped; the first at a check near line "
+                       f"{word[1]} of {source} or of a header it includes: index {word[2]}, extent {word[3]}")
+    return out
 
 
 def all_library_names(head_dims=(16, 32, 48, 64, 128, 256)) -> List[str]:

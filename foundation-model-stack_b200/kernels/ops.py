@@ -25,21 +25,22 @@ _P, _I, _F, _U64, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_u
 
 _SIGNATURES = {
     "fms_embed_rows": [_P, _I, _P, _P, _I, _I, _I, _F, _P, _P],
-    "fms_add_rmsnorm": [_P, _P, _P, _I, _F, _P, _I, _P, _I, _I, _P],
+    "fms_add_rmsnorm": [_P, _P, _P, _I, _F, _P, _I, _P, _I, _I, _I, _P],
     "fms_gated_activation": [_P, _P, _I, _I, _I, _I, _P],
-    "fms_rope_store": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "fms_rope_store": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _I, _P],
     "fms_decode_advance": [_P, _P, _P, _P, _I, _P],
     "fms_gemm_f32": [_P, _P, _P, _P, _I, _I, _I, _P],
     "fms_linear_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "fms_glu_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "fms_qkv_rope_store_bf16_skinny": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P,
-                                       _P],
+                                       _I, _I, _I, _P],
     "fms_gemm_bf16_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "fms_glu_bf16_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "fms_argmax": [_P, _P, _I, _I, _P],
     "fms_sample": [_P, _P, _I, _I, _F, _I, _U64, _P, _I, _P],
-    "fms_attention_prefill": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P],
-    "fms_attention_decode": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _F, _I, _I, _L, _P, _P, _P],
+    "fms_attention_prefill": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P],
+    "fms_attention_decode": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _F, _I, _I, _I, _L, _P, _P,
+                             _P],
 }
 _functions = {}
 # kernels launched through this module since import (a decode-attention call over several splits launches two)
@@ -125,8 +126,15 @@ def _work_counter(device) -> torch.Tensor:
 
 
 def check_error_flag(device) -> None:
+    """Raises if a kernel met something the host should have prevented; in a bounds-checked build
+    (FMS_B200_DEBUG_BOUNDS=1) also if any kernel computed an index outside its array.  Synchronises."""
     flag = error_flag(device)
     v = int(flag.item())
+    from .build import bounds_violations
+
+    outside = bounds_violations()
+    if outside:
+        raise KernelError("bounds-checked build: " + "; ".join(outside))
     if v:
         flag.zero_()
         raise KernelError({1: "a token id outside the vocabulary reached the embedding",
@@ -159,7 +167,7 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], gain: tor
         raise KernelError(f"sublayer output is {delta.dtype}, compute dtype is {out_dtype}")
     out = torch.empty((n, dim), dtype=out_dtype, device=residual.device)
     _call("elementwise", "fms_add_rmsnorm", _ptr(residual), _ptr(delta), _ptr(gain), _code(gain.dtype), float(eps),
-          _ptr(out), _code(out_dtype), _ptr(rows), n, dim, _stream())
+          _ptr(out), _code(out_dtype), _ptr(rows), n, dim, residual.shape[0], _stream())
     return out
 
 
@@ -271,7 +279,7 @@ def rope_store(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], batch, view,
           _ptr(getattr(batch, "position_ids", None)), _ptr(batch.token_seq), _ptr(batch.slots), _ptr(view.keys),
           _ptr(view.values), _ptr(view.table),
           view.table.shape[1], view.block_tokens, n, nheads, kvheads, head_dim, 1 if writes_cache else 0,
-          _ptr(error_flag(qkv.device)), _stream())
+          _ptr(error_flag(qkv.device)), batch.slots.shape[0], view.table.shape[0], view.keys.shape[0], _stream())
     return q
 
 
@@ -293,7 +301,8 @@ def qkv_rope_store(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
               _ptr(inv_freq), _ptr(batch.positions), _ptr(getattr(batch, "position_ids", None)), _ptr(batch.token_seq),
               _ptr(batch.slots), _ptr(view.keys), _ptr(view.values), _ptr(view.table), view.table.shape[1],
               view.block_tokens, n, weight.shape[1], nheads,
-              kvheads, head_dim, 1 if writes_cache else 0, _ptr(error_flag(x.device)), _stream())
+              kvheads, head_dim, 1 if writes_cache else 0, _ptr(error_flag(x.device)), batch.slots.shape[0],
+              view.table.shape[0], view.keys.shape[0], _stream())
         return q
     return rope_store(linear(x, weight, bias), inv_freq, batch, view, nheads, kvheads, head_dim, writes_cache)
 
@@ -330,7 +339,8 @@ def attention(q: torch.Tensor, batch, view, nheads: int, kvheads: int, head_dim:
         part_ml = torch.empty((batch.n_seqs, nheads, n_splits, 2), dtype=torch.float32, device=q.device)
         # total_len (what the host knows of the sequences' lengths) chooses between the two bfloat16 decode kernels
         _call(lib, "fms_attention_decode", *common, batch.n_seqs, n_splits, _ptr(part_o), _ptr(part_ml), nheads,
-              kvheads, head_dim, float(scale), int(window), view.keys.shape[0], int(getattr(batch, "total_len", 0)),
+              kvheads, head_dim, float(scale), int(window), view.keys.shape[0], view.table.shape[0],
+              int(getattr(batch, "total_len", 0)),
               _ptr(_work_counter(q.device)), _ptr(error_flag(q.device)), _stream())
         if n_splits > 1 or q.dtype == torch.float32:
             global launches
@@ -338,7 +348,7 @@ def attention(q: torch.Tensor, batch, view, nheads: int, kvheads: int, head_dim:
     else:
         tiles = batch.query_tiles(tile_rows)
         _call(lib, "fms_attention_prefill", *common, _ptr(tiles), tiles.shape[0], nheads, kvheads, head_dim,
-              float(scale), int(window), view.keys.shape[0], _ptr(error_flag(q.device)), _stream())
+              float(scale), int(window), view.keys.shape[0], view.table.shape[0], _ptr(error_flag(q.device)), _stream())
     return out
 
 

@@ -13,6 +13,7 @@ for p in (ROOT, os.path.dirname(os.path.abspath(__file__))):
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+    config.addinivalue_line("markers", "expects_a_recorded_index: the test itself reads the bounds-checked build's record")
 
 
 def pytest_collection_modifyitems(config, items):
@@ -33,3 +34,16 @@ def tiny_folders(tmp_path_factory):
 
     root = tmp_path_factory.mktemp("tiny_models")
     return {w: write_tiny(str(root / w), w) for w in ("a", "b", "c", "d", "e")}
+
+
+@pytest.fixture(autouse=True)
+def no_index_outside_its_array(request):
+    """When the kernels are built with their index checks (FMS_B200_DEBUG_BOUNDS=1), every GPU test also fails if a
+    kernel computed an index outside its array (the access was skipped and recorded)."""
+    yield
+    if "gpu" not in request.keywords:
+        return
+    from fms_b200.kernels import build
+
+    if build.DEBUG_BOUNDS and "expects_a_recorded_index" not in request.keywords:
+        assert build.bounds_violations() == []
