@@ -81,59 +81,90 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__
 }
 
 // Few rows (a decode step): the tiles above would be nearly empty and their loop, which waits for memory at every
-// step of 16 k, takes 20 times what the weights' bytes need.  Here a thread owns one column of y (one row of w) for
-// all rows of x, reads its row of w 16 bytes at a time with two batches of loads in flight, and takes x from shared
-// memory.  Every element is still one sequential fmaf chain over k = 0, 1, 2, ..., so the result is bit for bit the
-// tiled kernel's.
-constexpr int FEW_ROWS = 8, FEW_THREADS = 64, FEW_BATCH = 16;  // rows at most; columns a block; float4 a batch
+// step of 16 k, takes 20 times what the weights' bytes need.  Here a block owns 32 columns of y (32 rows of w) and a
+// thread one of them for 8 / MSPLIT of the rows of x (MSPLIT warps; 4 where the matrix has few rows and the
+// multiprocessors would else have too few warps, 2 where it has many).  The block brings its rows of w,
+// 64 k at a time, into shared memory by 16-byte asynchronous copies in which 16 lanes cover 256 contiguous bytes of
+// one row (four such stages a block, and up to five blocks a multiprocessor), and each thread then walks its
+// own row there.  Every element is still one sequential fmaf chain over k = 0, 1, 2, ..., so the result is bit for
+// bit the tiled kernel's.  (A thread that read its row of w straight from global memory, 16 bytes a lane and a row
+// apart from its neighbour's, got 0.7 TB/s out of the memory system.)
+constexpr int FEW_ROWS = 8, FEW_WROWS = 32, FEW_KT = 64, FEW_STAGES = 4, FEW_PAD = 4;
+constexpr int FEW_WSTRIDE = FEW_KT + FEW_PAD, FEW_STAGE_FLOATS = FEW_WROWS * FEW_WSTRIDE + FEW_ROWS * FEW_KT;
+constexpr size_t FEW_SMEM = (size_t)FEW_STAGES * FEW_STAGE_FLOATS * sizeof(float);
 
-__global__ void __launch_bounds__(FEW_THREADS) gemm_f32_few_rows_kernel(const float* __restrict__ x,
+__device__ __forceinline__ void few_copy16(void* smem, const void* gmem, bool valid) {
+  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;  // 0: the destination is filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(bytes) : "memory");
+}
+
+template <int FEW_MSPLIT>
+__global__ void __launch_bounds__(FEW_WROWS * FEW_MSPLIT) gemm_f32_few_rows_kernel(const float* __restrict__ x,
                                                                         const float* __restrict__ w,
                                                                         const float* __restrict__ bias,
                                                                         float* __restrict__ y, int M, int N, int K) {
-  __shared__ float4 xs[FEW_ROWS][FEW_BATCH];
-  const int n = blockIdx.x * FEW_THREADS + threadIdx.x;
-  const int k4 = K / 4;  // K is a multiple of 4 here
-  const float4* wrow = reinterpret_cast<const float4*>(w + (size_t)min(n, N - 1) * K);
-  float acc[FEW_ROWS];
+  extern __shared__ __align__(16) float few_smem[];
+  constexpr int FEW_THREADS = FEW_WROWS * FEW_MSPLIT, FEW_MPT = FEW_ROWS / FEW_MSPLIT;
+  const int tid = threadIdx.x, row = tid % FEW_WROWS, m0 = (tid / FEW_WROWS) * FEW_MPT;
+  const int n0 = blockIdx.x * FEW_WROWS;
+  const int steps = (K + FEW_KT - 1) / FEW_KT;  // K is a multiple of 4 here
+
+  auto issue = [&](int step) {
+    if (step < steps) {
+      float* ws = few_smem + (size_t)(step % FEW_STAGES) * FEW_STAGE_FLOATS;
+      float* xs = ws + FEW_WROWS * FEW_WSTRIDE;
+      const int k0 = step * FEW_KT;
 #pragma unroll
-  for (int m = 0; m < FEW_ROWS; ++m) acc[m] = 0.f;
-  float4 cur[FEW_BATCH], nxt[FEW_BATCH];
+      for (int c = tid; c < FEW_WROWS * (FEW_KT / 4); c += FEW_THREADS) {
+        const int r = c / (FEW_KT / 4), piece = c % (FEW_KT / 4);
+        const int k = k0 + 4 * piece;
+        const int n = min(n0 + r, N - 1);  // rows beyond N repeat the last one; their results are not stored
+        few_copy16(ws + r * FEW_WSTRIDE + 4 * piece, w + (size_t)n * K + min(k, K - 4), k < K);
+      }
 #pragma unroll
-  for (int u = 0; u < FEW_BATCH; ++u) cur[u] = u < k4 ? wrow[u] : make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int k0 = 0; k0 < k4; k0 += FEW_BATCH) {
-#pragma unroll
-    for (int u = 0; u < FEW_BATCH; ++u)  // the next batch of this row of w, while this one is used
-      nxt[u] = k0 + FEW_BATCH + u < k4 ? wrow[k0 + FEW_BATCH + u] : make_float4(0.f, 0.f, 0.f, 0.f);
-    __syncthreads();  // the batch of x before this one has been used by everyone
-    for (int i = threadIdx.x; i < FEW_ROWS * FEW_BATCH; i += FEW_THREADS) {
-      const int m = i / FEW_BATCH, u = i % FEW_BATCH;
-      xs[m][u] = (m < M && k0 + u < k4) ? reinterpret_cast<const float4*>(x + (size_t)m * K)[k0 + u]
-                                        : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    __syncthreads();
-    const int live = min(FEW_BATCH, k4 - k0);  // beyond K nothing is added: a chain must not see extra terms
-#pragma unroll
-    for (int u = 0; u < FEW_BATCH; ++u) {
-      if (u >= live) break;
-      const float4 wv = cur[u];
-#pragma unroll
-      for (int m = 0; m < FEW_ROWS; ++m) {
-        const float4 xv = xs[m][u];
-        acc[m] = fmaf(xv.x, wv.x, acc[m]);
-        acc[m] = fmaf(xv.y, wv.y, acc[m]);
-        acc[m] = fmaf(xv.z, wv.z, acc[m]);
-        acc[m] = fmaf(xv.w, wv.w, acc[m]);
+      for (int c = tid; c < FEW_ROWS * (FEW_KT / 4); c += FEW_THREADS) {
+        const int m = c / (FEW_KT / 4), piece = c % (FEW_KT / 4);
+        const int k = k0 + 4 * piece;
+        few_copy16(xs + m * FEW_KT + 4 * piece, x + (size_t)min(m, M - 1) * K + min(k, K - 4), m < M && k < K);
       }
     }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");  // an empty group keeps the count of groups in step
+  };
+
+  float acc[FEW_MPT];
 #pragma unroll
-    for (int u = 0; u < FEW_BATCH; ++u) cur[u] = nxt[u];
+  for (int i = 0; i < FEW_MPT; ++i) acc[i] = 0.f;
+#pragma unroll
+  for (int s = 0; s < FEW_STAGES - 1; ++s) issue(s);
+  for (int step = 0; step < steps; ++step) {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(FEW_STAGES - 2) : "memory");  // this step's stage has arrived
+    __syncthreads();  // ... for every thread, and everyone is done with the stage that is filled next
+    issue(step + FEW_STAGES - 1);
+    const float* ws = few_smem + (size_t)(step % FEW_STAGES) * FEW_STAGE_FLOATS + row * FEW_WSTRIDE;
+    const float* xs = few_smem + (size_t)(step % FEW_STAGES) * FEW_STAGE_FLOATS + FEW_WROWS * FEW_WSTRIDE + m0 * FEW_KT;
+    const int live = min(FEW_KT / 4, (K - step * FEW_KT) / 4);  // beyond K nothing is added: a chain sees no extra terms
+    if (m0 < M) {  // a warp whose rows of x do not exist has nothing to add
+#pragma unroll 4
+      for (int u = 0; u < live; ++u) {
+        const float4 wv = *reinterpret_cast<const float4*>(ws + 4 * u);
+#pragma unroll
+        for (int i = 0; i < FEW_MPT; ++i) {
+          const float4 xv = *reinterpret_cast<const float4*>(xs + i * FEW_KT + 4 * u);
+          acc[i] = fmaf(xv.x, wv.x, acc[i]);
+          acc[i] = fmaf(xv.y, wv.y, acc[i]);
+          acc[i] = fmaf(xv.z, wv.z, acc[i]);
+          acc[i] = fmaf(xv.w, wv.w, acc[i]);
+        }
+      }
+    }
   }
+  const int n = n0 + row;
   if (n < N) {
     const float b = bias ? bias[n] : 0.f;
 #pragma unroll
-    for (int m = 0; m < FEW_ROWS; ++m)
-      if (m < M && FMS_IN((size_t)m * N + n, (size_t)M * N)) y[(size_t)m * N + n] = acc[m] + b;
+    for (int i = 0; i < FEW_MPT; ++i)
+      if (m0 + i < M && FMS_IN((size_t)(m0 + i) * N + n, (size_t)M * N)) y[(size_t)(m0 + i) * N + n] = acc[i] + b;
   }
 }
 }  // namespace
@@ -143,7 +174,19 @@ FMS_API int fms_gemm_f32(const float* x, const float* w, const float* bias, floa
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0) return fms_fail("gemm_f32: K %d", K);
   if (M <= FEW_ROWS && K % 4 == 0 && K >= 4) {
-    gemm_f32_few_rows_kernel<<<(N + FEW_THREADS - 1) / FEW_THREADS, FEW_THREADS, 0, stream>>>(x, w, bias, y, M, N, K);
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_f32_few_rows_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FEW_SMEM);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_f32_few_rows_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FEW_SMEM);
+      if (e != cudaSuccess) return fms_fail("gemm_f32: %zu bytes of shared memory refused: %s", FEW_SMEM, cudaGetErrorString(e));
+      configured = true;
+    }
+    const int blocks = (N + FEW_WROWS - 1) / FEW_WROWS;
+    if (blocks < 4 * 148)
+      gemm_f32_few_rows_kernel<4><<<blocks, FEW_WROWS * 4, FEW_SMEM, stream>>>(x, w, bias, y, M, N, K);
+    else
+      gemm_f32_few_rows_kernel<2><<<blocks, FEW_WROWS * 2, FEW_SMEM, stream>>>(x, w, bias, y, M, N, K);
     return fms_launch_status("gemm_f32");
   }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
