@@ -36,6 +36,7 @@ PLAIN_LIBRARIES = {
     "elementwise": ("elementwise.cu", []),
     "gemm_f32": ("gemm_f32.cu", []),
     "gemm_bf16_skinny": ("gemm_bf16_skinny.cu", []),
+    "gemm_bf16_mid": ("gemm_bf16_mid.cu", []),
     "gemm_bf16_tc": ("gemm_bf16_tc.cu", []),
     "sampling": ("sampling.cu", []),
 }

@@ -5,10 +5,13 @@ product only); every function launches on torch's current stream.  There is no C
 no fallback: a tensor on another device, a missing compiler or a failed build raises.
 
 Matrix products: float32 runs ``gemm_f32`` (FFMA, no tensor-core mode).  bfloat16 runs the weight-streaming
-``mma.sync`` kernel up to 8 rows (decode), the tcgen05 kernel from ``TENSOR_CORE_ROWS`` rows on (prefill; pairs of
-thread blocks on one tile, fused GLU epilogue), and in between, or when K is no multiple of 8, the library product
-(cuBLAS through ``torch.nn.functional.linear``), as the reference does for every linear layer
-(fms/modules/linear.py:119-156).
+``mma.sync`` kernel up to 8 rows (decode of few sequences), the tcgen05 kernel with the tokens on the
+instruction's rows from ``TENSOR_CORE_ROWS`` rows on (prefill; pairs of thread blocks on one tile, fused GLU
+epilogue), and in between, or when K is no multiple of 8, the library product (cuBLAS through
+``torch.nn.functional.linear``), as the reference does for every linear layer (fms/modules/linear.py:119-156).
+With ``FMS_B200_MID_GEMM=1``, 9 to ``MID_ROWS`` (256) rows take a tcgen05 kernel of this library instead, with the
+weights on the instruction's rows (clusters of blocks share a tile along K; GLU and projection + rotation + cache
+write in its epilogue); the library's product is still ahead of it there, so it is not the default.
 """
 from __future__ import annotations
 
@@ -34,6 +37,10 @@ _SIGNATURES = {
     "fms_glu_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "fms_qkv_rope_store_bf16_skinny": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P,
                                        _I, _I, _I, _P],
+    "fms_linear_bf16_mid": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
+    "fms_glu_bf16_mid": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
+    "fms_qkv_rope_store_bf16_mid": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P,
+                                    _I, _I, _I, _P],
     "fms_gemm_bf16_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "fms_glu_bf16_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "fms_argmax": [_P, _P, _I, _I, _P],
@@ -193,6 +200,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         _call("gemm_bf16_skinny", "fms_linear_bf16_skinny", _ptr(x), _ptr(weight), _ptr(bias), _ptr(y), _code(out_dtype),
               x.shape[0], weight.shape[0], weight.shape[1], _stream())
         return y
+    if _mid_fits(x, weight, bias):
+        y = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
+        _call("gemm_bf16_mid", "fms_linear_bf16_mid", _ptr(x), _ptr(weight), _ptr(bias), _ptr(y), _code(out_dtype),
+              x.shape[0], weight.shape[0], weight.shape[1], _ptr(error_flag(x.device)), _stream())
+        return y
     if _tensor_core_fits(x, weight, bias):
         return linear_tensor_core(x, weight, bias, out_dtype)
     if out_dtype == torch.float32:
@@ -205,6 +217,20 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 # rows from which the tcgen05 kernel is used instead of the library product (measured: at par or ahead from there on)
 TENSOR_CORE_ROWS = int(os.environ.get("FMS_B200_TC_ROWS", "1024"))
 USE_TENSOR_CORE_GEMM = os.environ.get("FMS_B200_TC_GEMM", "1") != "0"
+
+
+# The tcgen05 kernel with the weights on the instruction's rows, for SKINNY_ROWS + 1 to MID_ROWS rows.  Off unless
+# FMS_B200_MID_GEMM=1: measured at the 8B sizes it is at par with the library's product at 16 rows and 3 to 9 us a
+# product behind it at 64 (a decode step of batch 16: 3.96 against 3.86 ms; of batch 64: 6.34 against 5.61), and its
+# fused epilogues (three kernels a layer fewer) do not make that up.
+MID_ROWS = min(256, int(os.environ.get("FMS_B200_MID_ROWS", "256")))
+USE_MID_GEMM = os.environ.get("FMS_B200_MID_GEMM", "0") == "1"
+
+
+def _mid_fits(x, weight, bias) -> bool:
+    return (USE_MID_GEMM and SKINNY_ROWS < x.shape[0] <= MID_ROWS and weight.shape[1] % 8 == 0
+            and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and (bias is None or bias.dtype == torch.bfloat16))
 
 
 def _tensor_core_fits(x, weight, bias) -> bool:
@@ -248,6 +274,12 @@ def gated_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
         y = torch.empty((x.shape[0], hidden), dtype=torch.bfloat16, device=x.device)
         _call("gemm_bf16_skinny", "fms_glu_bf16_skinny", _ptr(x), _ptr(weight), _ptr(bias), _ptr(y), x.shape[0], hidden,
               weight.shape[1], int(activation), _stream())
+        return y
+    if _mid_fits(x, weight, bias):
+        _ptr(x), _ptr(weight)
+        y = torch.empty((x.shape[0], hidden), dtype=torch.bfloat16, device=x.device)
+        _call("gemm_bf16_mid", "fms_glu_bf16_mid", _ptr(x), _ptr(weight), _ptr(bias), _ptr(y), x.shape[0], hidden,
+              weight.shape[1], int(activation), _ptr(error_flag(x.device)), _stream())
         return y
     if _tensor_core_fits(x, weight, bias):
         return gated_linear_tensor_core(x, weight, bias, activation)
@@ -303,6 +335,16 @@ def qkv_rope_store(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
               view.block_tokens, n, weight.shape[1], nheads,
               kvheads, head_dim, 1 if writes_cache else 0, _ptr(error_flag(x.device)), batch.slots.shape[0],
               view.table.shape[0], view.keys.shape[0], _stream())
+        return q
+    if (FUSE_QKV_ROPE and _mid_fits(x, weight, bias) and head_dim % 2 == 0 and view.keys.dtype == torch.bfloat16
+            and weight.shape[0] == (nheads + 2 * kvheads) * head_dim):
+        n = x.shape[0]
+        q = torch.empty((n, nheads * head_dim), dtype=x.dtype, device=x.device)
+        _call("gemm_bf16_mid", "fms_qkv_rope_store_bf16_mid", _ptr(x), _ptr(weight), _ptr(bias), _ptr(q), _ptr(inv_freq),
+              _ptr(batch.positions), _ptr(getattr(batch, "position_ids", None)), _ptr(batch.token_seq), _ptr(batch.slots),
+              _ptr(view.keys), _ptr(view.values), _ptr(view.table), view.table.shape[1], view.block_tokens, n,
+              weight.shape[1], nheads, kvheads, head_dim, 1 if writes_cache else 0, _ptr(error_flag(x.device)),
+              batch.slots.shape[0], view.table.shape[0], view.keys.shape[0], _stream())
         return q
     return rope_store(linear(x, weight, bias), inv_freq, batch, view, nheads, kvheads, head_dim, writes_cache)
 

@@ -23,6 +23,15 @@ def ops():
     return o
 
 
+@pytest.fixture
+def own_product_for_some_rows(ops):
+    """Products of 9 to 256 rows through this library's own tcgen05 kernel (by default they take the library's)."""
+    saved = ops.USE_MID_GEMM
+    ops.USE_MID_GEMM = True
+    yield
+    ops.USE_MID_GEMM = saved
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("vocab,dim", [(331, 240), (17, 16), (1000, 4096 + 48)])
 def test_embed(ops, dtype, vocab, dim):
@@ -155,6 +164,45 @@ def test_gated_linear_few_rows(ops, m, hidden, k, act):
                                P.gated_activation(P.linear(x2, w, None, torch.float32), act), atol=3e-2, rtol=3e-2)
 
 
+@pytest.mark.parametrize("m", [9, 16, 17, 64, 100, 256])
+@pytest.mark.parametrize("n,k", [(331, 240), (130, 64), (4096 + 16, 1000), (4096, 4096), (1000, 8), (256, 14336 + 8)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_linear_bfloat16_some_rows(ops, own_product_for_some_rows, m, n, k, out_dtype):
+    """9 to 256 rows: the tcgen05 kernel with the weights on the instruction's rows.  Numbers of weight rows that are
+    no multiples of its tile, K that is no multiple of 64, few and many steps of K (one block a tile, or clusters of
+    2, 4 and 8 that add their sums), with and without bias."""
+    g = torch.Generator().manual_seed(70 + m)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(n, k, generator=g) * (0.05 if k < 5000 else 0.01)).to(torch.bfloat16).cuda()
+    b = torch.randn(n, generator=g).to(torch.bfloat16).cuda()
+    for bias in (None, b):
+        got = ops.linear(x, w, bias, out_dtype)
+        want = P.linear(x, w, bias, torch.float64)
+        assert got.dtype == out_dtype and got.shape == (m, n)
+        t = dict(atol=2e-2, rtol=2e-2) if out_dtype == torch.bfloat16 else dict(atol=1e-3, rtol=1e-3)
+        torch.testing.assert_close(got.double(), want, **t)
+    ops.check_error_flag("cuda")
+    # a row's result does not depend on how many other rows there are
+    fewer = ops.linear(x[:9].contiguous(), w, None, out_dtype)
+    assert torch.equal(fewer, ops.linear(x, w, None, out_dtype)[:9])
+
+
+@pytest.mark.parametrize("m", [9, 40, 256])
+@pytest.mark.parametrize("hidden,k", [(176, 64), (328, 240), (1000, 96), (14336, 128), (331, 384), (5, 1024), (64, 4096)])
+@pytest.mark.parametrize("act", [0, 2])
+def test_gated_linear_some_rows(ops, own_product_for_some_rows, m, hidden, k, act):
+    g = torch.Generator().manual_seed(80 + m)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(2 * hidden, k, generator=g) * 0.1).to(torch.bfloat16).cuda()
+    b = (torch.randn(2 * hidden, generator=g) * 0.3).to(torch.bfloat16).cuda()
+    for bias in (None, b):
+        got = ops.gated_linear(x, w, bias, act)
+        want = P.gated_activation(P.linear(x, w, bias, torch.float32), act)
+        assert got.dtype == torch.bfloat16 and got.shape == (m, hidden)
+        torch.testing.assert_close(got.float(), want, atol=3e-2, rtol=2e-2)
+    ops.check_error_flag("cuda")
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 512, 256), (129, 331, 200), (1000, 777, 1000), (2048, 1024, 4096),
                                    (257, 4096 + 32, 72), (1024, 96, 4096), (640, 6144, 520), (100, 700, 136)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
@@ -268,11 +316,18 @@ def test_rope_store(ops, dtype, nheads, kvheads, hd):
     (3, 1, 32, [0, 63], [3, 2]),              # short prompts and a continuation across a block's edge
     (5, 5, 48, [130], [8]),                   # eight tokens of one sequence, odd head size
     (32, 8, 128, [100, 200, 300, 5, 64, 63, 1, 0], [1] * 8),  # the benchmark's head layout, batch 8
+    # more than 8 rows: the tcgen05 kernel with the weights on the instruction's rows has the same epilogue
+    (4, 2, 16, [70, 0, 5, 64, 63, 200, 1, 9, 10], [1] * 9),   # a decode step of nine
+    (3, 1, 32, [0, 63], [30, 2]),                             # a short prompt and a continuation across a block's edge
+    (5, 5, 48, [130], [100]),                                 # odd head size: tiles of 128 rows cut through heads
+    (32, 8, 128, [100 + 7 * i for i in range(64)], [1] * 64), # the benchmark's head layout, batch 64
+    (7, 1, 80, [5, 0], [120, 136]),                           # 256 rows
 ])
 @pytest.mark.parametrize("with_bias", [False, True])
-def test_projection_rotation_and_cache_write_in_one_kernel(ops, nheads, kvheads, hd, lens_before, num_new, with_bias):
-    """Up to 8 bfloat16 rows: the weight-streaming product rotates q and k and writes k and v into the cache in its
-    epilogue.  Against the plain product followed by the plain rotation and cache write (which round the product
+def test_projection_rotation_and_cache_write_in_one_kernel(ops, own_product_for_some_rows, nheads, kvheads, hd, lens_before,
+                                                           num_new, with_bias):
+    """Up to 256 bfloat16 rows: the product (weight-streaming mma.sync up to 8 rows, tcgen05 from 9 on) rotates q and
+    k and writes k and v into the cache in its epilogue.  Against the plain product followed by the plain rotation and cache write (which round the product
     to bfloat16 in between; the fused kernel rotates the float32 sums)."""
     dtype, k = torch.bfloat16, 8 * 21
     cache, view, batch = make_cache_case(dtype, nheads, kvheads, hd, lens_before, num_new, 23)
