@@ -337,15 +337,36 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, float* __r
   }
 }
 
+// One block per (sequence, head), one thread per value of the head.  Everything the block reads is asked for at
+// once, before anything is known: the length, the (maximum, sum) pairs of all splits the launch is sized for, and
+// the partial outputs of the first COMBINE_EARLY splits.  What belongs to splits without keys was never written
+// and is never used (selected away, not multiplied by zero).  So the kernel costs one trip to memory, not three in
+// a row (length, then pairs, then outputs).  The sums run over the live splits in ascending order.
+constexpr int COMBINE_EARLY = 8, COMBINE_MAX_SPLITS = 128;
+
 template <typename T>
 __global__ void attn_combine_kernel(AttnArgs a, const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     int n_splits, int* __restrict__ reset = nullptr, int* __restrict__ error_flag = nullptr) {
+  __shared__ float2 sml[COMBINE_MAX_SPLITS];
   pdl_launch_dependents();
   pdl_wait();
   // the kernel before this one is done: its work counter (if it has one) is put back for the next launch
   if (reset != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *reset = 0;
-  const int seq = blockIdx.x, head = blockIdx.y;
+  const int seq = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+  const float* ml = part_ml + ((size_t)seq * a.nheads + head) * n_splits * 2;
+  const float* po = part_o + ((size_t)seq * a.nheads + head) * n_splits * HD;
+  const bool staged = n_splits <= COMBINE_MAX_SPLITS;
   const int len = a.len_after[seq];
+  const int row0 = a.first_row[seq];
+  float2 mine = make_float2(0.f, 0.f);
+  if (staged)
+    for (int i = d; i < n_splits; i += HD) {
+      mine = reinterpret_cast<const float2*>(ml)[i];
+      sml[i] = mine;
+    }
+  float early[COMBINE_EARLY];
+#pragma unroll
+  for (int i = 0; i < COMBINE_EARLY; ++i) early[i] = i < n_splits ? po[(size_t)i * HD + d] : 0.f;
   const int pos = len - 1;
   const int kstart = a.window > 0 ? max(0, pos - a.window + 1) : 0;
   int s_lo = kstart / SPLIT, s_hi = pos / SPLIT;
@@ -356,19 +377,20 @@ __global__ void attn_combine_kernel(AttnArgs a, const float* __restrict__ part_o
     s_hi = n_splits - 1;
     s_lo = min(s_lo, s_hi);
   }
-  const float* ml = part_ml + ((size_t)seq * a.nheads + head) * n_splits * 2;
-  const float* po = part_o + ((size_t)seq * a.nheads + head) * n_splits * HD;
+  __syncthreads();
+  auto pair_of = [&](int s) { return staged ? sml[s] : make_float2(ml[2 * s], ml[2 * s + 1]); };
   float m = -INFINITY;
-  for (int s = s_lo; s <= s_hi; ++s) m = fmaxf(m, ml[2 * s]);
+  for (int s = s_lo; s <= s_hi; ++s) m = fmaxf(m, pair_of(s).x);
   float total = 0.f;
-  for (int s = s_lo; s <= s_hi; ++s) total += ml[2 * s + 1] * expf(ml[2 * s] - m);
+  for (int s = s_lo; s <= s_hi; ++s) total += pair_of(s).y * expf(pair_of(s).x - m);
   const float inv = total > 0.f ? 1.f / total : 0.f;
-  T* o = (T*)a.out + (size_t)a.first_row[seq] * a.nheads * HD + (size_t)head * HD;
-  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-    float sum = 0.f;
-    for (int s = s_lo; s <= s_hi; ++s) sum += po[(size_t)s * HD + d] * expf(ml[2 * s] - m);
-    o[d] = from_f32<T>(sum * inv);
-  }
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < COMBINE_EARLY; ++i)
+    if (i >= s_lo && i <= s_hi) sum += early[i] * expf(pair_of(i).x - m);
+  for (int s = max(s_lo, COMBINE_EARLY); s <= s_hi; ++s) sum += po[(size_t)s * HD + d] * expf(pair_of(s).x - m);
+  T* o = (T*)a.out + (size_t)row0 * a.nheads * HD + (size_t)head * HD;
+  o[d] = from_f32<T>(sum * inv);
 }
 
 #include "attention_mma.cuh"
@@ -435,7 +457,7 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
     const int chunks = (group + GC - 1) / GC;
     fms_launch(attn_decode_kernel<float>, dim3(n_seqs, a.kvheads * chunks, n_splits), dim3(128), 0, stream, a, part_o,
                part_ml, n_splits);
-    fms_launch(attn_combine_kernel<float>, dim3(n_seqs, a.nheads), dim3(HD >= 128 ? 128 : 64), 0, stream, a,
+    fms_launch(attn_combine_kernel<float>, dim3(n_seqs, a.nheads), dim3(HD), 0, stream, a,
                (const float*)part_o, (const float*)part_ml, n_splits, (int*)nullptr, error_flag);
   } else if (dtype == FMS_BF16) {
     // Few (sequence, kv head) pairs: four warps share a split, each with one block of 64 keys in flight, which
@@ -464,7 +486,7 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
       ++g_stream_launches;
       fms_launch(attn_decode_stream_kernel, dim3(blocks), dim3((SR_WARPS + 1) * 32), SR_SMEM, stream, map_k, map_v, a,
                  part_o, part_ml, n_seqs, n_splits, work_counter, error_flag);
-      fms_launch(attn_combine_kernel<__nv_bfloat16>, dim3(n_seqs, a.nheads), dim3(HD >= 128 ? 128 : 64), 0, stream, a,
+      fms_launch(attn_combine_kernel<__nv_bfloat16>, dim3(n_seqs, a.nheads), dim3(HD), 0, stream, a,
                  (const float*)part_o, (const float*)part_ml, n_splits, work_counter, error_flag);
       return fms_launch_status(what);
     }
@@ -483,7 +505,7 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
     fms_launch(kernel, dim3(n_seqs, a.kvheads * chunks, n_splits), dim3(nw * 32), smem, stream, a, part_o, part_ml,
                n_splits, nw == 4 ? pool_blocks : 0);
     if (n_splits > 1)  // with one split the kernel above has written the result itself
-      fms_launch(attn_combine_kernel<__nv_bfloat16>, dim3(n_seqs, a.nheads), dim3(HD >= 128 ? 128 : 64), 0, stream, a,
+      fms_launch(attn_combine_kernel<__nv_bfloat16>, dim3(n_seqs, a.nheads), dim3(HD), 0, stream, a,
                  (const float*)part_o, (const float*)part_ml, n_splits, (int*)nullptr, error_flag);
   } else {
     return fms_fail("%s: unsupported dtype code %d", what, dtype);

@@ -142,13 +142,15 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
   pdl_wait();
   const int g0 = chunk * GROWS;
   const int ng = min(GROWS, group - g0);
+  // the three values every block needs, asked for together: none of them waits for another
   const int len = a.len_after[seq];
+  const int slot = a.slots[seq];
+  const int first_row = a.first_row[seq];
   const int pos = len - 1;
   const int kstart = a.window > 0 ? max(0, pos - a.window + 1) : 0;
   const int k_lo = max(kstart, split * SPLIT), k_hi = min(len, (split + 1) * SPLIT);
   if (k_lo >= k_hi) return;
-  const int slot = a.slots[seq];
-  const __nv_bfloat16* q = (const __nv_bfloat16*)a.q + (size_t)a.first_row[seq] * a.nheads * HD +
+  const __nv_bfloat16* q = (const __nv_bfloat16*)a.q + (size_t)first_row * a.nheads * HD +
                            (size_t)(kvh * group + g0) * HD;
   const __nv_bfloat16* kc = (const __nv_bfloat16*)a.keys;
   const __nv_bfloat16* vc = (const __nv_bfloat16*)a.values;
