@@ -51,7 +51,7 @@ class Decoder(Part):
 
     def kernel_libraries(self, dtype):
         head = ["gemm_f32"] if dtype == torch.float32 or self.head_weight().dtype == torch.float32 else \
-            ["gemm_bf16_skinny", "gemm_bf16_mid", "gemm_bf16_tc"]
+            ["gemm_bf16_skinny", "gemm_bf16_tc"] + (["gemm_bf16_mid"] if ops.USE_MID_GEMM else [])
         return ["elementwise"] + head + super().kernel_libraries(dtype)
 
     def head_weight(self):

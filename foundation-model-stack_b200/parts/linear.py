@@ -24,4 +24,4 @@ class Linear(Part):
         w = self.tensor("weight")
         if dtype == torch.float32 or (w is not None and w.dtype == torch.float32):
             return ["gemm_f32"]
-        return ["gemm_bf16_skinny", "gemm_bf16_mid", "gemm_bf16_tc"]
+        return ["gemm_bf16_skinny", "gemm_bf16_tc"] + (["gemm_bf16_mid"] if ops.USE_MID_GEMM else [])
