@@ -84,6 +84,11 @@ def _tokens_of_padded_rows(input_ids: torch.Tensor, position_ids: torch.Tensor):
     return spans
 
 
+def _first_positions_of_padded_rows(position_ids: torch.Tensor) -> List[int]:
+    """The position of each row's first token: the smallest position of the row (padding stays at it)."""
+    return [int(min(row)) for row in position_ids.tolist()]
+
+
 def plan_batches(lengths: Sequence[int], max_new_tokens: int, batch_size: Optional[int], cache_tokens: int,
                  max_slots: int, block_tokens: int = 64) -> List[List[int]]:
     """Cuts request numbers 0..n-1 into batches, in order: at most ``batch_size`` (and ``max_slots``)
@@ -110,15 +115,16 @@ def plan_batches(lengths: Sequence[int], max_new_tokens: int, batch_size: Option
 
 def generate_batch(engine, sampler: Sampler, prompts: Sequence[Sequence[int]], requests: Sequence[int],
                    max_new_tokens: int, stop_tokens: Sequence[int] = (),
-                   post_iteration_hook: Optional[Callable] = None, times: Optional[List[float]] = None
-                   ) -> List[List[int]]:
+                   post_iteration_hook: Optional[Callable] = None, times: Optional[List[float]] = None,
+                   first_positions: Optional[Sequence[int]] = None) -> List[List[int]]:
     """One batch of sequences that start together: the prompts in one step, then one token each until
     every sequence has met a stop token or has ``max_new_tokens`` new tokens.  ``engine`` needs ``begin``,
-    ``step``, ``release`` and ``device``."""
+    ``step``, ``release`` and ``device``.  ``first_positions``: the position of each prompt's first token where
+    that is not 0 (the reference's ``position_ids``, fms/utils/generation.py:122-132)."""
     n = len(prompts)
     stop = set(int(t) for t in stop_tokens)
     outputs = [list(p) for p in prompts]
-    slots = engine.begin(n)
+    slots = engine.begin(n, list(first_positions)) if first_positions is not None and any(first_positions) else engine.begin(n)
     held = set(slots)
     horizon = max(len(p) for p in prompts) + max_new_tokens
     try:
@@ -176,7 +182,8 @@ def generate(model, input_ids: Prompts, max_seq_len: int = 4096, max_new_tokens:
     prepare_model_inputs_hook, extra_kwargs: the reference passes these into its model's forward
         (fms/utils/generation.py:246-252).  The engine builds its own inputs, so a hook is refused, and of
         ``extra_kwargs`` only what ``pad_input_ids`` returned is taken (``position_ids``, ``mask``), with a
-        2-D ``input_ids``: each row then runs without its padding, and comes back with it.
+        2-D ``input_ids``: each row then runs without its padding, from the position its ``position_ids`` start
+        at (``position_ids_offset``), and comes back with its padding.
     eos_token_id: one stop token or several; a sequence ends with its stop token.
     timing: "" | "per-token" | "e2e": also return the seconds of each step, or of the whole call.
     post_iteration_hook(step, logits, tokens, requests): called after every step of a batch.
@@ -200,16 +207,19 @@ def generate(model, input_ids: Prompts, max_seq_len: int = 4096, max_new_tokens:
     if timing not in ("", "per-token", "e2e"):
         raise ValueError('timing must be "", "per-token" or "e2e"')
     prompts, kind = _as_lists(input_ids)
-    padded_rows = None
+    padded_rows, first_positions = None, None
     if extra:
         if kind != "2d" or "position_ids" not in extra:
             raise ValueError("extra_kwargs of pad_input_ids go with its 2-D input_ids and need position_ids")
         padded_rows = prompts
         spans = _tokens_of_padded_rows(input_ids, torch.as_tensor(extra["position_ids"]))
+        first_positions = _first_positions_of_padded_rows(torch.as_tensor(extra["position_ids"]))
         prompts = [row[a:b] for row, (a, b) in zip(prompts, spans)]
     if not prompts or any(len(p) == 0 for p in prompts):
         raise ValueError("every prompt needs at least one token")
     given = [len(p) for p in prompts]
+    if first_positions is not None:  # a prompt that is cut to its last max_seq_len tokens starts that much later
+        first_positions = [f + max(0, len(p) - max_seq_len) for f, p in zip(first_positions, prompts)]
     prompts = [p[-max_seq_len:] for p in prompts]
     stop = [] if eos_token_id is None else ([int(eos_token_id)] if isinstance(eos_token_id, int) else list(eos_token_id))
     sampler = Sampler(do_sample, temperature, top_k, seed)
@@ -225,15 +235,17 @@ def generate(model, input_ids: Prompts, max_seq_len: int = 4096, max_new_tokens:
     max_slots = cache.max_slots if cache is not None else len(prompts)
     limit = cache.max_positions if cache is not None else 1 << 60
     for i, p in enumerate(prompts):
-        if len(p) + max_new_tokens > limit:
-            raise ValueError(f"prompt {i}: {len(p)} + {max_new_tokens} tokens exceed the model's {limit} positions")
+        first = first_positions[i] if first_positions is not None else 0
+        if first + len(p) + max_new_tokens > limit:
+            raise ValueError(f"prompt {i}: {first + len(p)} + {max_new_tokens} tokens exceed the model's {limit} positions")
 
     times: List[float] = []
     start = time.perf_counter()
     results: List[Optional[List[int]]] = [None] * len(prompts)
     for batch in plan_batches([len(p) for p in prompts], max_new_tokens, batch_size, capacity, max_slots):
         outs = generate_batch(engine, sampler, [prompts[i] for i in batch], batch, max_new_tokens, stop,
-                              post_iteration_hook, times if timing == "per-token" else None)
+                              post_iteration_hook, times if timing == "per-token" else None,
+                              [first_positions[i] for i in batch] if first_positions is not None else None)
         for i, o in zip(batch, outs):
             results[i] = o
     if timing == "e2e":

@@ -276,12 +276,13 @@ def plain_sample(logits: torch.Tensor, temperature: float, top_k: int, u: float)
 
 def plain_generate(model: PlainLlama, prompt: Sequence[int], max_new_tokens: int, do_sample: bool = False,
                    temperature: float = 1.0, top_k: int = 0, seed: int = 0, request: int = 0,
-                   eos: Optional[Sequence[int]] = None, logits_out: Optional[List[torch.Tensor]] = None) -> List[int]:
+                   eos: Optional[Sequence[int]] = None, logits_out: Optional[List[torch.Tensor]] = None,
+                   first_position: int = 0) -> List[int]:
     """Recomputes the whole sequence for every new token (the reference's loop without a cache,
     fms/utils/generation.py:287-346); stops after a stop token."""
     ids = list(prompt)
     for step in range(max_new_tokens):
-        lg = model.logits(ids)[-1]
+        lg = model.logits(ids, first_position=first_position)[-1]
         if logits_out is not None:
             logits_out.append(lg)
         if do_sample:

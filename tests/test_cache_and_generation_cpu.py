@@ -148,8 +148,9 @@ class CountingEngine:
         self.steps = []  # (kind, number of sequences)
         self.released = []
 
-    def begin(self, n):
+    def begin(self, n, first_positions=None):
         assert n <= len(self.free)
+        self.first_positions = first_positions
         out = [self.free.pop(0) for _ in range(n)]
         return out
 
@@ -276,9 +277,10 @@ def test_padded_rectangle_runs_without_its_padding_and_comes_back_with_it(greedy
     assert ids.tolist() == [[4, 7, 7], [1, 2, 3], [9, 10, 7]]
     assert extra["position_ids"].tolist() == [[2, 2, 2], [2, 3, 4], [2, 3, 2]]
     assert (extra["mask"][2] == 0).tolist() == [[True, True, False], [True, True, False], [False, False, True]]
-    out = generate(CountingEngine(), ids[1:], max_new_tokens=2, do_sample=False,
-                   extra_kwargs={k: v[1:] for k, v in extra.items()})
+    e = CountingEngine()
+    out = generate(e, ids[1:], max_new_tokens=2, do_sample=False, extra_kwargs={k: v[1:] for k, v in extra.items()})
     assert out.tolist() == [[1, 2, 3, 4, 5], [9, 10, 7, 11, 12]]
+    assert e.first_positions == [2, 2]  # the sequences start at the offset
 
     with pytest.raises(ValueError):  # the mapping belongs to the rectangle it was made with
         generate(CountingEngine(), prompts, max_new_tokens=1, do_sample=False, extra_kwargs=extra)

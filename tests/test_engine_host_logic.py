@@ -128,3 +128,19 @@ def test_a_sequence_that_starts_at_another_position(tiny_folders):
     rows = torch.cat([got[0].view(2, 30, -1)] + [g.view(2, 1, -1) for g in got[1:]], 1).double()
     torch.testing.assert_close(rows[0], oracle.logits(prompt), atol=2e-5, rtol=1e-4)
     torch.testing.assert_close(rows[1], oracle.logits(prompt, first_position=77), atol=2e-5, rtol=1e-4)
+
+
+def test_generate_honours_the_offset_of_padded_position_ids(tiny_folders):
+    """``pad_input_ids(..., position_ids_offset=k)`` makes every prompt start at position k
+    (fms/utils/generation.py:16-109); the engine starts the sequences there."""
+    from fms_b200.utils.generation import generate, pad_input_ids, trim_prefix
+
+    oracle = pl.PlainLlama(tiny_folders["e"])
+    prompts = [p for p in tiny_prompts("e")[:2]]
+    with use_plain_ops():
+        model = _model(tiny_folders["e"])
+        ids, extra = pad_input_ids([torch.tensor(p) for p in prompts], position_ids_offset=9, pad_token_id=172)
+        out = generate(model.new_engine(max_tokens=512), ids, max_new_tokens=4, do_sample=False, extra_kwargs=extra)
+    for row, p in zip(out, prompts):
+        got = row.tolist()[ids.shape[1] - len(p):]
+        assert got == pl.plain_generate(oracle, p, 4, first_position=9)
