@@ -25,7 +25,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--model_path", type=str, default=None,
                    help="Folder (or file, or glob) of safetensors; with a config.json the configuration is read "
                         "from it.  Without it the weights are random.")
-    p.add_argument("--model_source", type=str, default=None, help="Naming of the checkpoint: hf or fms")
+    p.add_argument("--model_source", type=str, default=None, help="Naming of the checkpoint: hf, meta or fms")
     p.add_argument("--tokenizer", type=str, default=None,
                    help='"char_tokenizer" or a folder with a tokenizer.json; without one give --prompt_ids')
     p.add_argument("--default_dtype", type=str, default=None, choices=["bf16", "fp32"],

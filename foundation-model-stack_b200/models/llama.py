@@ -300,8 +300,43 @@ def _weight_fusion(tensors: Dict[str, torch.Tensor], **kw) -> Dict[str, torch.Te
     return _fuse(out, ["ff_sub_layer.wg", "ff_sub_layer.w1"], "ff_sub_layer.wg1_fused")
 
 
+_META_TO_ENGINE = [  # fms/models/llama.py:618-645: the names of Meta's own checkpoints
+    (r"^tok_embeddings", "base_model.embedding"),
+    (r"^norm", "base_model.dec_norm"),
+    (r"^output", "head"),
+    (r"^layers", "base_model.layers"),
+    (r"\.attention\.", ".attn."),
+    (r"attn\.wq", "attn.in_proj.query"),
+    (r"attn\.wk", "attn.in_proj.key"),
+    (r"attn\.wv", "attn.in_proj.value"),
+    (r"attn\.wo", "attn.dense"),
+    (r"attention_norm", "ln"),
+    (r"feed_forward\.w1", "ff_sub_layer.wg"),
+    (r"feed_forward\.w2", "ff_sub_layer.w2"),
+    (r"feed_forward\.w3", "ff_sub_layer.w1"),
+    (r"ffn_norm", "ff_ln"),
+]
+
+
+def _meta_to_engine_names(tensors: Dict[str, torch.Tensor], config: LLaMAConfig = None, **_) -> Dict[str, torch.Tensor]:
+    """Meta's names; their q and k rows already lie as adjacent rotary pairs, so no rows are moved."""
+    out = {}
+    for name, t in tensors.items():
+        if name == "rope.freqs":
+            continue  # a table; the frequencies are computed from the configuration
+        if config is not None and config.tie_heads and name == "output.weight":
+            continue
+        new = name
+        for pattern, repl in _META_TO_ENGINE:
+            new = re.sub(pattern, repl, new)
+        out[new] = t
+    return out
+
+
+register_adapter_step("llama", "meta_to_fms_names", _meta_to_engine_names)
 register_adapter_step("llama", "hf_to_fms_names", _hf_to_engine_names)
 register_adapter_step("llama", "hf_to_fms_rope", _hf_rope_rows_to_interleaved)
 register_adapter_step("llama", "weight_fusion", _weight_fusion)
 register_adapter("llama", "hf", ["hf_to_fms_names", "hf_to_fms_rope", "weight_fusion"])
+register_adapter("llama", "meta", ["meta_to_fms_names", "weight_fusion"])
 register_adapter("llama", "fms", ["weight_fusion"])

@@ -110,10 +110,51 @@ class JsonTokenizer(BaseTokenizer):
         return self._tok.get_vocab_size()
 
 
+class SentencePieceTokenizer(BaseTokenizer):
+    """A sentencepiece ``.model`` file, as the reference reads Meta's tokenizers (fms/utils/tokenizers.py:146-203)."""
+
+    def __init__(self, path: str) -> None:
+        from sentencepiece import SentencePieceProcessor  # optional dependency
+
+        self._sp = SentencePieceProcessor(model_file=path)
+        super().__init__(self._sp.bos_id(), self._sp.eos_id())
+
+    def tokenize(self, text: str) -> List[str]:
+        return self._sp.encode_as_pieces(text)
+
+    def convert_tokens_to_ids(self, tokens):
+        return self._sp.piece_to_id(tokens)
+
+    def convert_ids_to_tokens(self, ids) -> List[str]:
+        return self._sp.id_to_piece([int(i) for i in ids])
+
+    def convert_tokens_to_string(self, tokens: List[str]) -> str:
+        return self._sp.decode_pieces(list(tokens))
+
+    def encode(self, text: str, add_special_tokens: bool = False) -> List[int]:
+        ids = self._sp.encode(text)
+        return [self.bos_token_id] + ids if add_special_tokens and self.bos_token_id >= 0 else ids
+
+    def decode(self, ids, skip_special_tokens: bool = True) -> str:
+        return self._sp.decode([int(i) for i in ids])
+
+    def vocab_size(self) -> int:
+        return self._sp.vocab_size()
+
+
 def get_tokenizer(name: str) -> BaseTokenizer:
+    """"char_tokenizer", a sentencepiece ``.model`` file, a ``tokenizer.json`` or a folder that holds one of the two
+    (fms/utils/tokenizers.py:459-502)."""
     if name == "char_tokenizer":
         return CharTokenizer()
-    path = os.path.join(name, "tokenizer.json") if os.path.isdir(name) else name
-    if os.path.isfile(path) and path.endswith(".json"):
-        return JsonTokenizer(path)
-    raise ValueError(f'no tokenizer at {name!r}: give "char_tokenizer" or a folder with a tokenizer.json')
+    if os.path.isdir(name):
+        for candidate in ("tokenizer.json", "tokenizer.model"):
+            if os.path.isfile(os.path.join(name, candidate)):
+                name = os.path.join(name, candidate)
+                break
+    if os.path.isfile(name) and name.endswith(".json"):
+        return JsonTokenizer(name)
+    if os.path.isfile(name) and name.endswith(".model"):
+        return SentencePieceTokenizer(name)
+    raise ValueError(f'no tokenizer at {name!r}: give "char_tokenizer", a sentencepiece .model file, a tokenizer.json or '
+                     "a folder with one of them")

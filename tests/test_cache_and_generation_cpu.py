@@ -433,3 +433,22 @@ def test_sequences_that_start_at_other_positions_keep_length_and_position_apart(
     assert cache.offset(c) == 0  # nothing of the old offset is left in a slot that is used again
     with pytest.raises(ValueError):
         cache.begin(1, [-1])
+
+
+def test_sentencepiece_model_file(tmp_path):
+    sentencepiece = pytest.importorskip("sentencepiece")
+    from fms_b200.utils.tokenizers import get_tokenizer
+
+    corpus = tmp_path / "corpus.txt"
+    corpus.write_text("\n".join(["the quick brown fox jumps over the lazy dog", "a small whole engine for one gpu",
+                                 "keys and values in blocks of sixty four tokens"] * 20))
+    sentencepiece.SentencePieceTrainer.train(input=str(corpus), model_prefix=str(tmp_path / "tokenizer"), vocab_size=60,
+                                             model_type="bpe", bos_id=1, eos_id=2, unk_id=0)
+    for where in (str(tmp_path / "tokenizer.model"), str(tmp_path)):
+        tok = get_tokenizer(where)
+        assert (tok.bos_token_id, tok.eos_token_id) == (1, 2) and tok.vocab_size() == 60
+        ids = tok.encode("the lazy fox", add_special_tokens=True)
+        assert ids[0] == 1 and tok.decode(ids[1:]) == "the lazy fox"
+        pieces = tok.tokenize("the lazy fox")
+        assert tok.convert_tokens_to_ids(pieces) == ids[1:] and tok.convert_tokens_to_string(pieces) == "the lazy fox"
+        assert tok.convert_ids_to_tokens(ids[1:]) == pieces

@@ -339,3 +339,31 @@ def test_the_references_own_initialisation():
     assert abs(sd["head.weight"].std().item() - (d * v) ** -0.25) < 0.1 * (d * v) ** -0.25
     with pytest.raises(ValueError):
         get_model("llama", "micro", device_type="cpu", init="no_such_init")
+
+
+def test_meta_named_checkpoint_loads_like_the_hf_one(tmp_path, tiny_folders):
+    """fms/models/llama.py:618-645: Meta's own names (tok_embeddings, layers.N.attention.wq, feed_forward.w1/w3/w2,
+    attention_norm, ffn_norm, norm, output); their q and k rows are adjacent rotary pairs already."""
+    import plain_llama as pl
+    from fms_b200.models import get_model
+    from fms_b200.weights import list_sources
+
+    assert "meta" in list_sources("llama")
+    cfg, seed, gain_dtype = TINY["a"]
+    hf = tiny_tensors(cfg, seed, gain_dtype)
+    hd = cfg["hidden_size"] // cfg["num_attention_heads"]
+    meta = {"tok_embeddings.weight": hf["model.embed_tokens.weight"], "norm.weight": hf["model.norm.weight"],
+            "output.weight": hf["lm_head.weight"], "rope.freqs": torch.zeros(hd // 2)}
+    names = {"self_attn.q_proj": "attention.wq", "self_attn.k_proj": "attention.wk", "self_attn.v_proj": "attention.wv",
+             "self_attn.o_proj": "attention.wo", "mlp.gate_proj": "feed_forward.w1", "mlp.up_proj": "feed_forward.w3",
+             "mlp.down_proj": "feed_forward.w2", "input_layernorm": "attention_norm", "post_attention_layernorm": "ffn_norm"}
+    for i in range(cfg["num_hidden_layers"]):
+        for h_name, m_name in names.items():
+            t = hf[f"model.layers.{i}.{h_name}.weight"]
+            if h_name in ("self_attn.q_proj", "self_attn.k_proj"):
+                t = pl.hf_rows_to_interleaved(t, hd)  # the layout Meta's checkpoints have
+            meta[f"layers.{i}.{m_name}.weight"] = t
+    folder = write_folder(str(tmp_path / "meta"), cfg, meta)
+    a = get_model("llama", model_path=tiny_folders["a"], source="hf", device_type="cpu", data_type="bf16").state_dict()
+    b = get_model("llama", model_path=folder, source="meta", device_type="cpu", data_type="bf16").state_dict()
+    assert sorted(a) == sorted(b) and all(torch.equal(a[k], b[k]) for k in a)
