@@ -3,6 +3,9 @@
 // the WEIGHTS fill the instruction's 128 rows and the tokens are its columns (16 to 256): a step of this size is
 // bound by reading w once, and nothing of the instruction is wasted on padding rows.
 //
+// Of the products of a layer the library hands the gated feed-forward one to this kernel by default (9 to 64 rows),
+// where it is ahead of the library's product plus an activation kernel; the others it can take on request.
+//
 // A thread block owns 128 rows of w (one tile) for a slice of K; the KS blocks that share a tile (KS = 1, 2, 4
 // or 8, chosen from the matrix's shape alone so that two blocks a multiprocessor are there to stream) form a thread
 // block CLUSTER and add their partial sums through distributed shared memory, in a fixed order, before the epilogue:
@@ -331,8 +334,8 @@ int launch_mid(const char* what, const void* x, const void* w, MidArgs p, int M,
   if (tiles > 65535) return fms_fail("%s: %d tiles of rows of w", what, tiles);
   p.ks = choose_ks(tiles, K);
   const int stage_bytes = W_BYTES + p.n_tokens * TILE_K * 2;
-  // three blocks a multiprocessor where the stages are small, two or one where the tokens are many
-  int budget = p.n_tokens <= 32 ? 70 : (p.n_tokens <= 128 ? 104 : 200);
+  // two blocks a multiprocessor, one where the tokens are many
+  int budget = p.n_tokens <= 128 ? 104 : 200;  // KB: two blocks a multiprocessor (measured ahead of three with fewer stages)
   if (tiles * p.ks <= 148) budget = 200;  // a block a multiprocessor at most: all of its shared memory for stages
   if (const char* e = getenv("FMS_B200_MID_SMEM_KB")) budget = atoi(e);
   int stages = budget * 1024 / stage_bytes;

@@ -9,9 +9,10 @@ Matrix products: float32 runs ``gemm_f32`` (FFMA, no tensor-core mode).  bfloat1
 instruction's rows from ``TENSOR_CORE_ROWS`` rows on (prefill; pairs of thread blocks on one tile, fused GLU
 epilogue), and in between, or when K is no multiple of 8, the library product (cuBLAS through
 ``torch.nn.functional.linear``), as the reference does for every linear layer (fms/modules/linear.py:119-156).
-With ``FMS_B200_MID_GEMM=1``, 9 to ``MID_ROWS`` (256) rows take a tcgen05 kernel of this library instead, with the
-weights on the instruction's rows (clusters of blocks share a tile along K; GLU and projection + rotation + cache
-write in its epilogue); the library's product is still ahead of it there, so it is not the default.
+The gated feed-forward product of 9 to 64 rows takes a tcgen05 kernel of this library with the weights on the
+instruction's rows and the activation in its epilogue (``gemm_bf16_mid.cu``); the same kernel can take the plain
+products and the fused projection up to 256 rows (clusters of blocks share a tile along K; projection + rotation
++ cache write in its epilogue; ``FMS_B200_MID_OPS``), where the library's product is still ahead of it.
 """
 from __future__ import annotations
 
@@ -219,16 +220,20 @@ TENSOR_CORE_ROWS = int(os.environ.get("FMS_B200_TC_ROWS", "1024"))
 USE_TENSOR_CORE_GEMM = os.environ.get("FMS_B200_TC_GEMM", "1") != "0"
 
 
-# The tcgen05 kernel with the weights on the instruction's rows, for SKINNY_ROWS + 1 to MID_ROWS rows.  Off unless
-# FMS_B200_MID_GEMM=1: measured at the 8B sizes it is at par with the library's product at 16 rows and 3 to 9 us a
-# product behind it at 64 (a decode step of batch 16: 3.96 against 3.86 ms; of batch 64: 6.34 against 5.61), and its
-# fused epilogues (three kernels a layer fewer) do not make that up.
-MID_ROWS = min(256, int(os.environ.get("FMS_B200_MID_ROWS", "256")))
-USE_MID_GEMM = os.environ.get("FMS_B200_MID_GEMM", "0") == "1"
+# The tcgen05 kernel with the weights on the instruction's rows (gemm_bf16_mid.cu), for SKINNY_ROWS + 1 to MID_ROWS
+# rows.  By default it takes the gated feed-forward product up to 64 rows, where it is ahead of the library's
+# product followed by the activation kernel (a decode step of batch 16 at the 8B sizes: 3.75 against 3.86 ms; batch 32:
+# 4.59 against 4.66; batch 64: at par).  The plain products and the fused projection, whose matrices have too few
+# rows for one block a tile and so run as clusters that add their sums, are 3 to 9 us a product behind the library
+# (batch 16: 4.02 ms with them, batch 64: 6.47) and stay with it unless FMS_B200_MID_OPS names them
+# ("linear,glu,qkv"; FMS_B200_MID_ROWS up to 256; FMS_B200_MID_GEMM=0 turns the kernel off).
+MID_ROWS = min(256, int(os.environ.get("FMS_B200_MID_ROWS", "64")))
+USE_MID_GEMM = os.environ.get("FMS_B200_MID_GEMM", "1") != "0"
+MID_OPS = os.environ.get("FMS_B200_MID_OPS", "glu").split(",")
 
 
-def _mid_fits(x, weight, bias) -> bool:
-    return (USE_MID_GEMM and SKINNY_ROWS < x.shape[0] <= MID_ROWS and weight.shape[1] % 8 == 0
+def _mid_fits(x, weight, bias, op: str = "linear") -> bool:
+    return (USE_MID_GEMM and op in MID_OPS and SKINNY_ROWS < x.shape[0] <= MID_ROWS and weight.shape[1] % 8 == 0
             and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
             and (bias is None or bias.dtype == torch.bfloat16))
 
@@ -275,7 +280,7 @@ def gated_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
         _call("gemm_bf16_skinny", "fms_glu_bf16_skinny", _ptr(x), _ptr(weight), _ptr(bias), _ptr(y), x.shape[0], hidden,
               weight.shape[1], int(activation), _stream())
         return y
-    if _mid_fits(x, weight, bias):
+    if _mid_fits(x, weight, bias, "glu"):
         _ptr(x), _ptr(weight)
         y = torch.empty((x.shape[0], hidden), dtype=torch.bfloat16, device=x.device)
         _call("gemm_bf16_mid", "fms_glu_bf16_mid", _ptr(x), _ptr(weight), _ptr(bias), _ptr(y), x.shape[0], hidden,
@@ -336,7 +341,7 @@ def qkv_rope_store(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
               kvheads, head_dim, 1 if writes_cache else 0, _ptr(error_flag(x.device)), batch.slots.shape[0],
               view.table.shape[0], view.keys.shape[0], _stream())
         return q
-    if (FUSE_QKV_ROPE and _mid_fits(x, weight, bias) and head_dim % 2 == 0 and view.keys.dtype == torch.bfloat16
+    if (FUSE_QKV_ROPE and _mid_fits(x, weight, bias, "qkv") and head_dim % 2 == 0 and view.keys.dtype == torch.bfloat16
             and weight.shape[0] == (nheads + 2 * kvheads) * head_dim):
         n = x.shape[0]
         q = torch.empty((n, nheads * head_dim), dtype=x.dtype, device=x.device)

@@ -25,11 +25,12 @@ def ops():
 
 @pytest.fixture
 def own_product_for_some_rows(ops):
-    """Products of 9 to 256 rows through this library's own tcgen05 kernel (by default they take the library's)."""
-    saved = ops.USE_MID_GEMM
-    ops.USE_MID_GEMM = True
+    """Every product of 9 to 256 rows through this library's own tcgen05 kernel (by default only the gated
+    feed-forward product up to 64 rows takes it)."""
+    saved = ops.USE_MID_GEMM, ops.MID_OPS, ops.MID_ROWS
+    ops.USE_MID_GEMM, ops.MID_OPS, ops.MID_ROWS = True, ["linear", "glu", "qkv"], 256
     yield
-    ops.USE_MID_GEMM = saved
+    ops.USE_MID_GEMM, ops.MID_OPS, ops.MID_ROWS = saved
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

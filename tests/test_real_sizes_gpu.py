@@ -189,14 +189,17 @@ def test_three_unequal_prompts_then_one_token_each(llama3, dtype):
 
 @pytest.fixture(params=["library_product", "own_product"])
 def product_for_some_rows(request):
-    """Products of 9 to 256 bfloat16 rows: the library's (the default), or this library's own tcgen05 kernel with
-    its fused epilogues (FMS_B200_MID_GEMM=1)."""
+    """Products of 9 to 256 bfloat16 rows: all by the library's product, or all by this library's own tcgen05 kernel
+    with its fused epilogues (the default is in between: the gated feed-forward product by the own kernel)."""
     from fms_b200.kernels import ops
 
-    saved = ops.USE_MID_GEMM
-    ops.USE_MID_GEMM = request.param == "own_product"
+    saved = ops.USE_MID_GEMM, ops.MID_OPS, ops.MID_ROWS
+    if request.param == "own_product":
+        ops.USE_MID_GEMM, ops.MID_OPS, ops.MID_ROWS = True, ["linear", "glu", "qkv"], 256
+    else:
+        ops.USE_MID_GEMM = False
     yield request.param
-    ops.USE_MID_GEMM = saved
+    ops.USE_MID_GEMM, ops.MID_OPS, ops.MID_ROWS = saved
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
