@@ -98,12 +98,12 @@ def test_linear_float32_is_true_float32(ops, m, n, k, bias):
 
 
 @pytest.mark.parametrize("n,k", [(70, 4), (100, 68), (64, 2052), (333, 1024), (130, 30)])
-@pytest.mark.parametrize("few", [1, 3, 8])
+@pytest.mark.parametrize("few", [1, 3, 8, 9, 16, 30, 64])
 def test_linear_float32_few_rows_are_bit_for_bit_the_same_rows_among_many(ops, few, n, k):
-    """A decode step's rows go through a kernel of their own (one thread a column); its sums run in the same
-    order as the tiled kernel's, so a token's logits do not depend on which of the two its step took."""
+    """Up to 64 rows go through a kernel of their own (one thread a column); its sums run in the same order as the
+    tiled kernel's (which 70 rows take), so a token's logits do not depend on which of the two its step took."""
     g = torch.Generator().manual_seed(31)
-    x = torch.randn(40, k, generator=g).cuda()
+    x = torch.randn(70, k, generator=g).cuda()
     w = torch.randn(n, k, generator=g).cuda()
     b = torch.randn(n, generator=g).cuda()
     many = ops.linear(x, w, b)
