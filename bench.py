@@ -339,7 +339,8 @@ def run_ours(args):
 
     if args.only:  # a short run of one part, for profilers: prints that part's figures only
         if args.only == "prefill":
-            print(json.dumps({"only": "prefill", "ms": round(run.prefill(PREFILL_TOKENS, repeats=args.steps), 3)}))
+            print(json.dumps({"only": "prefill", "tokens": args.prefill_tokens,
+                              "ms": round(run.prefill(args.prefill_tokens, repeats=args.steps), 3)}))
         else:
             batch = int(args.only.split("_b")[1])
             v, ms, _, _, _ = run.device_decode(batch, args.steps, args.warmup, regions=1)
@@ -511,6 +512,7 @@ def main():
     ap.add_argument("--model", choices=sorted(MODELS), default="llama-3-8b",
                     help="the shape to measure; the default is the benchmark's, the others are its further configurations")
     ap.add_argument("--dtype", choices=["bf16", "fp32"], default="bf16", help="fp32: the true 32-bit path")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="with --only prefill: the prompt's length")
     ap.add_argument("--points", choices=["default", "main", "long"], default="default",
                     help="main: without the further configurations; long: also decode at batch 64 with 8k contexts")
     args = ap.parse_args()

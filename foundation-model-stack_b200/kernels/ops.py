@@ -5,10 +5,12 @@ product only); every function launches on torch's current stream.  There is no C
 no fallback: a tensor on another device, a missing compiler or a failed build raises.
 
 Matrix products: float32 runs ``gemm_f32`` (FFMA, no tensor-core mode).  bfloat16 runs the weight-streaming
-``mma.sync`` kernel up to 8 rows (decode of few sequences), the tcgen05 kernel with the tokens on the
-instruction's rows from ``TENSOR_CORE_ROWS`` rows on (prefill; pairs of thread blocks on one tile, fused GLU
-epilogue), and in between, or when K is no multiple of 8, the library product (cuBLAS through
-``torch.nn.functional.linear``), as the reference does for every linear layer (fms/modules/linear.py:119-156).
+``mma.sync`` kernel up to 8 rows (decode of few sequences) and otherwise the library product (cuBLAS through
+``torch.nn.functional.linear``), as the reference does for every linear layer (fms/modules/linear.py:119-156) —
+except the gated feed-forward product, which from ``TENSOR_CORE_ROWS_GLU`` (2,048) rows on takes the tcgen05 kernel
+with the tokens on the instruction's rows (prefill; pairs of thread blocks on one tile, the activation in its
+epilogue).  The same kernel takes the plain products from ``FMS_B200_TC_ROWS`` rows on where that is set; measured
+through whole prefills the library's plain products are ahead, so by default it is not.
 The gated feed-forward product of 9 to 64 rows takes a tcgen05 kernel of this library with the weights on the
 instruction's rows and the activation in its epilogue (``gemm_bf16_mid.cu``); the same kernel can take the plain
 products and the fused projection up to 256 rows (clusters of blocks share a tile along K; projection + rotation
@@ -215,8 +217,16 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return torch.nn.functional.linear(x, weight, b)
 
 
-# rows from which the tcgen05 kernel is used instead of the library product (measured: at par or ahead from there on)
-TENSOR_CORE_ROWS = int(os.environ.get("FMS_B200_TC_ROWS", "1024"))
+# Rows from which the tcgen05 kernel with the tokens on the instruction's rows (gemm_bf16_tc.cu) is used instead of the
+# library's product.  Measured through whole prefills at the 8B sizes, the three policies taking turns in one warmed-up
+# process (ms, medians; library for everything / own gated product only / own for everything): 1,100 tokens 15.4 /
+# 16.4 / 19.6 (the own kernel's tiles of 256 rows waste a sixth there); 2,048 tokens 27.5 / 27.5 / 27.5; 4,096 tokens
+# 56.0 / 54.8 / 54.9; 8,192 tokens (each policy in a process of its own) 117.0 / 118.7 / 123.2.  So the gated product,
+# whose activation the own kernel has in its epilogue, takes the own kernel from 2,048 rows on, and everything else
+# stays with the library unless FMS_B200_TC_ROWS / FMS_B200_TC_ROWS_GLU name a number of rows (both were 1,024 once,
+# which cost prompts of 1,024 to 1,800 tokens up to a quarter of their time).
+TENSOR_CORE_ROWS = int(os.environ.get("FMS_B200_TC_ROWS", str(1 << 30)))
+TENSOR_CORE_ROWS_GLU = int(os.environ.get("FMS_B200_TC_ROWS_GLU", "2048"))
 USE_TENSOR_CORE_GEMM = os.environ.get("FMS_B200_TC_GEMM", "1") != "0"
 
 
@@ -238,8 +248,9 @@ def _mid_fits(x, weight, bias, op: str = "linear") -> bool:
             and (bias is None or bias.dtype == torch.bfloat16))
 
 
-def _tensor_core_fits(x, weight, bias) -> bool:
-    return (USE_TENSOR_CORE_GEMM and x.shape[0] >= TENSOR_CORE_ROWS and weight.shape[1] % 8 == 0
+def _tensor_core_fits(x, weight, bias, rows_from: Optional[int] = None) -> bool:
+    rows_from = TENSOR_CORE_ROWS if rows_from is None else rows_from
+    return (USE_TENSOR_CORE_GEMM and x.shape[0] >= rows_from and weight.shape[1] % 8 == 0
             and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
             and (bias is None or bias.dtype == torch.bfloat16))
 
@@ -286,7 +297,7 @@ def gated_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
         _call("gemm_bf16_mid", "fms_glu_bf16_mid", _ptr(x), _ptr(weight), _ptr(bias), _ptr(y), x.shape[0], hidden,
               weight.shape[1], int(activation), _ptr(error_flag(x.device)), _stream())
         return y
-    if _tensor_core_fits(x, weight, bias):
+    if _tensor_core_fits(x, weight, bias, TENSOR_CORE_ROWS_GLU):
         return gated_linear_tensor_core(x, weight, bias, activation)
     return gated_activation(linear(x, weight, bias), activation)
 

@@ -454,11 +454,16 @@ FURTHER_MODELS = {
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", sorted(FURTHER_MODELS))
-def test_further_configurations_against_the_plain_implementation(tmp_path, name, dtype):
+def test_further_configurations_against_the_plain_implementation(tmp_path, monkeypatch, name, dtype):
     """Sizes and options that the tiny models do not have: the prompts in one step, then four tokens one by one."""
     from fms_b200.models import get_model
     from tiny_models import llama_config, tiny_tensors_with_biases, write_folder
 
+    from fms_b200.kernels import ops
+
+    if name.startswith("tc_"):  # send the long prompt's products through the own tcgen05 kernel, as smaller prompts do not by default
+        monkeypatch.setattr(ops, "TENSOR_CORE_ROWS", 1024)
+        monkeypatch.setattr(ops, "TENSOR_CORE_ROWS_GLU", 1024)
     sizes, lengths = FURTHER_MODELS[name]
     cfg = llama_config(**sizes)
     folder = write_folder(str(tmp_path / name), cfg, tiny_tensors_with_biases(cfg, 7))

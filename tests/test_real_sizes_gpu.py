@@ -128,10 +128,25 @@ LONG = 1100
 PLACES = [0, 1, 63, 64, 511, 1023, 1024, LONG - 1]
 
 
+@pytest.fixture(params=["default_products", "own_plain_products"])
+def products_of_many_rows(request):
+    """bfloat16 products of a prompt of 1,100 tokens: by default the library's; with FMS_B200_TC_ROWS=1024 and
+    FMS_B200_TC_ROWS_GLU=1024 the own tcgen05 kernel (which by default takes the gated product from 2,048 rows on)."""
+    from fms_b200.kernels import ops
+
+    saved = ops.TENSOR_CORE_ROWS, ops.TENSOR_CORE_ROWS_GLU
+    if request.param == "own_plain_products":
+        ops.TENSOR_CORE_ROWS = ops.TENSOR_CORE_ROWS_GLU = 1024
+    yield request.param
+    ops.TENSOR_CORE_ROWS, ops.TENSOR_CORE_ROWS_GLU = saved
+
+
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-def test_one_long_prompt_whole(llama3, dtype):
+def test_one_long_prompt_whole(llama3, dtype, products_of_many_rows):
     """1,100 tokens in one step: in bfloat16 the tcgen05 products (pairs of blocks, GLU epilogue) and the tcgen05
     attention; logits at a handful of places (the first, block and tile edges, the last)."""
+    if dtype == "fp32" and products_of_many_rows == "own_plain_products":
+        pytest.skip("the float32 path has one product")
     (req,) = requests_of(llama3.vocab, [LONG], 1)
     engine = llama3.engine(dtype, max_tokens=1152)
     (slot,) = engine.begin(1)
