@@ -297,7 +297,8 @@ def gated_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
         _call("gemm_bf16_mid", "fms_glu_bf16_mid", _ptr(x), _ptr(weight), _ptr(bias), _ptr(y), x.shape[0], hidden,
               weight.shape[1], int(activation), _ptr(error_flag(x.device)), _stream())
         return y
-    if _tensor_core_fits(x, weight, bias, TENSOR_CORE_ROWS_GLU):
+    # the own kernel works on tiles of 256 rows: where the last one would be mostly padding, the library is ahead
+    if _tensor_core_fits(x, weight, bias, TENSOR_CORE_ROWS_GLU) and (x.shape[0] + 255) // 256 * 256 <= 1.06 * x.shape[0]:
         return gated_linear_tensor_core(x, weight, bias, activation)
     return gated_activation(linear(x, weight, bias), activation)
 
