@@ -227,6 +227,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 # which cost prompts of 1,024 to 1,800 tokens up to a quarter of their time).
 TENSOR_CORE_ROWS = int(os.environ.get("FMS_B200_TC_ROWS", str(1 << 30)))
 TENSOR_CORE_ROWS_GLU = int(os.environ.get("FMS_B200_TC_ROWS_GLU", "2048"))
+TENSOR_CORE_MAX_PADDING = float(os.environ.get("FMS_B200_TC_MAX_PADDING", "1.06"))  # rows computed over rows asked for
 USE_TENSOR_CORE_GEMM = os.environ.get("FMS_B200_TC_GEMM", "1") != "0"
 
 
@@ -298,7 +299,8 @@ def gated_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
               weight.shape[1], int(activation), _ptr(error_flag(x.device)), _stream())
         return y
     # the own kernel works on tiles of 256 rows: where the last one would be mostly padding, the library is ahead
-    if _tensor_core_fits(x, weight, bias, TENSOR_CORE_ROWS_GLU) and (x.shape[0] + 255) // 256 * 256 <= 1.06 * x.shape[0]:
+    if (_tensor_core_fits(x, weight, bias, TENSOR_CORE_ROWS_GLU)
+            and (x.shape[0] + 255) // 256 * 256 <= TENSOR_CORE_MAX_PADDING * x.shape[0]):
         return gated_linear_tensor_core(x, weight, bias, activation)
     return gated_activation(linear(x, weight, bias), activation)
 

@@ -134,11 +134,12 @@ def products_of_many_rows(request):
     FMS_B200_TC_ROWS_GLU=1024 the own tcgen05 kernel (which by default takes the gated product from 2,048 rows on)."""
     from fms_b200.kernels import ops
 
-    saved = ops.TENSOR_CORE_ROWS, ops.TENSOR_CORE_ROWS_GLU
+    saved = ops.TENSOR_CORE_ROWS, ops.TENSOR_CORE_ROWS_GLU, ops.TENSOR_CORE_MAX_PADDING
     if request.param == "own_plain_products":
         ops.TENSOR_CORE_ROWS = ops.TENSOR_CORE_ROWS_GLU = 1024
+        ops.TENSOR_CORE_MAX_PADDING = 10.0
     yield request.param
-    ops.TENSOR_CORE_ROWS, ops.TENSOR_CORE_ROWS_GLU = saved
+    ops.TENSOR_CORE_ROWS, ops.TENSOR_CORE_ROWS_GLU, ops.TENSOR_CORE_MAX_PADDING = saved
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
