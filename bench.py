@@ -181,16 +181,22 @@ def run_kernels(args):
 
     bf16 = torch.bfloat16
     if args.only == "gemm_rows":
+        # every own kernel that takes the size, called directly (whatever the step would choose), beside the library
         shapes = {"qkv": ((h + 2 * kv) * hd, d), "dense": (d, h * hd), "down": (d, f)}
         ws = {k: (torch.randn(n, kk, device="cuda") * 0.02).to(bf16) for k, (n, kk) in shapes.items()}
         wg = (torch.randn(2 * f, d, device="cuda") * 0.02).to(bf16)
+        ops.USE_MID_GEMM, ops.MID_OPS, ops.MID_ROWS = True, ["linear", "glu", "qkv"], 256
         for rows in (1, 8, 16, 64, 256, 512, 1024, 2048, 4096):
             xs = {d: torch.randn(rows, d, device="cuda").to(bf16), f: torch.randn(rows, f, device="cuda").to(bf16)}
-            line = {"only": "gemm_rows", "rows": rows, "us": "own, library"}
+            line = {"only": "gemm_rows", "rows": rows, "us": "weight-streaming (<= 8 rows: mma.sync; 9-256: tcgen05, "
+                    "weights on the rows), tcgen05 with the tokens on the rows (>= 128), library"}
+            small, large = rows <= 256, rows >= 128
             for name, (n, kk) in shapes.items():
-                line[name] = [timed(lambda: ops.linear(xs[kk], ws[name])),
+                line[name] = [timed(lambda: ops.linear(xs[kk], ws[name])) if small else None,
+                              timed(lambda: ops.linear_tensor_core(xs[kk], ws[name])) if large else None,
                               timed(lambda: torch.nn.functional.linear(xs[kk], ws[name]))]
-            line["glu"] = [timed(lambda: ops.gated_linear(xs[d], wg, None, 0)),
+            line["glu"] = [timed(lambda: ops.gated_linear(xs[d], wg, None, 0)) if small else None,
+                           timed(lambda: ops.gated_linear_tensor_core(xs[d], wg, None, 0)) if large else None,
                            timed(lambda: ops.gated_activation(torch.nn.functional.linear(xs[d], wg), 0))]
             print(json.dumps(line), flush=True)
     else:

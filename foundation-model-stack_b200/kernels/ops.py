@@ -7,7 +7,8 @@ no fallback: a tensor on another device, a missing compiler or a failed build ra
 Matrix products: float32 runs ``gemm_f32`` (FFMA, no tensor-core mode).  bfloat16 runs the weight-streaming
 ``mma.sync`` kernel up to 8 rows (decode of few sequences) and otherwise the library product (cuBLAS through
 ``torch.nn.functional.linear``), as the reference does for every linear layer (fms/modules/linear.py:119-156) —
-except the gated feed-forward product, which from ``TENSOR_CORE_ROWS_GLU`` (2,048) rows on takes the tcgen05 kernel
+except the gated feed-forward product, which from ``TENSOR_CORE_ROWS_GLU`` (512) rows on, where its tiles of 256
+rows fit the number of rows to 6%, takes the tcgen05 kernel
 with the tokens on the instruction's rows (prefill; pairs of thread blocks on one tile, the activation in its
 epilogue).  The same kernel takes the plain products from ``FMS_B200_TC_ROWS`` rows on where that is set; measured
 through whole prefills the library's plain products are ahead, so by default it is not.
@@ -218,15 +219,17 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 
 
 # Rows from which the tcgen05 kernel with the tokens on the instruction's rows (gemm_bf16_tc.cu) is used instead of the
-# library's product.  Measured through whole prefills at the 8B sizes, the three policies taking turns in one warmed-up
-# process (ms, medians; library for everything / own gated product only / own for everything): 1,100 tokens 15.4 /
-# 16.4 / 19.6 (the own kernel's tiles of 256 rows waste a sixth there); 2,048 tokens 27.5 / 27.5 / 27.5; 4,096 tokens
-# 56.0 / 54.8 / 54.9; 8,192 tokens (each policy in a process of its own) 117.0 / 118.7 / 123.2.  So the gated product,
-# whose activation the own kernel has in its epilogue, takes the own kernel from 2,048 rows on, and everything else
-# stays with the library unless FMS_B200_TC_ROWS / FMS_B200_TC_ROWS_GLU name a number of rows (both were 1,024 once,
-# which cost prompts of 1,024 to 1,800 tokens up to a quarter of their time).
+# library's product.  Measured through whole prefills at the 8B sizes (ms; library for everything / own gated product
+# only / own for everything).  The policies taking turns in one warmed-up process: 1,100 tokens 15.4 / 16.4 / 19.6;
+# 2,048 tokens 27.5 / 27.5 / 27.5; 4,096 tokens 56.0 / 54.8 / 54.9.  Each in a process of its own: 512 tokens 8.0 /
+# 7.8 / 7.8; 1,024 tokens 14.8 / 12.8 / -; 1,280 tokens 17.7 / 17.6 / 19.1; 8,192 tokens 117.0 / 118.7 / 123.2.  The
+# own kernel works on tiles of 256 rows, so it loses where the last tile is mostly padding (1,100 rows: a sixth is).
+# So the gated product, whose activation the own kernel has in its epilogue, takes the own kernel from 512 rows on
+# where at most 6% of the computed rows are padding, and everything else stays with the library unless
+# FMS_B200_TC_ROWS / FMS_B200_TC_ROWS_GLU / FMS_B200_TC_MAX_PADDING say otherwise (both row limits were 1,024 once, which
+# cost prompts of 1,025 to 1,800 tokens up to a quarter of their time).
 TENSOR_CORE_ROWS = int(os.environ.get("FMS_B200_TC_ROWS", str(1 << 30)))
-TENSOR_CORE_ROWS_GLU = int(os.environ.get("FMS_B200_TC_ROWS_GLU", "2048"))
+TENSOR_CORE_ROWS_GLU = int(os.environ.get("FMS_B200_TC_ROWS_GLU", "512"))
 TENSOR_CORE_MAX_PADDING = float(os.environ.get("FMS_B200_TC_MAX_PADDING", "1.06"))  # rows computed over rows asked for
 USE_TENSOR_CORE_GEMM = os.environ.get("FMS_B200_TC_GEMM", "1") != "0"
 
