@@ -598,7 +598,8 @@ def test_decode_of_many_long_sequences(tmp_path, dtype):
 
 
 def windowed_model(folder, dtype, window):
-    """Llama's layers with a window on every mixer: a test's variation, not a model of anyone's."""
+    """Llama's layers with a window on every mixer (``window``: one number, or one a layer with 0 for none): a
+    test's variation, not a model of anyone's."""
     import dataclasses
 
     from fms_b200.models import get_model
@@ -608,7 +609,9 @@ def windowed_model(folder, dtype, window):
     class WindowedLLaMA(LLaMA):
         def decoder_spec(self):
             spec = super().decoder_spec()
-            layers = tuple(dataclasses.replace(b, mixer=dataclasses.replace(b.mixer, window=window)) for b in spec.layers)
+            windows = window if isinstance(window, (list, tuple)) else [window] * len(spec.layers)
+            layers = tuple(dataclasses.replace(b, mixer=dataclasses.replace(b.mixer, window=w))
+                           for b, w in zip(spec.layers, windows))
             return dataclasses.replace(spec, layers=layers)
 
     base = get_model("hf_pretrained", model_path=folder, device_type="cuda", data_type=dtype)
@@ -619,8 +622,9 @@ def windowed_model(folder, dtype, window):
 
 def plain_windowed_logits(plain, ids, window):
     x = pl.plain_embedding(torch.as_tensor(ids), plain.w["model.embed_tokens.weight"])
+    windows = window if isinstance(window, (list, tuple)) else [window] * plain.c["nlayers"]
     for i in range(plain.c["nlayers"]):
-        x = plain.block(i, x, torch.arange(len(ids)), window=window)
+        x = plain.block(i, x, torch.arange(len(ids)), window=windows[i])
     x = pl.plain_rmsnorm(x, plain.w["model.norm.weight"], plain.c["eps"])
     return x @ plain.w["lm_head.weight"].T
 
@@ -644,6 +648,42 @@ def test_window_attention_through_the_engine(tiny_folders, oracles, which):
         engine.release([slot])
         engine.check()
         close(torch.cat(parts), want, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_layers_with_different_needs_have_storage_of_their_own(tiny_folders, oracles, dtype):
+    """Layer 0 keeps a window of 40 keys, layer 1 all keys: two groups in the cache, each with its own blocks and
+    table; the windowed group gives blocks back while the other keeps them.  Three requests of unequal lengths,
+    prompts in one step and then single tokens, the shortest ending first."""
+    windows = [40, 0]
+    reqs = long_requests("d", 4)[:3]  # 33, 300, 65 tokens
+    want = [plain_windowed_logits(oracles["d"], r, windows) for r in reqs]
+    engine = windowed_model(tiny_folders["d"], dtype, windows).new_engine(max_tokens=64 * 8, max_slots=3)
+    assert len(engine.cache.groups) == 2 and sorted(g.request.window for g in engine.cache.groups) == [0, 40]
+    slots = engine.begin(3)
+    cut = [20, 200, 60]
+    got = [[] for _ in reqs]
+    lg = engine.step(slots, [r[:c] for r, c in zip(reqs, cut)], [list(range(c)) for c in cut])
+    o = 0
+    for i, c in enumerate(cut):
+        got[i].append(lg[o:o + c])
+        o += c
+    at, live = list(cut), [0, 1, 2]
+    while live:
+        lg = engine.step([slots[i] for i in live], [[reqs[i][at[i]]] for i in live])
+        for j, i in enumerate(live):
+            got[i].append(lg[j:j + 1])
+            at[i] += 1
+        if 1 in live and at[1] == 290:
+            held = {g.request.window: len(g.held_blocks(slots[1])) for g in engine.cache.groups}
+            assert held[0] == 5 and held[40] <= 2  # all 290 keys there, 40 of them here
+        for i in [i for i in live if at[i] == len(reqs[i])]:
+            engine.release([slots[i]])
+            live.remove(i)
+    engine.check()
+    assert all(g.pool.n_held == 0 for g in engine.cache.groups)
+    for i in range(3):
+        close(torch.cat(got[i]), want[i], dtype)
 
 
 @pytest.fixture(scope="module")
