@@ -33,9 +33,30 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict
   const float* x = logits + (size_t)blockIdx.x * vocab;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += THREADS) {
-    const float v = x[i];
-    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  if ((vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    // 16 bytes a load, four loads on their way before the first comparison: the row is one block's to read, so
+    // what counts is how many bytes that block keeps in flight
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    const int n4 = vocab >> 2;
+    for (int i0 = threadIdx.x; i0 < n4; i0 += 4 * THREADS) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        v[u] = i0 + u * THREADS < n4 ? x4[i0 + u * THREADS] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = 4 * (i0 + u * THREADS);
+        const float e[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (e[j] > bv || (e[j] == bv && i + j < bi)) { bv = e[j]; bi = i + j; }
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += THREADS) {
+      const float v = x[i];
+      if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
