@@ -439,6 +439,35 @@ FMS_API int fms_rope_store(const void* qkv, int dtype, void* q_out, const float*
 }
 
 // ---------------------------------------------------------------------------------------------------
+// (sin, cos) of every token's rotation angles, once a step for all layers that rotate by the same frequencies:
+//   out[t, i] = (sin, cos)(position(t) * inv_freq[i]),  position = position_ids[t] if given, else positions[t]
+// the float32 product and sincosf of the rotation kernels themselves, so a kernel that reads the table turns by the
+// very angles one that takes them itself would
+// ---------------------------------------------------------------------------------------------------
+__global__ void rotary_table_kernel(const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                                    const int* __restrict__ position_ids, float2* __restrict__ out, int n_tokens, int half) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long total = (long)n_tokens * half;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int t = (int)(i / half), p = (int)(i - (long)t * half);
+    float sn, cs;
+    sincosf((float)(position_ids ? position_ids[t] : positions[t]) * inv_freq[p], &sn, &cs);
+    out[i] = make_float2(sn, cs);
+  }
+}
+
+FMS_API int fms_rotary_table(const float* inv_freq, const int* positions, const int* position_ids, void* out, int n_tokens,
+                             int half, cudaStream_t stream) {
+  if (n_tokens <= 0 || half <= 0) return 0;
+  const long total = (long)n_tokens * half;
+  const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  fms_launch(rotary_table_kernel, dim3(blocks), dim3(256), 0, stream, inv_freq, positions, position_ids, (float2*)out,
+             n_tokens, half);
+  return fms_launch_status("rotary_table");
+}
+
+// ---------------------------------------------------------------------------------------------------
 // start of a decode step: every sequence's new token sits at its current length, which then grows by one; the
 // position its encoding sees is that place plus the offset at which the sequence started (offsets null: none)
 // ---------------------------------------------------------------------------------------------------

@@ -52,12 +52,42 @@ struct Epilogue {
   int act;
   int tile_n;         // accumulator columns of a tile: rows of w per tile (GLU: gate and up together)
   int stages;
+  // The fused projection of an attention layer (qkv 1): rows of w are [q heads | k heads | v heads]; q and k are
+  // rotated by each token's position (adjacent pairs, float32 angles, fms/modules/positions.py:438-456), q goes to
+  // `out` [M, nheads * head_dim], k and v into the token's place in the block cache.
+  int qkv;
+  const float2* sincos;       // [M, head_dim / 2] (sin, cos) of every token's rotation angles, or null: nothing is rotated
+  const int* positions;       // [M] each token's place in its sequence's cache
+  const int* token_seq;       // [M] index into slots
+  const int* slots;
+  __nv_bfloat16* k_cache;     // [blocks, kvheads, block_tokens, head_dim]
+  __nv_bfloat16* v_cache;
+  const int* table;           // [table_rows, table_stride]
+  int table_stride, block_tokens, nheads, kvheads, head_dim, write_cache;
+  int n_seqs, table_rows, pool_blocks;  // extents, for the bounds-checked build
+  int* error_flag;
 };
 
 // One thread's row of a tile's accumulator (tensor-memory address `taddr`, lane = row), `tile_n` output columns
 // from column n0 on: bias, the GLU product, conversion, store.  Every lane of the warp must call it.
 __device__ __forceinline__ void store_rows(const Epilogue& ep, uint32_t taddr, int row, int n0, int tile_n, int M, int N) {
   const __nv_bfloat16* bias = (const __nv_bfloat16*)ep.bias;
+  // the fused projection: what this thread's token needs for the rotation and for its place in the cache, once a tile
+  int pos = 0, blk = -1;
+  if (ep.qkv && row < M) {
+    pos = ep.positions[row];
+    if (ep.write_cache && n0 + tile_n > ep.nheads * ep.head_dim) {  // the tile holds columns of k or v
+      const int seq = ep.token_seq[row];
+      if (FMS_IN(seq, ep.n_seqs)) {
+        const int slot = ep.slots[seq];
+        if (FMS_IN(slot, ep.table_rows) && FMS_IN(pos / ep.block_tokens, ep.table_stride)) {
+          blk = ep.table[(size_t)slot * ep.table_stride + pos / ep.block_tokens];
+          if (blk < 0 && ep.error_flag) atomicExch(ep.error_flag, 2);
+          if (blk >= 0 && !FMS_IN(blk, ep.pool_blocks)) blk = -1;
+        }
+      }
+    }
+  }
   // 16 columns at a time (every lane loads: tensor-memory loads are warp-wide; only rows inside M store)
   for (int c0 = 0; c0 < tile_n; c0 += 16) {
     float v[16];
@@ -81,6 +111,49 @@ __device__ __forceinline__ void store_rows(const Epilogue& ep, uint32_t taddr, i
         if (col0 + jj < ncols) v[jj] += __bfloat162float(bias[col0 + jj]);
     }
     if (row >= M || col0 >= ncols) continue;  // nothing of these 16 columns lies inside y
+    if (ep.qkv) {
+      // 16 columns of one head (head sizes are multiples of 16, and so is col0): 8 rotary pairs
+      const int head = col0 / ep.head_dim, d0 = col0 - head * ep.head_dim;
+      const bool is_q = head < ep.nheads, is_v = head >= ep.nheads + ep.kvheads;
+      if (!is_v && ep.sincos != nullptr) {
+        // the step's table of (sin, cos): 64 contiguous bytes of this token's row
+        float2 sc[8];
+        const float4* t = reinterpret_cast<const float4*>(ep.sincos + (size_t)row * (ep.head_dim >> 1) + (d0 >> 1));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float4 two = t[j];
+          sc[2 * j] = make_float2(two.x, two.y);
+          sc[2 * j + 1] = make_float2(two.z, two.w);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float sn = sc[j].x, cs = sc[j].y;
+          const float x0 = v[2 * j], x1 = v[2 * j + 1];
+          v[2 * j] = cs * x0 - sn * x1;
+          v[2 * j + 1] = sn * x0 + cs * x1;
+        }
+      }
+      __nv_bfloat16* o;
+      if (is_q) {
+        o = (__nv_bfloat16*)ep.out + ((size_t)row * ep.nheads + head) * ep.head_dim + d0;
+      } else {
+        if (!ep.write_cache || blk < 0) continue;
+        const int kvh = is_v ? head - ep.nheads - ep.kvheads : head - ep.nheads;
+        o = (is_v ? ep.v_cache : ep.k_cache) +
+            (((size_t)blk * ep.kvheads + kvh) * ep.block_tokens + (pos % ep.block_tokens)) * ep.head_dim + d0;
+      }
+#pragma unroll
+      for (int jj = 0; jj < 16; jj += 8) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          __nv_bfloat162 t = __floats2bfloat162_rn(v[jj + 2 * q], v[jj + 2 * q + 1]);
+          pk[q] = *reinterpret_cast<uint32_t*>(&t);
+        }
+        *reinterpret_cast<uint4*>(o + jj) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+      continue;
+    }
     if (!FMS_IN((size_t)row * ncols + col0, (size_t)M * ncols)) continue;
     if (ep.out_f32) {
       float* o = (float*)ep.out + (size_t)row * ncols + col0;
@@ -428,7 +501,10 @@ FMS_API int fms_gemm_bf16_tc(const void* x, const void* w, const void* bias, voi
                              int* error_flag, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (out_dtype != FMS_F32 && out_dtype != FMS_BF16) return fms_fail("gemm_tc: out dtype %d", out_dtype);
-  Epilogue ep{y, bias, out_dtype == FMS_F32 ? 1 : 0, 0, 0, 0, 0, 0};
+  Epilogue ep = {};
+  ep.out = y;
+  ep.bias = bias;
+  ep.out_f32 = out_dtype == FMS_F32 ? 1 : 0;
   return launch(x, w, N, ep, M, N, K, error_flag, stream);
 }
 
@@ -437,6 +513,54 @@ FMS_API int fms_glu_bf16_tc(const void* x, const void* w, const void* bias, void
                             int* error_flag, cudaStream_t stream) {
   if (M <= 0 || hidden <= 0) return 0;
   if (act < 0 || act > 3) return fms_fail("glu_tc: activation %d", act);
-  Epilogue ep{y, bias, 0, 1, hidden, act, 0, 0};
+  Epilogue ep = {};
+  ep.out = y;
+  ep.bias = bias;
+  ep.glu = 1;
+  ep.hidden = hidden;
+  ep.act = act;
   return launch(x, w, 2 * hidden, ep, M, hidden, K, error_flag, stream);
+}
+
+// The fused projection of an attention layer for many tokens: [q | k | v] = x w^T + bias; q and k rotated by each
+// token's position; q -> q_out [M, nheads head_dim], k and v -> the token's place in the block cache (write_cache 0: q
+// only).  head_dim must be a multiple of 16.  A token whose position has no block sets error flag 2 and is skipped.
+// sincos: (sin, cos) of every token's rotation angles, [M, head_dim / 2] float2, 16-byte aligned, as fms_rotary_table
+// (elementwise.cu) makes it once a step for all layers; null: nothing is rotated.  (Taking them in the epilogue with
+// sincosf made the epilogue longer than the tile's products: a prefill of 2,048 tokens lost 1.3 ms to it.)
+FMS_API int fms_qkv_rope_store_bf16_tc(const void* x, const void* w, const void* bias, void* q_out, const void* sincos,
+                                       const int* positions, const int* token_seq,
+                                       const int* slots, void* k_cache, void* v_cache, const int* table, int table_stride,
+                                       int block_tokens, int M, int K, int nheads, int kvheads, int head_dim,
+                                       int write_cache, int* error_flag, int n_seqs, int table_rows, int pool_blocks,
+                                       cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (nheads <= 0 || kvheads <= 0 || head_dim <= 0 || head_dim % 16 || block_tokens <= 0)
+    return fms_fail("qkv_rope_store_bf16_tc: %d heads, %d kv heads, head size %d (a multiple of 16), blocks of %d", nheads,
+                    kvheads, head_dim, block_tokens);
+  const long rows = (long)(nheads + 2 * kvheads) * head_dim;
+  if (rows > 0x7fffffffL) return fms_fail("qkv_rope_store_bf16_tc: %ld rows of w", rows);
+  Epilogue ep = {};
+  ep.out = q_out;
+  ep.bias = bias;
+  ep.qkv = 1;
+  ep.sincos = (const float2*)sincos;
+  ep.positions = positions;
+  ep.token_seq = token_seq;
+  ep.slots = slots;
+  ep.k_cache = (__nv_bfloat16*)k_cache;
+  ep.v_cache = (__nv_bfloat16*)v_cache;
+  ep.table = table;
+  ep.table_stride = table_stride;
+  ep.block_tokens = block_tokens;
+  ep.nheads = nheads;
+  ep.kvheads = kvheads;
+  ep.head_dim = head_dim;
+  ep.write_cache = write_cache;
+  ep.n_seqs = n_seqs;
+  ep.table_rows = table_rows;
+  ep.pool_blocks = pool_blocks;
+  ep.error_flag = error_flag;
+  if (ep.sincos != nullptr && ((uintptr_t)ep.sincos & 15)) return fms_fail("qkv_rope_store_bf16_tc: the table must be 16-byte aligned");
+  return launch(x, w, (int)rows, ep, M, (int)rows, K, error_flag, stream);
 }

@@ -38,6 +38,7 @@ class Batch:
         self.want_rows: Optional[torch.Tensor] = None  # [n_wanted] int32 rows whose logits are returned
         self.n_wanted = 0
         self._tiles = {}
+        self.scratch = {}  # what a step's layers share (a table of rotation angles, ...); emptied when a step starts
 
     @staticmethod
     def from_lists(slots: Sequence[int], len_before: Sequence[int], tokens: Sequence[Sequence[int]],

@@ -58,6 +58,8 @@ class Decoder(Part):
         return self.embedding.tensor("weight") if self.spec.tie_head else self.head.tensor("weight")
 
     def forward(self, batch, cache):
+        if getattr(batch, "scratch", None) is not None:
+            batch.scratch.clear()  # nothing of an earlier step with the same arrays (a decode step) is kept
         residual = ops.embed(self.embedding.tensor("weight"), batch.tokens, self.spec.embedding_scale)
         pending = None
         for call in self.spec.schedule:

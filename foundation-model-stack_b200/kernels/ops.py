@@ -10,8 +10,10 @@ Matrix products: float32 runs ``gemm_f32`` (FFMA, no tensor-core mode).  bfloat1
 except the gated feed-forward product, which from ``TENSOR_CORE_ROWS_GLU`` (512) rows on, where its tiles of 256
 rows fit the number of rows to 6%, takes the tcgen05 kernel
 with the tokens on the instruction's rows (prefill; pairs of thread blocks on one tile, the activation in its
-epilogue).  The same kernel takes the plain products from ``FMS_B200_TC_ROWS`` rows on where that is set; measured
-through whole prefills the library's plain products are ahead, so by default it is not.
+epilogue), and the fused projection of queries, keys and values, which from ``TENSOR_CORE_ROWS_QKV`` (2,048) rows
+on takes the same kernel with the rotation and the cache write in its epilogue.  The same kernel takes the plain
+products from ``FMS_B200_TC_ROWS`` rows on where that is set; measured through whole prefills the library's plain
+products are ahead, so by default it is not.
 The gated feed-forward product of 9 to 64 rows takes a tcgen05 kernel of this library with the weights on the
 instruction's rows and the activation in its epilogue (``gemm_bf16_mid.cu``); the same kernel can take the plain
 products and the fused projection up to 256 rows (clusters of blocks share a tile along K; projection + rotation
@@ -36,6 +38,7 @@ _SIGNATURES = {
     "fms_gated_activation": [_P, _P, _I, _I, _I, _I, _P],
     "fms_rope_store": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _I, _P],
     "fms_decode_advance": [_P, _P, _P, _P, _I, _P],
+    "fms_rotary_table": [_P, _P, _P, _P, _I, _I, _P],
     "fms_gemm_f32": [_P, _P, _P, _P, _I, _I, _I, _P],
     "fms_linear_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "fms_glu_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
@@ -47,6 +50,8 @@ _SIGNATURES = {
                                     _I, _I, _I, _P],
     "fms_gemm_bf16_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "fms_glu_bf16_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
+    "fms_qkv_rope_store_bf16_tc": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P,
+                                   _I, _I, _I, _P],
     "fms_argmax": [_P, _P, _I, _I, _P],
     "fms_sample": [_P, _P, _I, _I, _F, _I, _U64, _P, _I, _P],
     "fms_attention_prefill": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P],
@@ -230,6 +235,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 # cost prompts of 1,025 to 1,800 tokens up to a quarter of their time).
 TENSOR_CORE_ROWS = int(os.environ.get("FMS_B200_TC_ROWS", str(1 << 30)))
 TENSOR_CORE_ROWS_GLU = int(os.environ.get("FMS_B200_TC_ROWS_GLU", "512"))
+# The projection with the rotation and the cache write in the own kernel's epilogue, against the library's product and
+# the rotation kernel after it, whole prefills in processes of their own (ms, fused / two kernels): 1,024 tokens 14.5 /
+# 14.1; 2,048 tokens 26.5 / 26.6; 3,000 tokens 40.0 / 41.0; 4,096 tokens 53.3 / 54.3; 8,192 tokens 121.2 / 120.1.
+TENSOR_CORE_ROWS_QKV = int(os.environ.get("FMS_B200_TC_ROWS_QKV", "2048"))
 TENSOR_CORE_MAX_PADDING = float(os.environ.get("FMS_B200_TC_MAX_PADDING", "1.06"))  # rows computed over rows asked for
 USE_TENSOR_CORE_GEMM = os.environ.get("FMS_B200_TC_GEMM", "1") != "0"
 
@@ -340,6 +349,23 @@ def rope_store(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], batch, view,
 FUSE_QKV_ROPE = os.environ.get("FMS_B200_FUSE_QKV_ROPE", "1") != "0"
 
 
+def rotary_table(inv_freq: torch.Tensor, batch) -> torch.Tensor:
+    """[tokens, head_dim / 2, 2] float32: (sin, cos) of every token's rotation angles, made once a step and kept
+    with the batch (``batch.scratch``, which the decoder empties when a step starts) for every layer that rotates by
+    the same frequencies."""
+    scratch = getattr(batch, "scratch", None)
+    key = ("rotary_table", inv_freq.data_ptr())
+    if scratch is not None and key in scratch:
+        return scratch[key]
+    n, half = batch.positions.shape[0], inv_freq.shape[0]
+    out = torch.empty((n, half, 2), dtype=torch.float32, device=inv_freq.device)
+    _call("elementwise", "fms_rotary_table", _ptr(inv_freq), _ptr(batch.positions), _ptr(getattr(batch, "position_ids", None)),
+          _ptr(out), n, half, _stream())
+    if scratch is not None:
+        scratch[key] = out
+    return out
+
+
 def qkv_rope_store(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
                    batch, view, nheads: int, kvheads: int, head_dim: int, writes_cache: bool = True) -> torch.Tensor:
     """An attention layer's fused projection and what follows it: qkv = x weight^T (+ bias), q and k rotated by each
@@ -364,6 +390,20 @@ def qkv_rope_store(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
         q = torch.empty((n, nheads * head_dim), dtype=x.dtype, device=x.device)
         _call("gemm_bf16_mid", "fms_qkv_rope_store_bf16_mid", _ptr(x), _ptr(weight), _ptr(bias), _ptr(q), _ptr(inv_freq),
               _ptr(batch.positions), _ptr(getattr(batch, "position_ids", None)), _ptr(batch.token_seq), _ptr(batch.slots),
+              _ptr(view.keys), _ptr(view.values), _ptr(view.table), view.table.shape[1], view.block_tokens, n,
+              weight.shape[1], nheads, kvheads, head_dim, 1 if writes_cache else 0, _ptr(error_flag(x.device)),
+              batch.slots.shape[0], view.table.shape[0], view.keys.shape[0], _stream())
+        return q
+    if (FUSE_QKV_ROPE and _tensor_core_fits(x, weight, bias, TENSOR_CORE_ROWS_QKV) and head_dim % 16 == 0
+            and (x.shape[0] + 255) // 256 * 256 <= TENSOR_CORE_MAX_PADDING * x.shape[0]
+            and view.keys.dtype == torch.bfloat16 and weight.shape[0] == (nheads + 2 * kvheads) * head_dim):
+        # many tokens: the tcgen05 product with the rotation and the cache write in its epilogue; the angles' sines and
+        # cosines come from a table that the step's first such layer makes for all layers with the same frequencies
+        n = x.shape[0]
+        q = torch.empty((n, nheads * head_dim), dtype=x.dtype, device=x.device)
+        table = None if inv_freq is None else rotary_table(inv_freq, batch)
+        _call("gemm_bf16_tc", "fms_qkv_rope_store_bf16_tc", _ptr(x), _ptr(weight), _ptr(bias), _ptr(q), _ptr(table),
+              _ptr(batch.positions), _ptr(batch.token_seq), _ptr(batch.slots),
               _ptr(view.keys), _ptr(view.values), _ptr(view.table), view.table.shape[1], view.block_tokens, n,
               weight.shape[1], nheads, kvheads, head_dim, 1 if writes_cache else 0, _ptr(error_flag(x.device)),
               batch.slots.shape[0], view.table.shape[0], view.keys.shape[0], _stream())

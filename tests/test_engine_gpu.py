@@ -464,6 +464,7 @@ def test_further_configurations_against_the_plain_implementation(tmp_path, monke
     if name.startswith("tc_"):  # send the long prompt's products through the own tcgen05 kernel, as smaller prompts do not by default
         monkeypatch.setattr(ops, "TENSOR_CORE_ROWS", 1024)
         monkeypatch.setattr(ops, "TENSOR_CORE_ROWS_GLU", 1024)
+        monkeypatch.setattr(ops, "TENSOR_CORE_ROWS_QKV", 1024)
         monkeypatch.setattr(ops, "TENSOR_CORE_MAX_PADDING", 10.0)
     sizes, lengths = FURTHER_MODELS[name]
     cfg = llama_config(**sizes)

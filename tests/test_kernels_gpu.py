@@ -26,11 +26,12 @@ def ops():
 @pytest.fixture
 def own_product_for_some_rows(ops):
     """Every product of 9 to 256 rows through this library's own tcgen05 kernel (by default only the gated
-    feed-forward product up to 64 rows takes it)."""
-    saved = ops.USE_MID_GEMM, ops.MID_OPS, ops.MID_ROWS
+    feed-forward product up to 64 rows takes it), and the own kernels for many rows whatever padding their tiles need."""
+    saved = ops.USE_MID_GEMM, ops.MID_OPS, ops.MID_ROWS, ops.TENSOR_CORE_MAX_PADDING, ops.TENSOR_CORE_ROWS_QKV
     ops.USE_MID_GEMM, ops.MID_OPS, ops.MID_ROWS = True, ["linear", "glu", "qkv"], 256
+    ops.TENSOR_CORE_MAX_PADDING, ops.TENSOR_CORE_ROWS_QKV = 10.0, 512
     yield
-    ops.USE_MID_GEMM, ops.MID_OPS, ops.MID_ROWS = saved
+    ops.USE_MID_GEMM, ops.MID_OPS, ops.MID_ROWS, ops.TENSOR_CORE_MAX_PADDING, ops.TENSOR_CORE_ROWS_QKV = saved
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -323,12 +324,17 @@ def test_rope_store(ops, dtype, nheads, kvheads, hd):
     (5, 5, 48, [130], [100]),                                 # odd head size: tiles of 128 rows cut through heads
     (32, 8, 128, [100 + 7 * i for i in range(64)], [1] * 64), # the benchmark's head layout, batch 64
     (7, 1, 80, [5, 0], [120, 136]),                           # 256 rows
+    # from 512 rows on: the tcgen05 kernel with the tokens on the instruction's rows has the epilogue too
+    (32, 8, 128, [0, 100], [400, 112]),                       # the benchmark's head layout, 512 rows
+    (5, 5, 48, [10, 0, 70], [300, 1, 219]),                   # odd head size, tiles that cut through heads, 520 rows
+    (4, 1, 16, [0], [700]),                                   # the smallest head size
 ])
 @pytest.mark.parametrize("with_bias", [False, True])
 def test_projection_rotation_and_cache_write_in_one_kernel(ops, own_product_for_some_rows, nheads, kvheads, hd, lens_before,
                                                            num_new, with_bias):
-    """Up to 256 bfloat16 rows: the product (weight-streaming mma.sync up to 8 rows, tcgen05 from 9 on) rotates q and
-    k and writes k and v into the cache in its epilogue.  Against the plain product followed by the plain rotation and cache write (which round the product
+    """bfloat16 rows: the product (weight-streaming mma.sync up to 8 rows, tcgen05 with the weights on the rows from
+    9 to 256, tcgen05 with the tokens on the rows from 512 on) rotates q and k and writes k and v into the cache in its
+    epilogue.  Against the plain product followed by the plain rotation and cache write (which round the product
     to bfloat16 in between; the fused kernel rotates the float32 sums)."""
     dtype, k = torch.bfloat16, 8 * 21
     cache, view, batch = make_cache_case(dtype, nheads, kvheads, hd, lens_before, num_new, 23)
@@ -360,6 +366,27 @@ def test_projection_rotation_and_cache_write_in_one_kernel(ops, own_product_for_
     q2 = ops.qkv_rope_store(x, w, b, None, batch, view, nheads, kvheads, hd, writes_cache=False)
     torch.testing.assert_close(q2.float(), P.linear(x, w, b, torch.float32)[:, : nheads * hd].float(), **t)
     assert torch.equal(torch.nan_to_num(view.keys.float()), torch.nan_to_num(before.float()))
+
+
+@pytest.mark.parametrize("half,n", [(8, 5), (64, 700), (40, 33)])
+@pytest.mark.parametrize("with_ids", [False, True])
+def test_table_of_rotation_angles(ops, half, n, with_ids):
+    """(sin, cos) of position * frequency in float32, once a step for all layers; with position ids, of those."""
+    g = torch.Generator().manual_seed(half)
+    inv = (1.0 / (10000.0 ** (torch.arange(half).float() / half))).cuda()
+
+    class B:
+        positions = torch.randint(0, 100000, (n,), generator=g, dtype=torch.int32).cuda()
+        position_ids = torch.randint(0, 100000, (n,), generator=g, dtype=torch.int32).cuda() if with_ids else None
+        scratch = {}
+
+    got = ops.rotary_table(inv, B)
+    seen = (B.position_ids if with_ids else B.positions).float()
+    angles = (seen[:, None] * inv[None, :]).double()  # the float32 product, as the rotation kernels take it
+    assert got.shape == (n, half, 2) and got.dtype == torch.float32
+    torch.testing.assert_close(got[..., 0].double(), angles.sin(), atol=2e-7, rtol=0)
+    torch.testing.assert_close(got[..., 1].double(), angles.cos(), atol=2e-7, rtol=0)
+    assert ops.rotary_table(inv, B) is got  # kept with the batch until the next step empties it
 
 
 ATTN_CASES = [

@@ -130,16 +130,17 @@ PLACES = [0, 1, 63, 64, 511, 1023, 1024, LONG - 1]
 
 @pytest.fixture(params=["default_products", "own_plain_products"])
 def products_of_many_rows(request):
-    """bfloat16 products of a prompt of 1,100 tokens: by default the library's; with FMS_B200_TC_ROWS=1024 and
-    FMS_B200_TC_ROWS_GLU=1024 the own tcgen05 kernel (which by default takes the gated product from 2,048 rows on)."""
+    """bfloat16 products of a prompt of 1,100 tokens: by default the library's; with the row limits at 1,024 and no
+    limit on padding the own tcgen05 kernel for all of them (plain, gated, and the projection with the rotation and
+    the cache write in its epilogue), which by default waits for more rows and for tiles that fit."""
     from fms_b200.kernels import ops
 
-    saved = ops.TENSOR_CORE_ROWS, ops.TENSOR_CORE_ROWS_GLU, ops.TENSOR_CORE_MAX_PADDING
+    saved = ops.TENSOR_CORE_ROWS, ops.TENSOR_CORE_ROWS_GLU, ops.TENSOR_CORE_ROWS_QKV, ops.TENSOR_CORE_MAX_PADDING
     if request.param == "own_plain_products":
-        ops.TENSOR_CORE_ROWS = ops.TENSOR_CORE_ROWS_GLU = 1024
+        ops.TENSOR_CORE_ROWS = ops.TENSOR_CORE_ROWS_GLU = ops.TENSOR_CORE_ROWS_QKV = 1024
         ops.TENSOR_CORE_MAX_PADDING = 10.0
     yield request.param
-    ops.TENSOR_CORE_ROWS, ops.TENSOR_CORE_ROWS_GLU, ops.TENSOR_CORE_MAX_PADDING = saved
+    ops.TENSOR_CORE_ROWS, ops.TENSOR_CORE_ROWS_GLU, ops.TENSOR_CORE_ROWS_QKV, ops.TENSOR_CORE_MAX_PADDING = saved
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
