@@ -340,7 +340,8 @@ def run_ours(args):
     nlayers = args.layers or MODEL["nlayers"]
     room = max(3, args.warmup) + REGIONS * args.steps + 8
     long_context = args.points != "main" and not args.only and MODEL["context"] >= 8192
-    run = Measured(MODEL, dtype, nlayers, room, PROMPT_MAX, slots=64,
+    slots = max(64, int(args.only.split("_b")[1])) if args.only.startswith("decode_b") else 64
+    run = Measured(MODEL, dtype, nlayers, room, PROMPT_MAX, slots=slots,
                    long_requests=(64 if args.points == "long" else 8) if long_context else 0)
 
     if args.only:  # a short run of one part, for profilers: prints that part's figures only

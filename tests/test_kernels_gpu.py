@@ -258,7 +258,8 @@ def make_cache_case(dtype, nheads, kvheads, hd, lens_before, num_new, seed, wind
     g = torch.Generator().manual_seed(seed)
     n = len(lens_before)
     cache = Cache([KVRequest(kvheads, hd, window)], max_tokens=64 * (sum((a + b + 63) // 64 for a, b in zip(lens_before, num_new)) + 5),
-                  max_positions=8192, dtype=dtype, device="cuda")
+                  max_positions=max(8192, 64 * ((max(a + b for a, b in zip(lens_before, num_new)) + 63) // 64)),
+                  dtype=dtype, device="cuda")
     # scramble the free list so that block ids are not in order
     pool = cache.groups[0].pool
     perm = torch.randperm(len(pool._free), generator=g).tolist()
@@ -277,10 +278,10 @@ def make_cache_case(dtype, nheads, kvheads, hd, lens_before, num_new, seed, wind
     table = cache.groups[0].table_host
     for s, lb in zip(slots, lens_before):
         lo = max(0, lb - window + 1) // 64 * 64 if window else 0
-        for p in range(lo, lb):
-            blk = int(table[s, p // 64])
-            view.keys[blk, :, p % 64] = torch.randn(kvheads, hd, generator=g).to(dtype).cuda()
-            view.values[blk, :, p % 64] = torch.randn(kvheads, hd, generator=g).to(dtype).cuda()
+        for first in range(lo, lb, 64):  # block by block
+            blk, count = int(table[s, first // 64]), min(64, lb - first)
+            view.keys[blk, :, :count] = torch.randn(kvheads, count, hd, generator=g).to(dtype).cuda()
+            view.values[blk, :, :count] = torch.randn(kvheads, count, hd, generator=g).to(dtype).cuda()
     tokens = [[0] * k for k in num_new]
     batch = Batch.from_lists(slots, lens_before, tokens, [[] for _ in tokens], "cuda")
     return cache, view, batch
@@ -409,6 +410,9 @@ ATTN_CASES = [
     (5, 5, 48, [130, 70], [1, 1], 0),               # decode, a head size whose 16-byte pieces do not divide a warp
     (4, 2, 80, [100, 200], [1, 1], 0),              # decode, head size 80 (a last k-step of 16 alone)
     (4, 2, 80, [10], [70], 0),                      # prefill, head size 80
+    (2, 1, 64, [33000], [1], 0),                    # decode over more splits (129) than the merge stages in shared memory
+    (4, 2, 16, [40000, 100], [1, 1], 3000),         # the same behind a window: the first 144 splits hold nothing
+    (8, 8, 128, [33000, 100, 5000, 64], [1, 1, 1, 1], 0),  # the same with enough to read for the streaming kernel
 ]
 
 
