@@ -105,7 +105,7 @@ def get_model(architecture: str, variant: Optional[str] = None, model_path: Opti
             if names[0] not in _hf_architectures:
                 raise KeyError(f"config.json names architecture {names[0]!r}; known: {sorted(_hf_architectures)}")
             architecture = _hf_architectures[names[0]]
-            source = source or "hf"
+            source = source or _architectures[architecture].default_source
         if architecture not in _architectures:
             raise KeyError(f"{architecture} is not registered. See `models.list_models()` for available architectures")
         config = _architectures[architecture].config_from_json(values)
