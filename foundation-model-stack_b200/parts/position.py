@@ -73,6 +73,9 @@ class PositionEncoding(Part):
         return ["elementwise"]
 
 
+_frequencies_on_device = {}  # (PositionSpec, device) -> float32 [head_dim / 2]; a few hundred bytes each
+
+
 class RotaryEmbedding(PositionEncoding):
     def __init__(self, spec: PositionSpec) -> None:
         super().__init__(spec)
@@ -82,7 +85,12 @@ class RotaryEmbedding(PositionEncoding):
         self._inv_freq = None
 
     def finalize(self, device, dtype) -> None:
-        self._inv_freq = self._inv_freq_host.to(device=device, dtype=torch.float32).contiguous()
+        # one device tensor for all layers with the same frequencies: constants that nothing writes, and what a step's
+        # layers share (the table of sines and cosines of many tokens) is kept by the tensor it was made from
+        key = (self.spec, str(torch.device(device)))
+        if key not in _frequencies_on_device:
+            _frequencies_on_device[key] = self._inv_freq_host.to(device=device, dtype=torch.float32).contiguous()
+        self._inv_freq = _frequencies_on_device[key]
 
     def rotary_frequencies(self):
         return self._inv_freq
