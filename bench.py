@@ -351,7 +351,8 @@ def run_ours(args):
         else:
             batch = int(args.only.split("_b")[1])
             v, ms, _, _, _ = run.device_decode(batch, args.steps, args.warmup, regions=1)
-            print(json.dumps({"only": args.only, "value": round(v, 1), "ms_per_step": round(ms, 4)}))
+            e2e, _, _ = run.host_decode(batch, args.steps, args.warmup, regions=1)
+            print(json.dumps({"only": args.only, "value": round(v, 1), "ms_per_step": round(ms, 4), "e2e": round(e2e, 1)}))
         return
     sampler = ClockSampler()
     sampler.start()
