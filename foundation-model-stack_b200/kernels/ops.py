@@ -14,7 +14,7 @@ epilogue), and the fused projection of queries, keys and values, which from ``TE
 on takes the same kernel with the rotation and the cache write in its epilogue.  The same kernel takes the plain
 products from ``FMS_B200_TC_ROWS`` rows on where that is set; measured through whole prefills the library's plain
 products are ahead, so by default it is not.
-The gated feed-forward product of 9 to 64 rows takes a tcgen05 kernel of this library with the weights on the
+The gated feed-forward product of 9 to 128 rows takes a tcgen05 kernel of this library with the weights on the
 instruction's rows and the activation in its epilogue (``gemm_bf16_mid.cu``); the same kernel can take the plain
 products and the fused projection up to 256 rows (clusters of blocks share a tile along K; projection + rotation
 + cache write in its epilogue; ``FMS_B200_MID_OPS``), where the library's product is still ahead of it.
@@ -244,13 +244,14 @@ USE_TENSOR_CORE_GEMM = os.environ.get("FMS_B200_TC_GEMM", "1") != "0"
 
 
 # The tcgen05 kernel with the weights on the instruction's rows (gemm_bf16_mid.cu), for SKINNY_ROWS + 1 to MID_ROWS
-# rows.  By default it takes the gated feed-forward product up to 64 rows, where it is ahead of the library's
+# rows.  By default it takes the gated feed-forward product up to 128 rows, where it is ahead of the library's
 # product followed by the activation kernel (a decode step of batch 16 at the 8B sizes: 3.75 against 3.86 ms; batch 32:
-# 4.59 against 4.66; batch 64: at par).  The plain products and the fused projection, whose matrices have too few
+# 4.59 against 4.66; batch 64: at par; batch 96: 6.80 against 6.90; batch 128: 7.89 against 7.93; batch 256: 13.70
+# against 12.99, hence no further).  The plain products and the fused projection, whose matrices have too few
 # rows for one block a tile and so run as clusters that add their sums, are 3 to 9 us a product behind the library
 # (batch 16: 4.02 ms with them, batch 64: 6.47) and stay with it unless FMS_B200_MID_OPS names them
 # ("linear,glu,qkv"; FMS_B200_MID_ROWS up to 256; FMS_B200_MID_GEMM=0 turns the kernel off).
-MID_ROWS = min(256, int(os.environ.get("FMS_B200_MID_ROWS", "64")))
+MID_ROWS = min(256, int(os.environ.get("FMS_B200_MID_ROWS", "128")))
 USE_MID_GEMM = os.environ.get("FMS_B200_MID_GEMM", "1") != "0"
 MID_OPS = os.environ.get("FMS_B200_MID_OPS", "glu").split(",")
 

@@ -26,7 +26,7 @@ def ops():
 @pytest.fixture
 def own_product_for_some_rows(ops):
     """Every product of 9 to 256 rows through this library's own tcgen05 kernel (by default only the gated
-    feed-forward product up to 64 rows takes it), and the own kernels for many rows whatever padding their tiles need."""
+    feed-forward product up to 128 rows takes it), and the own kernels for many rows whatever padding their tiles need."""
     saved = ops.USE_MID_GEMM, ops.MID_OPS, ops.MID_ROWS, ops.TENSOR_CORE_MAX_PADDING, ops.TENSOR_CORE_ROWS_QKV
     ops.USE_MID_GEMM, ops.MID_OPS, ops.MID_ROWS = True, ["linear", "glu", "qkv"], 256
     ops.TENSOR_CORE_MAX_PADDING, ops.TENSOR_CORE_ROWS_QKV = 10.0, 512
