@@ -1,0 +1,111 @@
+"""Schedules drawn at random (fixed seeds): batches of one to five requests of unequal lengths, each request cut
+into pieces of its own (so that one step holds a request's first 40 tokens beside another's next single token),
+requests that end while others go on, a cache with just enough blocks so that every batch takes over what the one
+before gave back, and logits wanted at random places.  Every wanted row is compared with the plain implementation's
+row for the whole request.  A hand-made schedule tests what its author thought of; these are there for the rest."""
+import random
+
+import pytest
+import torch
+
+import plain_llama as pl
+from tiny_models import TINY
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def oracles(tiny_folders):
+    return {w: pl.PlainLlama(tiny_folders[w]) for w in tiny_folders}
+
+
+@pytest.fixture(scope="module")
+def models(tiny_folders):
+    from fms_b200.models import get_model
+
+    cache = {}
+
+    def get(which, dtype):
+        if (which, dtype) not in cache:
+            cache[(which, dtype)] = get_model("hf_pretrained", model_path=tiny_folders[which], device_type="cuda",
+                                              data_type=dtype)
+        return cache[(which, dtype)]
+
+    return get
+
+
+def close(got, want, largest, dtype, what):
+    """The rule of the other engine tests: float32 to the engine's own rounding; bfloat16 to 2% of the largest logit
+    of the request (``largest``), not of the one row."""
+    want, got = want.double(), got.double().cpu()
+    tol = dict(atol=2e-5, rtol=1e-4) if dtype == "fp32" else dict(atol=0.02 * largest, rtol=0.02)
+    torch.testing.assert_close(got, want, msg=lambda m: f"{what}: {m}", **tol)
+
+
+def draw_batch(rng, vocab, top):
+    """Requests (token lists) and, for each, the sizes of the pieces it is fed in."""
+    n = rng.randint(1, 5)
+    requests, pieces = [], []
+    for _ in range(n):
+        hi = min(top, 330)
+        length = rng.choice([1, 2, rng.randint(3, min(70, hi)), rng.randint(min(60, hi), min(140, hi)), rng.randint(min(120, hi), hi)])
+        requests.append([rng.randrange(vocab) for _ in range(length)])
+        cut, left = [], length
+        first = rng.randint(1, left)  # the prompt's first piece: anything from one token to the whole request
+        cut.append(first)
+        left -= first
+        while left:
+            piece = 1 if rng.random() < 0.6 else rng.randint(1, min(left, 70))
+            cut.append(piece)
+            left -= piece
+        pieces.append(cut)
+    return requests, pieces
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("seed", range(15))
+def test_a_random_schedule_against_the_plain_implementation(models, oracles, seed, dtype):
+    rng = random.Random(1000 + seed)
+    which = "abcde"[seed % 5]
+    cfg = TINY[which][0]
+    vocab, top = cfg["vocab_size"], cfg["max_position_embeddings"]
+    engine = None
+    for batch_number in range(3):
+        requests, pieces = draw_batch(rng, vocab, top)
+        need = sum((len(r) + 63) // 64 for r in requests) * 64
+        if engine is None or engine.cache.n_blocks * 64 < need:
+            # no more blocks than the largest batch so far needs: each batch reuses what the last one gave back
+            engine = models(which, dtype).new_engine(max_tokens=need, max_slots=5)
+        want = [oracles[which].logits(r) for r in requests]
+        largest = [w.abs().max().item() for w in want]
+        slots = engine.begin(len(requests))
+        fed = [0] * len(requests)
+        turn = [0] * len(requests)
+        live = list(range(len(requests)))
+        step = 0
+        while live:
+            tokens, wanted, rows = [], [], []
+            for i in live:
+                k = pieces[i][turn[i]]
+                tokens.append(requests[i][fed[i]:fed[i] + k])
+                mode = rng.random()
+                places = list(range(k)) if mode < 0.4 else ([k - 1] if mode < 0.8 else sorted(rng.sample(range(k), rng.randint(0, min(k, 3)))))
+                wanted.append(places)
+                rows += [(i, fed[i] + p) for p in places]
+            logits = engine.step([slots[i] for i in live], tokens, wanted)
+            assert logits.shape[0] == len(rows)
+            for row, (i, p) in enumerate(rows):
+                close(logits[row], want[i][p], largest[i], dtype, f"seed {seed} model {which} batch {batch_number} step {step} request {i} "
+                                                      f"(of {len(requests[i])} tokens) position {p}")
+            done = []
+            for i in live:
+                fed[i] += pieces[i][turn[i]]
+                turn[i] += 1
+                if fed[i] == len(requests[i]):
+                    done.append(i)
+            if done:  # those that are through leave; the others go on
+                engine.release([slots[i] for i in done])
+                live = [i for i in live if i not in done]
+            step += 1
+        engine.check()
+        assert engine.cache.slots.n_held == 0
