@@ -62,21 +62,17 @@ def draw_batch(rng, vocab, top):
     return requests, pieces
 
 
-@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("seed", range(15))
-def test_a_random_schedule_against_the_plain_implementation(models, oracles, seed, dtype):
-    rng = random.Random(1000 + seed)
-    which = "abcde"[seed % 5]
-    cfg = TINY[which][0]
-    vocab, top = cfg["vocab_size"], cfg["max_position_embeddings"]
+def run_batches(rng, new_engine, plain_logits, vocab, top, dtype, label):
+    """Three batches one after another through engines from ``new_engine(max_tokens)``; every wanted row against
+    ``plain_logits(request)``."""
     engine = None
     for batch_number in range(3):
         requests, pieces = draw_batch(rng, vocab, top)
         need = sum((len(r) + 63) // 64 for r in requests) * 64
         if engine is None or engine.cache.n_blocks * 64 < need:
             # no more blocks than the largest batch so far needs: each batch reuses what the last one gave back
-            engine = models(which, dtype).new_engine(max_tokens=need, max_slots=5)
-        want = [oracles[which].logits(r) for r in requests]
+            engine = new_engine(need)
+        want = [plain_logits(r) for r in requests]
         largest = [w.abs().max().item() for w in want]
         slots = engine.begin(len(requests))
         fed = [0] * len(requests)
@@ -95,8 +91,8 @@ def test_a_random_schedule_against_the_plain_implementation(models, oracles, see
             logits = engine.step([slots[i] for i in live], tokens, wanted)
             assert logits.shape[0] == len(rows)
             for row, (i, p) in enumerate(rows):
-                close(logits[row], want[i][p], largest[i], dtype, f"seed {seed} model {which} batch {batch_number} step {step} request {i} "
-                                                      f"(of {len(requests[i])} tokens) position {p}")
+                close(logits[row], want[i][p], largest[i], dtype, f"{label} batch {batch_number} step {step} request {i} "
+                                                                  f"(of {len(requests[i])} tokens) position {p}")
             done = []
             for i in live:
                 fed[i] += pieces[i][turn[i]]
@@ -109,3 +105,30 @@ def test_a_random_schedule_against_the_plain_implementation(models, oracles, see
             step += 1
         engine.check()
         assert engine.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("seed", range(15))
+def test_a_random_schedule_against_the_plain_implementation(models, oracles, seed, dtype):
+    which = "abcde"[seed % 5]
+    cfg = TINY[which][0]
+    run_batches(random.Random(1000 + seed), lambda need: models(which, dtype).new_engine(max_tokens=need, max_slots=5),
+                oracles[which].logits, cfg["vocab_size"], cfg["max_position_embeddings"], dtype, f"seed {seed} model {which}")
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("seed", range(6))
+def test_a_random_schedule_with_windows_on_some_layers(tiny_folders, oracles, seed, dtype):
+    """The same with layers that keep a window of keys (a test's variation of the model): the windowed group of the
+    cache gives blocks back while a request runs and takes them again for the next, beside a group that keeps all."""
+    from test_engine_gpu import plain_windowed_logits, windowed_model
+
+    which = "cd"[seed % 2]
+    cfg = TINY[which][0]
+    layers = cfg["num_hidden_layers"]
+    windows = [[40, 0], [0, 33], [70, 70]][seed % 3]
+    windows = (windows * layers)[:layers]
+    model = windowed_model(tiny_folders[which], dtype, windows)
+    run_batches(random.Random(2000 + seed), lambda need: model.new_engine(max_tokens=need, max_slots=5),
+                lambda r: plain_windowed_logits(oracles[which], r, windows), cfg["vocab_size"],
+                cfg["max_position_embeddings"], dtype, f"seed {seed} model {which} windows {windows}")
