@@ -132,3 +132,29 @@ def test_a_random_schedule_with_windows_on_some_layers(tiny_folders, oracles, se
     run_batches(random.Random(2000 + seed), lambda need: model.new_engine(max_tokens=need, max_slots=5),
                 lambda r: plain_windowed_logits(oracles[which], r, windows), cfg["vocab_size"],
                 cfg["max_position_embeddings"], dtype, f"seed {seed} model {which} windows {windows}")
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_requests_through_generate_with_stop_tokens_and_small_batches(models, oracles, seed):
+    """More requests than a batch holds, of unequal lengths, greedy; two stop tokens chosen so that some requests
+    end early (the tokens that the plain implementation emits third for one request and sixth for another).  Each
+    request's tokens equal the plain loop's, whatever batch it fell into."""
+    from fms_b200.utils.generation import generate
+
+    rng = random.Random(3000 + seed)
+    which = "bcde"[seed % 4]
+    cfg = TINY[which][0]
+    top = min(cfg["max_position_embeddings"], 200) - 12
+    prompts = [[rng.randrange(cfg["vocab_size"]) for _ in range(rng.choice([1, 2, rng.randint(3, top)]))]
+               for _ in range(rng.randint(3, 7))]
+    free = [pl.plain_generate(oracles[which], p, 10) for p in prompts]
+    stop = [free[0][len(prompts[0]) + 2], free[1][len(prompts[1]) + 5]]
+    want = [pl.plain_generate(oracles[which], p, 10, eos=stop) for p in prompts]
+    assert any(len(w) < len(p) + 10 for w, p in zip(want, prompts))  # some do end early
+    model = models(which, "fp32")
+    for batch_size in (None, rng.randint(1, 3)):
+        out = generate(model, [torch.tensor(p) for p in prompts], max_new_tokens=10, do_sample=False, eos_token_id=stop,
+                       batch_size=batch_size)
+        assert [o.tolist() for o in out] == want
+    engine = model.engine()
+    assert engine.cache.slots.n_held == 0
