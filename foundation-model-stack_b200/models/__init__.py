@@ -134,5 +134,21 @@ def get_model(architecture: str, variant: Optional[str] = None, model_path: Opti
 
 from . import llama  # noqa: E402,F401  (registers the architecture and its variants)
 
+
+def _import_plugins() -> None:
+    """Modules named in FMS_B200_PLUGINS (comma-separated, importable names) are imported once the built-in
+    architectures are registered: an architecture, part or adapter that lives outside this library registers itself
+    there, and the command-line programs (which find the model class through config.json) then know it."""
+    import importlib
+
+    for name in filter(None, (n.strip() for n in os.environ.get("FMS_B200_PLUGINS", "").split(","))):
+        try:
+            importlib.import_module(name)
+        except Exception as e:
+            raise ImportError(f"FMS_B200_PLUGINS names {name!r}, which cannot be imported: {e}") from e
+
+
+_import_plugins()
+
 __all__ = ["Model", "get_model", "list_models", "list_variants", "register_architecture", "register_model",
            "read_config_json"]

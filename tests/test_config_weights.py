@@ -367,3 +367,20 @@ def test_meta_named_checkpoint_loads_like_the_hf_one(tmp_path, tiny_folders):
     a = get_model("llama", model_path=tiny_folders["a"], source="hf", device_type="cpu", data_type="bf16").state_dict()
     b = get_model("llama", model_path=folder, source="meta", device_type="cpu", data_type="bf16").state_dict()
     assert sorted(a) == sorted(b) and all(torch.equal(a[k], b[k]) for k in a)
+
+
+def test_a_plugin_module_that_cannot_be_imported_is_named_in_the_error(tmp_path):
+    """FMS_B200_PLUGINS: modules that register architectures or parts from outside the library."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    (tmp_path / "a_plugin_of_a_test.py").write_text(
+        "from fms_b200 import models\nmodels.register_model('llama', 'from_a_plugin', lambda **kw: None)\n")
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([str(tmp_path), root]), FMS_B200_PLUGINS="a_plugin_of_a_test")
+    code = "from fms_b200 import models; print('from_a_plugin' in models.list_variants('llama'))"
+    ok = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=300)
+    assert ok.returncode == 0 and ok.stdout.strip() == "True", ok.stderr[-1000:]
+    env["FMS_B200_PLUGINS"] = "a_plugin_of_a_test, no_such_module_anywhere"
+    bad = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=300)
+    assert bad.returncode != 0 and "no_such_module_anywhere" in bad.stderr and "FMS_B200_PLUGINS" in bad.stderr

@@ -226,3 +226,36 @@ def test_a_checkpoint_of_the_toy_architecture_with_a_missing_and_a_misshapen_ten
         get_model("hf_pretrained", model_path=str(tmp_path / "broken"), device_type="cuda", data_type="fp32")
     text = str(e.value)
     assert "base_model.layers.1.ff_ln.weight" in text and "stray" in text and "base_model.layers.2.ff_sub_layer.w2.weight" in text
+
+
+def test_the_trace_program_finds_the_toy_architecture_through_a_plugin_module(toy_folder, tmp_path):
+    """bin/trace_run is a process of its own: it knows the architecture because FMS_B200_PLUGINS names a module that
+    registers it (here a two-line module that calls this file's registration)."""
+    import subprocess
+    import sys
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    (tmp_path / "toy_plugin_of_a_test.py").write_text(
+        "import test_toy_architecture_gpu as t\nt.register_toy_architecture()\n")
+    ids = [3, 60, 17, 17, 42, 8, 0, 25]
+    steps = [{"step": 0, "entries": [{"id": "r", "tokens": ids[:5], "want": [0, 4]}], "end": []},
+             {"step": 1, "entries": [{"id": "r", "tokens": ids[5:6], "want": [0]}], "end": []},
+             {"step": 2, "entries": [{"id": "r", "tokens": ids[6:], "want": [1]}], "end": ["r"]}]
+    env = dict(os.environ, FMS_B200_PLUGINS="toy_plugin_of_a_test",
+               PYTHONPATH=os.pathsep.join([str(tmp_path), here, os.environ.get("PYTHONPATH", "")]))
+    proc = subprocess.run(
+        [sys.executable, os.path.join(os.path.dirname(here), "bin", "trace_run"), "--model", toy_folder, "--dtype", "float32",
+         "--out", str(tmp_path / "out"), "--max-tokens", "64"],
+        input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600, env=env)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split() == ["done", "0", "done", "1", "done", "2"]
+    want = plain_toy_logits(toy_folder, ids)
+    got = torch.cat([torch.from_numpy(np.fromfile(tmp_path / "out" / f"{s}.f32", dtype="<f4").reshape(-1, 61).copy())
+                     for s in range(3)])
+    torch.testing.assert_close(got.double(), want[[0, 4, 5, 7]], atol=2e-4, rtol=1e-4)
+    # without the plugin the program says which architectures it knows
+    env.pop("FMS_B200_PLUGINS")
+    proc = subprocess.run(
+        [sys.executable, os.path.join(os.path.dirname(here), "bin", "trace_run"), "--model", toy_folder, "--dtype", "float32",
+         "--out", str(tmp_path / "out2"), "--max-tokens", "64"], input="", capture_output=True, text=True, timeout=600, env=env)
+    assert proc.returncode != 0 and "ToyStackForTests" in proc.stderr and "LlamaForCausalLM" in proc.stderr
