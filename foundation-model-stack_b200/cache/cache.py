@@ -61,11 +61,14 @@ class KVGroup:
         self.layers = list(layers)
         self.pool = BlockPool(n_blocks)
         self.blocks_per_sequence = blocks_per_sequence
+        # one block and one table row more than the pool and the slots hand out: the spare slot (row max_slots) with
+        # the spare block (n_blocks) at its first position, where a step's filler rows write and read
         self.storage = torch.zeros(
-            (len(self.layers), 2, n_blocks, request.kvheads, BLOCK_TOKENS, request.head_dim), dtype=dtype, device=device
+            (len(self.layers), 2, n_blocks + 1, request.kvheads, BLOCK_TOKENS, request.head_dim), dtype=dtype, device=device
         )
-        self.table_host = torch.full((max_slots, blocks_per_sequence), -1, dtype=torch.int32)
-        self.table = torch.full((max_slots, blocks_per_sequence), -1, dtype=torch.int32, device=device)
+        self.table_host = torch.full((max_slots + 1, blocks_per_sequence), -1, dtype=torch.int32)
+        self.table_host[max_slots, 0] = n_blocks
+        self.table = self.table_host.to(device)
         self._dirty: set = set()
 
     def held_blocks(self, slot: int) -> List[int]:
@@ -142,8 +145,8 @@ class StateGroup:
                  device: torch.device) -> None:
         self.request = request
         self.layers = list(layers)
-        self.storage = torch.zeros(
-            (len(self.layers), max_slots) + tuple(request.shape), dtype=request.dtype or dtype, device=device
+        self.storage = torch.zeros(  # one row more than there are slots: the spare slot's
+            (len(self.layers), max_slots + 1) + tuple(request.shape), dtype=request.dtype or dtype, device=device
         )
 
     def reset(self, slot: int) -> None:
@@ -170,6 +173,9 @@ class Cache:
         self.max_slots = int(max_slots) if max_slots else n_blocks
         self.blocks_per_sequence = round_up(self.max_positions, BLOCK_TOKENS) // BLOCK_TOKENS
         self.slots = SlotAllocator(self.max_slots)
+        # A slot that no sequence gets, with one block of its own in every group: rows that only fill a decode step up
+        # to a size for which a graph is captured live there, at position 0, and what they compute is thrown away.
+        self.spare_slot = self.max_slots
         # fixed-size state that every sequence has, whatever the architecture: its length (tokens in the
         # cache) and the position of its next token, which is what a position encoding sees.  They differ
         # by the position at which the sequence started (``begin(n, first_positions)``), 0 by default.

@@ -472,23 +472,27 @@ FMS_API int fms_rotary_table(const float* inv_freq, const int* positions, const 
 // position its encoding sees is that place plus the offset at which the sequence started (offsets null: none)
 // ---------------------------------------------------------------------------------------------------
 __global__ void decode_advance_kernel(int* __restrict__ positions, int* __restrict__ lengths,
-                                      const int* __restrict__ offsets, int* __restrict__ position_ids, int n) {
+                                      const int* __restrict__ offsets, int* __restrict__ position_ids,
+                                      const int* __restrict__ slots, int spare_slot, int n) {
   pdl_launch_dependents();
   pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) {
-    const int len = lengths[i];
+    // a row that only fills the step up to a size with a captured graph sits in the cache's spare slot and stays at
+    // its first position, whatever the array held
+    const int len = (slots != nullptr && slots[i] == spare_slot) ? 0 : lengths[i];
     positions[i] = len;
     lengths[i] = len + 1;
     if (offsets != nullptr) position_ids[i] = len + offsets[i];
   }
 }
 
-FMS_API int fms_decode_advance(int* positions, int* lengths, const int* offsets, int* position_ids, int n,
-                               cudaStream_t stream) {
+// slots, spare_slot: rows whose slot is spare_slot restart at position 0 every step (slots null: no such rows)
+FMS_API int fms_decode_advance(int* positions, int* lengths, const int* offsets, int* position_ids, const int* slots,
+                               int spare_slot, int n, cudaStream_t stream) {
   if (n <= 0) return 0;
   if ((offsets == nullptr) != (position_ids == nullptr)) return fms_fail("decode_advance: offsets without position_ids");
   fms_launch(decode_advance_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, positions, lengths, offsets, position_ids,
-             n);
+             slots, spare_slot, n);
   return fms_launch_status("decode_advance");
 }

@@ -9,6 +9,9 @@ left-padded rectangle with a mask; here rows are ragged, nothing is padded and c
 A step in which every sequence brings one token and wants its logits is a decode step.  It runs the same
 kernels as any other step, but from arrays that stay on the device (tokens, positions, lengths, slots)
 and, from its second occurrence on, as one CUDA graph launch instead of some hundred kernel launches.
+More than eight sequences are filled up to the next of a few sizes (12, 16, 24, 32, 48, 64, ...) with rows that
+live in the cache's spare slot and whose results are thrown away, so that a batch whose sequences end one by one
+goes on through a handful of captured graphs instead of capturing one for every number of sequences.
 """
 from __future__ import annotations
 
@@ -25,10 +28,23 @@ from .batch import Batch
 _REQUIRE_CUDA = True
 
 
-class _DecodeBuffers:
-    """Device arrays of decode steps of n sequences, and the CUDA graphs captured over them."""
+def decode_rows(n: int) -> int:
+    """Rows of the decode step that n sequences take: n up to 8 (the weight-streaming products take 1 to 8 rows as
+    they are), else the next of 12, 16, 24, 32, 48, 64, 96, 128, ... (a power of two, or one and a half)."""
+    if n <= 8:
+        return n
+    size = 8
+    while True:
+        for rows in (size + size // 2, 2 * size):
+            if rows >= n:
+                return rows
+        size *= 2
 
-    def __init__(self, n: int, device) -> None:
+
+class _DecodeBuffers:
+    """Device arrays of decode steps of n rows, and the CUDA graphs captured over them."""
+
+    def __init__(self, n: int, device, spare_slot: int) -> None:
         self.n = n
         ar = torch.arange(n + 1, dtype=torch.int32, device=device)
         self.batch = Batch()
@@ -39,7 +55,7 @@ class _DecodeBuffers:
         b.positions = torch.zeros(n, dtype=torch.int32, device=device)
         b.token_seq = ar[:n].clone()
         b.first_row = ar
-        b.slots = torch.zeros(n, dtype=torch.int32, device=device)
+        b.slots = torch.full((n,), spare_slot, dtype=torch.int32, device=device)
         b.len_after = torch.zeros(n, dtype=torch.int32, device=device)  # between steps: the current lengths
         # for sequences that did not start at position 0: what the encoding sees (batch.position_ids points at it
         # while any of the loaded sequences has an offset, else stays None)
@@ -77,6 +93,9 @@ class Engine:
         self.cache = Cache(self.decoder.cache_requests(), max_tokens, self.decoder.spec.max_positions,
                            self.decoder.dtype, self.device, max_slots)
         self.use_graphs = use_graphs and self.device.type == "cuda"
+        # decode steps of more than 8 sequences are filled up to one of a few sizes (``decode_rows``): it pays where a
+        # size means a captured graph
+        self.fill_rows = self.use_graphs
         self.max_graphs = max(1, int(max_graphs))
         self._decode: Dict[int, _DecodeBuffers] = {}
         # (sequences, bound on their lengths, with position offsets) -> (graph, logits), least recently used first
@@ -147,9 +166,10 @@ class Engine:
         for s in slots:
             if not self.cache.slots.is_held(s):
                 raise ValueError(f"slot {s} is not held")
-        buf = self._decode.get(n)
+        rows = decode_rows(n) if self.fill_rows else n  # rows beyond n only fill the step up to a captured size
+        buf = self._decode.get(rows)
         if buf is None:
-            buf = self._decode[n] = _DecodeBuffers(n, self.device)
+            buf = self._decode[rows] = _DecodeBuffers(rows, self.device, self.cache.spare_slot)
         key = tuple(slots)
         lengths = [self.cache.length[s] for s in slots]
         self.cache.prepare_decode(slots)
@@ -157,19 +177,21 @@ class Engine:
             buf.copied.synchronize()  # the last copy out of the pinned array is over
         if buf.loaded != key or buf.lengths != lengths:
             offsets = [self.cache.offset(s) for s in slots]
-            state = torch.tensor([list(slots), lengths, offsets], dtype=torch.int32)
+            fill = rows - n
+            state = torch.tensor([list(slots) + [self.cache.spare_slot] * fill, lengths + [0] * fill, offsets + [0] * fill],
+                                 dtype=torch.int32)
             buf.batch.slots.copy_(state[0])
             buf.batch.len_after.copy_(state[1])
             buf.offsets.copy_(state[2])
             buf.batch.position_ids = buf.position_ids if any(offsets) else None
             buf.loaded, buf.lengths = key, lengths
-            self.h2d_bytes += 12 * n
+            self.h2d_bytes += 12 * rows
         if tokens_device is not None:
-            buf.batch.tokens.copy_(tokens_device)
+            buf.batch.tokens[:n].copy_(tokens_device)
         else:
-            buf.tokens_np[:] = tokens
+            buf.tokens_np[:n] = tokens  # the filler rows keep whatever valid token they had (0 at first)
             buf.batch.tokens.copy_(buf.tokens_host, non_blocking=True)
-            self.h2d_bytes += 4 * n
+            self.h2d_bytes += 4 * rows
             if self.device.type == "cuda":
                 if buf.copied is None:
                     buf.copied = torch.cuda.Event()
@@ -183,13 +205,14 @@ class Engine:
             raise
         self.cache.commit(slots, [1] * n)
         buf.lengths = [x + 1 for x in lengths]
-        return logits
+        return logits if rows == n else logits[:n]
 
     def _decode_body(self, buf: _DecodeBuffers) -> torch.Tensor:
+        spare = self.cache.spare_slot
         if buf.batch.position_ids is None:
-            ops.decode_advance(buf.batch.positions, buf.batch.len_after)
+            ops.decode_advance(buf.batch.positions, buf.batch.len_after, None, None, buf.batch.slots, spare)
         else:
-            ops.decode_advance(buf.batch.positions, buf.batch.len_after, buf.offsets, buf.position_ids)
+            ops.decode_advance(buf.batch.positions, buf.batch.len_after, buf.offsets, buf.position_ids, buf.batch.slots, spare)
         return self.decoder.forward(buf.batch, self.cache)
 
     def _run_decode(self, buf: _DecodeBuffers, longest: int) -> torch.Tensor:

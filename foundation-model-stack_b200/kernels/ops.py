@@ -37,7 +37,7 @@ _SIGNATURES = {
     "fms_add_rmsnorm": [_P, _P, _P, _I, _F, _P, _I, _P, _I, _I, _I, _P],
     "fms_gated_activation": [_P, _P, _I, _I, _I, _I, _P],
     "fms_rope_store": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _I, _P],
-    "fms_decode_advance": [_P, _P, _P, _P, _I, _P],
+    "fms_decode_advance": [_P, _P, _P, _P, _P, _I, _I, _P],
     "fms_rotary_table": [_P, _P, _P, _P, _I, _I, _P],
     "fms_gemm_f32": [_P, _P, _P, _P, _I, _I, _I, _P],
     "fms_linear_bf16_skinny": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
@@ -465,11 +465,14 @@ def attention_stream_launches(head_dim: int) -> int:
 
 
 def decode_advance(positions: torch.Tensor, lengths: torch.Tensor, offsets: Optional[torch.Tensor] = None,
-                   position_ids: Optional[torch.Tensor] = None) -> None:
+                   position_ids: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
+                   spare_slot: int = -1) -> None:
     """positions[i] = lengths[i]; lengths[i] += 1 — the bookkeeping of a decode step, on the device.  With
-    ``offsets`` (sequences that did not start at position 0) also position_ids[i] = positions[i] + offsets[i]."""
+    ``offsets`` (sequences that did not start at position 0) also position_ids[i] = positions[i] + offsets[i].
+    With ``slots``: a row in ``spare_slot`` (one that only fills the step up to a captured size) restarts at
+    position 0 every step."""
     _call("elementwise", "fms_decode_advance", _ptr(positions), _ptr(lengths), _ptr(offsets), _ptr(position_ids),
-          positions.shape[0], _stream())
+          _ptr(slots), int(spare_slot), positions.shape[0], _stream())
 
 
 # ---- sampling ----------------------------------------------------------------------------------------

@@ -108,7 +108,9 @@ def attention(q, batch, view, nheads, kvheads, head_dim, scale, window):
     return out
 
 
-def decode_advance(positions, lengths, offsets=None, position_ids=None):
+def decode_advance(positions, lengths, offsets=None, position_ids=None, slots=None, spare_slot=-1):
+    if slots is not None:
+        lengths.masked_fill_(slots == spare_slot, 0)
     positions.copy_(lengths)
     if offsets is not None:
         position_ids.copy_(lengths + offsets)

@@ -62,8 +62,10 @@ def test_cache_lengths_blocks_groups_and_reuse():
     assert len(c.groups) == 3  # layers 0 and 1 share a group; the windowed layer and the state have their own
     full, win, state = c.groups
     assert full.layers == [0, 1] and win.layers == [2] and state.layers == [4]
-    assert full.storage.shape == (2, 2, 6, 2, 64, 16) and state.storage.shape == (1, 3, 3, 4)
-    assert c.layer_view(3) is None and c.layer_view(0).keys.shape == (6, 2, 64, 16)
+    # one block and one slot more than are handed out: the spare slot with its block, for a step's filler rows
+    assert full.storage.shape == (2, 2, 7, 2, 64, 16) and state.storage.shape == (1, 4, 3, 4)
+    assert c.layer_view(3) is None and c.layer_view(0).keys.shape == (7, 2, 64, 16)
+    assert c.spare_slot == 3 and full.table_host[3].tolist()[:2] == [6, -1] and full.pool.n_blocks == 6
     s0, s1 = c.begin(2)
     state.storage[0, s0] = 1.0
     assert c.prepare([s0, s1], [100, 5]) == [0, 0]

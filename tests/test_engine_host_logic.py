@@ -144,3 +144,41 @@ def test_generate_honours_the_offset_of_padded_position_ids(tiny_folders):
     for row, p in zip(out, prompts):
         got = row.tolist()[ids.shape[1] - len(p):]
         assert got == pl.plain_generate(oracle, p, 4, first_position=9)
+
+
+def test_decode_steps_filled_up_to_a_captured_size_change_no_result(tiny_folders):
+    """Eleven sequences decode as twelve rows, nine as twelve, then (two ended) seven as seven: the filler row lives in
+    the cache's spare slot and its block; the live sequences' logits are those of the plain implementation, no block
+    of the pool is taken for the filler, and the arrays on the device are brought anew when the live set changes."""
+    from fms_b200.engine.step import decode_rows
+
+    assert [decode_rows(n) for n in (1, 8, 9, 12, 13, 17, 33, 49, 64, 65, 100, 129)] == [1, 8, 12, 12, 16, 24, 48, 64, 64, 96, 128, 192]
+    oracle = pl.PlainLlama(tiny_folders["b"])
+    g = torch.Generator().manual_seed(4)
+    reqs = [torch.randint(0, 384, (int(k) + 8,), generator=g).tolist() for k in torch.randint(1, 40, (11,), generator=g)]
+    with use_plain_ops():
+        engine = _model(tiny_folders["b"]).new_engine(max_tokens=64 * 11, max_slots=11)
+        engine.fill_rows = True  # as on a GPU, where a size means a captured graph
+        slots = engine.begin(11)
+        engine.step(slots, [r[:-8] for r in reqs])
+        live = list(range(11))
+        got = {i: [] for i in live}
+        for t in range(8):
+            if t == 3:
+                engine.release([slots[2], slots[9]])
+                live = [i for i in live if i not in (2, 9)]
+            if t == 6:
+                engine.release([slots[0], slots[5]])
+                live = [i for i in live if i not in (0, 5)]
+            lg = engine.decode([slots[i] for i in live], [reqs[i][len(reqs[i]) - 8 + t] for i in live])
+            assert lg.shape[0] == len(live)
+            for row, i in enumerate(live):
+                got[i].append(lg[row].clone())
+            assert all(gr.pool.n_held == sum((engine.cache.length[slots[i]] + 63) // 64 for i in live)
+                       for gr in engine.cache.groups)
+        assert sorted(engine._decode) == [7, 12]
+        engine.release([slots[i] for i in live])
+        assert engine.cache.slots.n_held == 0 and all(gr.pool.n_held == 0 for gr in engine.cache.groups)
+    for i, r in enumerate(reqs):
+        want = oracle.logits(r)[len(r) - 8:][: len(got[i])]
+        torch.testing.assert_close(torch.stack(got[i]).double(), want, atol=2e-5, rtol=1e-4)
