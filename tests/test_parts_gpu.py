@@ -432,6 +432,30 @@ def test_toy_mixer_with_state_and_routed_feed_forward_are_registered_built_and_s
     assert engine.graph_launches > 0
 
 
+def test_toy_parts_in_decode_steps_that_are_filled_up_with_rows_in_the_spare_slot():
+    """Ten sequences decode as twelve rows: the two filler rows go through the toy mixer too, where they find a row
+    of state of their own (the spare slot's) and touch no sequence's; then seven of the ten go on."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    model, spec = toy_model(torch.float32)
+    engine = model.new_engine(max_tokens=64 * 10, max_slots=10)
+    g = torch.Generator().manual_seed(9)
+    reqs = [torch.randint(0, 97, (int(k),), generator=g).tolist() for k in torch.randint(9, 40, (10,), generator=g)]
+    want = [plain_toy(model, r) for r in reqs]
+    slots = engine.begin(10)
+    engine.step(slots, [r[:-8] for r in reqs], [[] for _ in reqs])
+    live = list(range(10))
+    for t in range(8):
+        if t == 5:
+            engine.release([slots[i] for i in (1, 4, 8)])
+            live = [i for i in live if i not in (1, 4, 8)]
+        lg = engine.step([slots[i] for i in live], [[reqs[i][len(reqs[i]) - 8 + t]] for i in live])
+        for row, i in enumerate(live):
+            close(lg[row:row + 1], want[i][len(reqs[i]) - 8 + t][None], torch.float32)
+    assert sorted(engine._decode) == [7, 12] and engine.graph_launches > 0
+    engine.release([slots[i] for i in live])
+    engine.check()
+
+
 # ---------------------------------------------------------------------------------------------------
 # another arrangement of a layer, scales at both ends of the decoder, sequences that start at other positions
 # ---------------------------------------------------------------------------------------------------
