@@ -248,6 +248,22 @@ class Engine:
         self.graph_launches += 1
         return entry[1]
 
+    def warm_up(self, sizes: Sequence[int], horizon: int) -> None:
+        """Captures the decode graphs of the given numbers of sequences ahead of the first request: two steps of
+        throw-away sequences each (the first runs uncaptured, the second captures).  ``horizon``: the longest a
+        sequence will get, as ``decode`` takes it (graphs are kept per bound on the lengths, a power of two of 256)."""
+        if not self.use_graphs:
+            return
+        for n in sorted(set(decode_rows(int(k)) for k in sizes)):
+            if n > self.cache.slots.n_free:
+                raise ValueError(f"warm_up: {n} sequences, {self.cache.slots.n_free} slots free")
+            slots = self.begin(n)
+            try:
+                for _ in range(2):
+                    self.decode(slots, [0] * n, horizon=horizon)
+            finally:
+                self.release(slots)
+
     def check(self) -> None:
         """Raises if a kernel met something the host should have prevented (synchronises)."""
         ops.check_error_flag(self.device)

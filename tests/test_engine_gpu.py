@@ -334,6 +334,24 @@ def test_a_batch_whose_requests_end_one_by_one_keeps_few_graphs(models, oracles)
     engine.check()
 
 
+def test_warm_up_captures_the_graphs_before_the_first_request(models, oracles):
+    model = models("b", "fp32")
+    engine = model.new_engine(max_tokens=64 * 2 * 12, max_slots=12)
+    engine.warm_up([1, 3, 10], horizon=100)
+    assert engine.graphs_captured == 3 and engine.cache.slots.n_held == 0 and sorted(engine._decode) == [1, 3, 12]
+    assert all(g.pool.n_held == 0 for g in engine.cache.groups)
+    reqs = long_requests("b", 3)
+    slots = engine.begin(3)
+    engine.step(slots, [r[:-2] for r in reqs], [[] for _ in reqs])
+    launched = engine.graph_launches
+    got = [engine.decode(slots, [r[-2 + t] for r in reqs], horizon=100).clone() for t in range(2)]
+    assert engine.graph_launches == launched + 2 and engine.graphs_captured == 3  # replayed from the first step on
+    engine.release(slots)
+    for i, r in enumerate(reqs):
+        close(torch.stack([got[0][i], got[1][i]]), oracles["b"].logits(r)[-2:], "fp32")
+    engine.check()
+
+
 def _trace_lines(reqs, prefill):
     """Steps of one batch: prompts together, then one token each; shorter requests end earlier."""
     lines, step = [], 0
