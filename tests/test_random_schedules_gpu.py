@@ -160,22 +160,14 @@ def test_random_requests_through_generate_with_stop_tokens_and_small_batches(mod
     assert engine.cache.slots.n_held == 0
 
 
-@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("seed", range(4))
-def test_random_batches_of_many_sequences_that_end_at_random_times(models, oracles, seed, dtype):
-    """Nine to twenty sequences decode together and leave at random steps: their steps are filled up to 12, 16 or 24
-    rows with rows in the cache's spare slot, and the live set changes under the captured graphs.  Two batches through
-    the same engine; every logit against the plain implementation."""
-    rng = random.Random(4000 + seed)
-    which = "bcde"[seed % 4]
-    cfg = TINY[which][0]
-    top = min(cfg["max_position_embeddings"], 128)
-    engine = models(which, dtype).new_engine(max_tokens=64 * 2 * 20, max_slots=20)
+def run_shrinking_batches(rng, engine, plain_logits, vocab, top, dtype, label):
+    """Two batches of nine to twenty sequences: the prompts in one step, then one token each, the sequences leaving at
+    random steps; every logit against ``plain_logits(request)``."""
     for batch_number in range(2):
         n = rng.randint(9, 20)
-        requests = [[rng.randrange(cfg["vocab_size"]) for _ in range(rng.randint(2, top))] for _ in range(n)]
+        requests = [[rng.randrange(vocab) for _ in range(rng.randint(2, top))] for _ in range(n)]
         prompt = [rng.randint(1, len(r) - 1) for r in requests]
-        want = [oracles[which].logits(r) for r in requests]
+        want = [plain_logits(r) for r in requests]
         largest = [w.abs().max().item() for w in want]
         slots = engine.begin(n)
         engine.step(slots, [r[:p] for r, p in zip(requests, prompt)], [[] for _ in requests])
@@ -186,8 +178,8 @@ def test_random_batches_of_many_sequences_that_end_at_random_times(models, oracl
             logits = engine.step([slots[i] for i in live], [[requests[i][at[i]]] for i in live])
             sizes.add(len(live))
             for row, i in enumerate(live):
-                close(logits[row], want[i][at[i]], largest[i], dtype, f"seed {seed} model {which} batch {batch_number} "
-                                                                     f"request {i} position {at[i]} among {len(live)}")
+                close(logits[row], want[i][at[i]], largest[i], dtype, f"{label} batch {batch_number} request {i} "
+                                                                     f"position {at[i]} among {len(live)}")
                 at[i] += 1
             done = [i for i in live if at[i] == len(requests[i])]
             if done:
@@ -196,3 +188,30 @@ def test_random_batches_of_many_sequences_that_end_at_random_times(models, oracl
         engine.check()
         assert engine.cache.slots.n_held == 0 and all(g.pool.n_held == 0 for g in engine.cache.groups)
         assert max(sizes) > 8 and not set(engine._decode) - {1, 2, 3, 4, 5, 6, 7, 8, 12, 16, 24}
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("seed", range(4))
+def test_random_batches_of_many_sequences_that_end_at_random_times(models, oracles, seed, dtype):
+    """Nine to twenty sequences decode together and leave at random steps: their steps are filled up to 12, 16 or 24
+    rows with rows in the cache's spare slot, and the live set changes under the captured graphs.  Two batches through
+    the same engine; every logit against the plain implementation."""
+    which = "bcde"[seed % 4]
+    cfg = TINY[which][0]
+    engine = models(which, dtype).new_engine(max_tokens=64 * 2 * 20, max_slots=20)
+    run_shrinking_batches(random.Random(4000 + seed), engine, oracles[which].logits, cfg["vocab_size"],
+                          min(cfg["max_position_embeddings"], 128), dtype, f"seed {seed} model {which}")
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_many_sequences_that_end_at_random_times_with_windows_on_some_layers(tiny_folders, oracles, dtype):
+    """The same where one layer keeps a window of 40 keys and the other all: the filler rows sit in the spare slot
+    of both groups of the cache."""
+    from test_engine_gpu import plain_windowed_logits, windowed_model
+
+    cfg = TINY["d"][0]
+    windows = [40, 0]
+    engine = windowed_model(tiny_folders["d"], dtype, windows).new_engine(max_tokens=64 * 2 * 20, max_slots=20)
+    assert len(engine.cache.groups) == 2
+    run_shrinking_batches(random.Random(5000), engine, lambda r: plain_windowed_logits(oracles["d"], r, windows),
+                          cfg["vocab_size"], 128, dtype, f"model d windows {windows}")
