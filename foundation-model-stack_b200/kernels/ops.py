@@ -88,7 +88,13 @@ def _call(library: str, name: str, *args):
         raise KernelError(f"{name}: {lib.fms_last_error().decode(errors='replace')}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current stream's handle (the direct getter where torch has it: a step makes some hundred launches)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
