@@ -11,7 +11,8 @@ pinned host-to-device copy of every step's tokens and a device-to-host read of e
 timed region), again the median of 5 regions of K steps.  ``prefill``: one prompt of 2,048 tokens.
 ``roofline``: the bytes a decode step has to read (every weight it uses once, and the cache of the live
 requests) over its time, against the measured copy bandwidth.  ``points``: tokens a second of decode at batch
-1, 16, 32 and 64, of decode at batch 8 with 7,000 to 8,000 cached tokens a request, of prefills of 512 and 8,192
+1, 16, 32 and 64, of a batch of 64 of which one sequence ends every third step (down to 16; by the clock, host
+tokens in, the live set changing under the captured graphs), of decode at batch 8 with 7,000 to 8,000 cached tokens a request, of prefills of 512 and 8,192
 tokens, and of the benchmark's further configurations (decode at batch 8 and a prefill of 2,048 tokens for the
 Llama-2-7B and Llama-2-13B shapes, decode at batch 8 in float32); ``points_frac``: each point's fraction of its
 roofline (copy bandwidth for decode, the dtype's arithmetic peak for prefill).  Weights (15 GB a step) are
@@ -292,6 +293,39 @@ class Measured:
             engine.release(slots)
         return batch / (ms / 1e3), ms, context, launched, per_region
 
+    def ending_decode(self, batch=64, every=3, until=16):
+        """Tokens a second of a batch whose sequences end one by one (one every ``every`` steps, down to ``until``):
+        host tokens in and out as a generation loop has them, timed by the clock from the first decode step to the
+        last, the second of two passes (the first leaves the graphs of the sizes captured, as a running engine has them)."""
+        import random as _random
+        import time as _time
+
+        torch, engine = self.torch, self.engine
+        lengths = prompt_lengths(batch)
+        prompts = random_prompts(lengths, self.m["vocab"])
+        value = 0.0
+        for _ in range(2):
+            rng = _random.Random(3)
+            slots = engine.begin(batch)
+            live = list(slots)
+            try:
+                engine.step(slots, prompts)
+                horizon = max(lengths) + every * batch
+                torch.cuda.synchronize()
+                start, done, step = _time.perf_counter(), 0, 0
+                while len(live) > until:
+                    step += 1
+                    if step % every == 0:
+                        engine.release([live.pop(rng.randrange(len(live)))])
+                    engine.decode(live, [1] * len(live), horizon=horizon)
+                    done += len(live)
+                torch.cuda.synchronize()
+                value = done / (_time.perf_counter() - start)
+                engine.check()
+            finally:
+                engine.release(live)
+        return value
+
     def host_decode(self, batch, steps, warmup, regions=REGIONS):
         """The same through generate(): host token lists in, host tokens out, every step."""
         from fms_b200.utils.generation import generate
@@ -372,6 +406,7 @@ def run_ours(args):
     side = max(32, args.steps // 2)
     for b in (1, 16, 32, 64):
         decode_point(f"decode_b{b}", run, b, side)
+    points["decode_b64_ending_one_by_one"] = round(run.ending_decode(), 1)
     pf_ms = run.prefill(PREFILL_TOKENS)
     prefill_point("prefill_512", run, 512)
     if long_context:
