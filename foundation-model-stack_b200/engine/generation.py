@@ -113,11 +113,30 @@ def plan_batches(lengths: Sequence[int], max_new_tokens: int, batch_size: Option
     return batches
 
 
+# The most prompt tokens of one step: the prompts of a batch run together up to this many tokens, else a few sequences
+# at a time, so that the step's intermediate tensors (a few tens of KB a token at the 8B sizes) stay bounded.
+PROMPT_TOKENS_PER_STEP = 65536
+
+
+def prompt_groups(lengths: Sequence[int], most: int) -> List[List[int]]:
+    """Consecutive sequences packed into groups of at most ``most`` tokens (a longer prompt is a group of its own)."""
+    groups: List[List[int]] = []
+    total = 0
+    for i, n in enumerate(lengths):
+        if not groups or total + n > most:
+            groups.append([])
+            total = 0
+        groups[-1].append(i)
+        total += n
+    return groups
+
+
 def generate_batch(engine, sampler: Sampler, prompts: Sequence[Sequence[int]], requests: Sequence[int],
                    max_new_tokens: int, stop_tokens: Sequence[int] = (),
                    post_iteration_hook: Optional[Callable] = None, times: Optional[List[float]] = None,
                    first_positions: Optional[Sequence[int]] = None) -> List[List[int]]:
-    """One batch of sequences that start together: the prompts in one step, then one token each until
+    """One batch of sequences that start together: the prompts in one step (in a few, sequence by sequence, where they
+    hold more than ``PROMPT_TOKENS_PER_STEP`` tokens), then one token each until
     every sequence has met a stop token or has ``max_new_tokens`` new tokens.  ``engine`` needs ``begin``,
     ``step``, ``release`` and ``device``.  ``first_positions``: the position of each prompt's first token where
     that is not 0 (the reference's ``position_ids``, fms/utils/generation.py:122-132)."""
@@ -136,7 +155,9 @@ def generate_batch(engine, sampler: Sampler, prompts: Sequence[Sequence[int]], r
             if it > 0 and hasattr(engine, "decode"):
                 logits = engine.decode([slots[i] for i in live], [f[0] for f in feed], horizon=horizon)
             else:
-                logits = engine.step([slots[i] for i in live], feed)
+                groups = prompt_groups([len(f) for f in feed], PROMPT_TOKENS_PER_STEP)
+                parts = [engine.step([slots[live[i]] for i in g], [feed[i] for i in g]) for g in groups]
+                logits = parts[0] if len(parts) == 1 else torch.cat(parts)
             if req_of != live:  # the request numbers of the live sequences, on the device (sampling draws by them)
                 req = torch.tensor([requests[i] for i in live], dtype=torch.int32).to(engine.device)
                 req_of = list(live)

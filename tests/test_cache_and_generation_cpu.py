@@ -217,6 +217,25 @@ def test_generate_runs_batches_one_after_another_and_keeps_the_order(greedy_on_c
     assert rect.tolist() == [[3, 4, 5, 6, 7], [5, 6, 7, 0, 0]]
 
 
+def test_prompts_of_many_tokens_run_a_few_sequences_at_a_time(greedy_on_cpu, monkeypatch):
+    """A batch's prompts go through one step up to a number of tokens; beyond it, consecutive sequences are packed
+    into steps of at most that many (a longer prompt alone), and the tokens are the same."""
+    from fms_b200.engine import generation
+    from fms_b200.utils.generation import generate
+
+    assert generation.prompt_groups([5, 5, 5], 100) == [[0, 1, 2]]
+    assert generation.prompt_groups([5, 5, 5], 10) == [[0, 1], [2]]
+    assert generation.prompt_groups([50, 5, 5, 7], 10) == [[0], [1, 2], [3]]
+    prompts = [[1] * 6, [2] * 3, [3] * 3, [4] * 9, [5]]
+    whole = generate(CountingEngine(max_slots=5), prompts, max_new_tokens=3, do_sample=False)
+    monkeypatch.setattr(generation, "PROMPT_TOKENS_PER_STEP", 8)
+    e = CountingEngine(max_slots=5)
+    cut = generate(e, prompts, max_new_tokens=3, do_sample=False)
+    assert [o.tolist() for o in cut] == [o.tolist() for o in whole]
+    assert [s[2] for s in e.steps if s[0] == "step"] == [[6], [3, 3], [9], [1]]
+    assert [s[:2] for s in e.steps if s[0] == "decode"] == [("decode", 5)] * 2
+
+
 def test_generate_argument_checks_and_release_on_error(greedy_on_cpu):
     from fms_b200.utils.generation import generate
 

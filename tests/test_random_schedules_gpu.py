@@ -135,7 +135,7 @@ def test_a_random_schedule_with_windows_on_some_layers(tiny_folders, oracles, se
 
 
 @pytest.mark.parametrize("seed", range(4))
-def test_random_requests_through_generate_with_stop_tokens_and_small_batches(models, oracles, seed):
+def test_random_requests_through_generate_with_stop_tokens_and_small_batches(models, oracles, seed, monkeypatch):
     """More requests than a batch holds, of unequal lengths, greedy; two stop tokens chosen so that some requests
     end early (the tokens that the plain implementation emits third for one request and sixth for another).  Each
     request's tokens equal the plain loop's, whatever batch it fell into."""
@@ -156,6 +156,12 @@ def test_random_requests_through_generate_with_stop_tokens_and_small_batches(mod
         out = generate(model, [torch.tensor(p) for p in prompts], max_new_tokens=10, do_sample=False, eos_token_id=stop,
                        batch_size=batch_size)
         assert [o.tolist() for o in out] == want
+    # the prompts of a batch in several steps, a few sequences at a time: the same tokens
+    from fms_b200.engine import generation
+
+    monkeypatch.setattr(generation, "PROMPT_TOKENS_PER_STEP", 60)
+    out = generate(model, [torch.tensor(p) for p in prompts], max_new_tokens=10, do_sample=False, eos_token_id=stop)
+    assert [o.tolist() for o in out] == want
     engine = model.engine()
     assert engine.cache.slots.n_held == 0
 
