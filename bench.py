@@ -11,7 +11,7 @@ pinned host-to-device copy of every step's tokens and a device-to-host read of e
 timed region), again the median of 5 regions of K steps.  ``prefill``: one prompt of 2,048 tokens.
 ``roofline``: the bytes a decode step has to read (every weight it uses once, and the cache of the live
 requests) over its time, against the measured copy bandwidth.  ``points``: tokens a second of decode at batch
-1, 16, 32 and 64, of a batch of 64 of which one sequence ends every third step (down to 16; by the clock, host
+1, 16, 32, 64 and 128, of a batch of 64 of which one sequence ends every third step (down to 16; by the clock, host
 tokens in, the live set changing under the captured graphs), of decode at batch 8 with 7,000 to 8,000 cached tokens a request, of prefills of 512 and 8,192
 tokens, and of the benchmark's further configurations (decode at batch 8 and a prefill of 2,048 tokens for the
 Llama-2-7B and Llama-2-13B shapes, decode at batch 8 in float32); ``points_frac``: each point's fraction of its
@@ -374,7 +374,7 @@ def run_ours(args):
     nlayers = args.layers or MODEL["nlayers"]
     room = max(3, args.warmup) + REGIONS * args.steps + 8
     long_context = args.points != "main" and not args.only and MODEL["context"] >= 8192
-    slots = max(64, int(args.only.split("_b")[1])) if args.only.startswith("decode_b") else 64
+    slots = max(64, int(args.only.split("_b")[1])) if args.only.startswith("decode_b") else (128 if dtype == "bf16" else 64)
     run = Measured(MODEL, dtype, nlayers, room, PROMPT_MAX, slots=slots,
                    long_requests=(64 if args.points == "long" else 8) if long_context else 0)
 
@@ -404,7 +404,7 @@ def run_ours(args):
         points[name], fracs[name] = round(tokens / (ms / 1e3), 1), round(r.prefill_frac(ms, tokens, pk), 4)
 
     side = max(32, args.steps // 2)
-    for b in (1, 16, 32, 64):
+    for b in (1, 16, 32, 64) + ((128,) if slots >= 128 else ()):
         decode_point(f"decode_b{b}", run, b, side)
     points["decode_b64_ending_one_by_one"] = round(run.ending_decode(), 1)
     pf_ms = run.prefill(PREFILL_TOKENS)

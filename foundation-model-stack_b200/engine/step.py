@@ -75,11 +75,13 @@ class Engine:
     """A model's decoder together with a cache of a given size."""
 
     def __init__(self, model, max_tokens: int, max_slots: Optional[int] = None, sampling: bool = True,
-                 use_graphs: bool = True, max_graphs: int = 16) -> None:
+                 use_graphs: bool = True, max_graphs: int = 48) -> None:
         """``max_graphs``: the most captured decode steps the engine keeps (one per number of sequences and bound on
         their lengths).  When one more is captured, the one used longest ago is dropped with its logits buffer, and
         all captures draw their buffers from one pool; so a batch whose requests end one by one holds at most
-        ``max_graphs`` logits buffers [sequences, vocabulary] and one set of a step's intermediate buffers."""
+        ``max_graphs`` logits buffers [sequences, vocabulary] and one set of a step's intermediate buffers.  The
+        default holds what an engine meets that serves every size (some 14 numbers of rows up to 128, each with the
+        few bounds its lengths pass through) without capturing anything twice."""
         if model.decoder is None:
             raise ValueError("the model has no weights yet")
         self.model = model
