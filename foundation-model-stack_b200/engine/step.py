@@ -76,8 +76,8 @@ class Engine:
 
     def __init__(self, model, max_tokens: int, max_slots: Optional[int] = None, sampling: bool = True,
                  use_graphs: bool = True, max_graphs: int = 48) -> None:
-        """``max_graphs``: the most captured decode steps the engine keeps (one per number of sequences and bound on
-        their lengths).  When one more is captured, the one used longest ago is dropped with its logits buffer, and
+        """``max_graphs``: the most captured decode steps the engine keeps (one per number of rows, see
+        ``decode_rows``, and bound on the sequences' lengths).  When one more is captured, the one used longest ago is dropped with its logits buffer, and
         all captures draw their buffers from one pool; so a batch whose requests end one by one holds at most
         ``max_graphs`` logits buffers [sequences, vocabulary] and one set of a step's intermediate buffers.  The
         default holds what an engine meets that serves every size (some 14 numbers of rows up to 128, each with the
@@ -100,7 +100,7 @@ class Engine:
         self.fill_rows = self.use_graphs
         self.max_graphs = max(1, int(max_graphs))
         self._decode: Dict[int, _DecodeBuffers] = {}
-        # (sequences, bound on their lengths, with position offsets) -> (graph, logits), least recently used first
+        # (rows, bound on the lengths, with position offsets) -> (graph, logits), least recently used first
         self._graphs: "collections.OrderedDict[tuple, Tuple[object, torch.Tensor]]" = collections.OrderedDict()
         self._graph_pool = None
         self.graphs_captured = 0
