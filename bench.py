@@ -374,7 +374,11 @@ def run_ours(args):
     nlayers = args.layers or MODEL["nlayers"]
     room = max(3, args.warmup) + REGIONS * args.steps + 8
     long_context = args.points != "main" and not args.only and MODEL["context"] >= 8192
-    slots = max(64, int(args.only.split("_b")[1])) if args.only.startswith("decode_b") else (128 if dtype == "bf16" else 64)
+    # 128 slots (for the point at batch 128) where their cache stays well inside the memory: the 8B shape in bfloat16
+    # holds 128 KB a token, the shapes with as many kv heads as heads four times that
+    token_bytes = 2 * nlayers * MODEL["kvheads"] * MODEL["head_dim"] * (2 if dtype == "bf16" else 4)
+    roomy = 128 * (PROMPT_MAX + 2 * room + 128) * token_bytes < 60e9
+    slots = max(64, int(args.only.split("_b")[1])) if args.only.startswith("decode_b") else (128 if roomy else 64)
     run = Measured(MODEL, dtype, nlayers, room, PROMPT_MAX, slots=slots,
                    long_requests=(64 if args.points == "long" else 8) if long_context else 0)
 
