@@ -448,6 +448,19 @@ int multiprocessors() {
 }
 #endif
 
+// (sequence, kv head) pairs up to which decode attention takes pieces of 32 keys on 8 warps a split
+// (FMS_B200_ATTN_PIECES: another number; 0: never).  Measured in the decode step of the 8B sizes (8 kv heads,
+// contexts of 128 to 2,048), 8 warps against 4: one sequence 3.145 against 3.229 ms, two 3.262 / 3.355, four 3.296 /
+// 3.425, six 3.340 / 3.415, eight 3.591 / 3.500: with 64 pairs the blocks of 256 threads no longer all fit at once.
+static int decode_pieces_up_to() {
+  static int n = -1;
+  if (n < 0) {
+    const char* e = getenv("FMS_B200_ATTN_PIECES");
+    n = e ? atoi(e) : 48;
+  }
+  return n;
+}
+
 int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, int n_splits, float* part_o,
                   float* part_ml, int pool_blocks, long total_len, int* work_counter, int* error_flag, cudaStream_t stream) {
   if (n_splits <= 0 || n_splits > 65535) return fms_fail("%s: %d splits", what, n_splits);
@@ -491,11 +504,16 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
       return fms_launch_status(what);
     }
 #endif
-    const int nw = units >= 512 ? 1 : (units >= 192 ? 2 : 4);
-    const size_t smem = (size_t)nw * BLK * ROWB;
-    auto kernel = nw == 1 ? attn_decode_mma_kernel<1> : (nw == 2 ? attn_decode_mma_kernel<2> : attn_decode_mma_kernel<4>);
-    static bool configured[3] = {false, false, false};
-    const int slot = nw == 1 ? 0 : (nw == 2 ? 1 : 2);
+    // Very few (up to six sequences of 8 kv heads): eight warps share a split, each with one piece of 32 keys: the
+    // shortest chain a block can have, while all blocks still fit on the GPU at once.
+    const int nw = units >= 512 ? 1 : (units >= 192 ? 2 : (units <= decode_pieces_up_to() ? 8 : 4));
+    const int wk = nw == 8 ? 32 : BLK;
+    const size_t smem = (size_t)nw * wk * ROWB;
+    auto kernel = nw == 1 ? attn_decode_mma_kernel<1, BLK>
+                          : (nw == 2 ? attn_decode_mma_kernel<2, BLK>
+                                     : (nw == 4 ? attn_decode_mma_kernel<4, BLK> : attn_decode_mma_kernel<8, 32>));
+    static bool configured[4] = {false, false, false, false};
+    const int slot = nw == 1 ? 0 : (nw == 2 ? 1 : (nw == 4 ? 2 : 3));
     if (!configured[slot]) {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return fms_fail("%s: %zu bytes of shared memory refused: %s", what, smem, cudaGetErrorString(e));
@@ -503,7 +521,7 @@ int launch_decode(const char* what, const AttnArgs& a, int dtype, int n_seqs, in
     }
     // the early L2 hints pay only while the GPU is not full of key and value traffic anyway
     fms_launch(kernel, dim3(n_seqs, a.kvheads * chunks, n_splits), dim3(nw * 32), smem, stream, a, part_o, part_ml,
-               n_splits, nw == 4 ? pool_blocks : 0);
+               n_splits, nw >= 4 ? pool_blocks : 0);
     if (n_splits > 1)  // with one split the kernel above has written the result itself
       fms_launch(attn_combine_kernel<__nv_bfloat16>, dim3(n_seqs, a.nheads), dim3(HD), 0, stream, a,
                  (const float*)part_o, (const float*)part_ml, n_splits, (int*)nullptr, error_flag);

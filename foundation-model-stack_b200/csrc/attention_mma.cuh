@@ -76,11 +76,11 @@ __device__ __forceinline__ void prefetch_l2(const void* gmem, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(gmem), "r"(bytes) : "memory");
 }
 
-// A warp copies the 64 rows of one cache block (keys or values of one kv head) into its padded buffer.  Rows
-// outside [lo, hi) of the sequence are filled with zeros instead of being read.
+// A warp copies the 64 rows of one cache block (keys or values of one kv head), or the first `rows` of them, into
+// its padded buffer.  Rows outside [lo, hi) of the sequence are filled with zeros instead of being read.
 __device__ __forceinline__ void copy_block_async(unsigned char* dst, const __nv_bfloat16* src, int first_pos, int lo,
-                                                 int hi, int lane) {
-  for (int p = lane; p < BLK * PIECES; p += 32) {
+                                                 int hi, int lane, int rows = BLK) {
+  for (int p = lane; p < rows * PIECES; p += 32) {
     const int row = p / PIECES, piece = p - row * PIECES;
     const int pos = first_pos + row;
     cp_async_16(dst + row * ROWB + piece * 16, src + (size_t)row * HD + piece * 8, pos >= lo && pos < hi);
@@ -98,7 +98,9 @@ __device__ __forceinline__ void copy_block_async(unsigned char* dst, const __nv_
 //                                                          taken and read transposed (ldmatrix.trans); B = the
 //                                                          probabilities, turned from accumulator to operand
 //                                                          layout by movmatrix
-// Warp w takes the 64-key blocks w, w + NW, ... of the split, each warp with a running softmax of its own; the
+// Warp w takes the pieces of WK keys w, w + NW, ... of the split (WK = 64: a cache block; WK = 32: half of one, with
+// 8 warps a split of 256 keys is then one piece a warp, all of a warp's keys are on their way at once and nothing
+// is rescaled: the shortest chain, for launches of few blocks), each warp with a running softmax of its own; the
 // warps' results are merged in shared memory and written as one unnormalised partial result (m, l, o) per head,
 // which attn_combine_kernel merges over splits.
 // ---------------------------------------------------------------------------------------------------
@@ -110,8 +112,8 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
   return y;
 }
 
-template <int NW>
-__global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
+template <int NW, int WK>
+__global__ void __launch_bounds__(NW * 32, WK == 32 ? 16 / NW : 12 / NW)
     attn_decode_mma_kernel(AttnArgs a, float* __restrict__ part_o, float* __restrict__ part_ml, int n_splits,
                            int pool_blocks) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -130,12 +132,12 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
     const int start0 = a.window > 0 ? max(0, len0 - a.window) : 0;
     const int lo0 = max(start0, split * SPLIT), hi0 = min(len0, (split + 1) * SPLIT);
     if (slot0 >= 0) {
-      for (int kb = lo0 / BLK + warp; kb * BLK < hi0 && kb < a.table_stride; kb += NW) {
-        const int blk = __ldcg(a.table + (size_t)slot0 * a.table_stride + kb);
+      for (int piece = lo0 / WK + warp; piece * WK < hi0 && piece * WK / BLK < a.table_stride; piece += NW) {
+        const int blk = __ldcg(a.table + (size_t)slot0 * a.table_stride + piece * WK / BLK);
         if (blk < 0 || blk >= pool_blocks) continue;
-        const size_t at = ((size_t)blk * a.kvheads + kvh) * BLK * HD;
-        prefetch_l2((const __nv_bfloat16*)a.keys + at, BLK * HD * 2);
-        prefetch_l2((const __nv_bfloat16*)a.values + at, BLK * HD * 2);
+        const size_t at = (((size_t)blk * a.kvheads + kvh) * BLK + piece * WK % BLK) * HD;
+        prefetch_l2((const __nv_bfloat16*)a.keys + at, WK * HD * 2);
+        prefetch_l2((const __nv_bfloat16*)a.values + at, WK * HD * 2);
       }
     }
   }
@@ -154,7 +156,7 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
                            (size_t)(kvh * group + g0) * HD;
   const __nv_bfloat16* kc = (const __nv_bfloat16*)a.keys;
   const __nv_bfloat16* vc = (const __nv_bfloat16*)a.values;
-  unsigned char* vbuf = smem_raw + (size_t)warp * BLK * ROWB;  // one buffer of values per warp
+  unsigned char* vbuf = smem_raw + (size_t)warp * WK * ROWB;  // one buffer of values per warp
 
   // A lane's part of the k index: of every 32 values of a row it holds the 8 from 8 c on (k-steps 2 s and
   // 2 s + 1 take two pairs each); of a last 16 alone, the instruction's own pairs 2 c and 2 c + 8.
@@ -182,13 +184,16 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
   const float scale2 = a.scale * LOG2E;  // scores are kept times log2(e): exp(x) = exp2(x log2 e)
 
   bool first_block = true;
-  for (int kb = k_lo / BLK + warp; kb * BLK < k_hi; kb += NW) {
-    const int blk = block_of(a, slot, kb);
+  constexpr int WT = WK / 16;  // mma tiles of 16 keys a piece
+  for (int piece = k_lo / WK + warp; piece * WK < k_hi; piece += NW) {
+    const int first = piece * WK;  // position of the piece's first key
+    const int blk = block_of(a, slot, first / BLK);
     if (blk < 0) continue;
-    const __nv_bfloat16* ksrc = kc + ((size_t)blk * a.kvheads + kvh) * BLK * HD;
-    __syncwarp();  // the buffer is free: every lane is past the previous block
-    const bool whole = kb * BLK >= k_lo && kb * BLK + BLK <= k_hi;  // every key of the block counts: no masks
-    const __nv_bfloat16* vsrc = vc + ((size_t)blk * a.kvheads + kvh) * BLK * HD;
+    const size_t at = (((size_t)blk * a.kvheads + kvh) * BLK + first % BLK) * HD;
+    const __nv_bfloat16* ksrc = kc + at;
+    __syncwarp();  // the buffer is free: every lane is past the previous piece
+    const bool whole = first >= k_lo && first + WK <= k_hi;  // every key of the piece counts: no masks
+    const __nv_bfloat16* vsrc = vc + at;
     if (whole) {  // a lane copies piece (lane % PIECES) of the rows (lane / PIECES) + i (32 / PIECES): constant offsets
       if (32 % PIECES == 0) {  // the lanes of a warp cover whole rows
         constexpr int RSTEP = 32 % PIECES == 0 ? 32 / PIECES : 1;
@@ -196,17 +201,17 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
         unsigned char* dst = vbuf + row0 * ROWB + part * 16;
         const __nv_bfloat16* src = vsrc + (size_t)row0 * HD + part * 8;
 #pragma unroll
-        for (int i = 0; i < BLK / RSTEP; ++i) cp_async_16(dst + i * RSTEP * ROWB, src + (size_t)i * RSTEP * HD, true);
+        for (int i = 0; i < WK / RSTEP; ++i) cp_async_16(dst + i * RSTEP * ROWB, src + (size_t)i * RSTEP * HD, true);
       } else {
-        copy_block_async(vbuf, vsrc, kb * BLK, k_lo, k_hi, lane);
+        copy_block_async(vbuf, vsrc, first, k_lo, k_hi, lane, WK);
       }
     } else {
-      copy_block_async(vbuf, vsrc, kb * BLK, k_lo, k_hi, lane);
+      copy_block_async(vbuf, vsrc, first, k_lo, k_hi, lane, WK);
     }
     cp_async_commit_group();
     // scores, 16 keys at a time: element e of tile t is (key 16 t + g + 8 (e / 2), head 2 c + (e % 2)).  Rows of
     // the block beyond the sequence are read too (they exist) and masked below.
-    float st[4][4];
+    float st[WT][4];
     uint4 ka[2][G32 > 0 ? G32 : 1][2];
     uint32_t kt[2][2][2];
     auto load_keys = [&](int t) {
@@ -226,8 +231,8 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
     };
     load_keys(0);
 #pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      if (t + 1 < 4) load_keys(t + 1);
+    for (int t = 0; t < WT; ++t) {
+      if (t + 1 < WT) load_keys(t + 1);
       st[t][0] = st[t][1] = st[t][2] = st[t][3] = 0.f;
 #pragma unroll
       for (int s = 0; s < G32; ++s) {
@@ -244,16 +249,16 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
     // raw scores; the scale (positive) goes into the exponent's multiply-add
     if (!whole) {
 #pragma unroll
-      for (int t = 0; t < 4; ++t)
+      for (int t = 0; t < WT; ++t)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int kpos = kb * BLK + 16 * t + g + 8 * (e >> 1);
+          const int kpos = first + 16 * t + g + 8 * (e >> 1);
           if (kpos < k_lo || kpos >= k_hi) st[t][e] = -INFINITY;
         }
     }
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int t = 0; t < 4; ++t)
+    for (int t = 0; t < WT; ++t)
 #pragma unroll
       for (int e = 0; e < 4; ++e) tile_max[e & 1] = fmaxf(tile_max[e & 1], st[t][e]);
     float alpha[2], psum[2] = {0.f, 0.f}, neg_m[2];
@@ -267,9 +272,9 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
       alpha[h] = ex2_approx(m[h] + neg_m[h]);  // 2^-inf = 0 while nothing has been seen
       m[h] = m_new;
     }
-    uint32_t pb[4][2];  // P^T as B operand of k-step t (keys 16 t ..): (keys 2 c, 2 c + 1 (+ 8); head g)
+    uint32_t pb[WT][2];  // P^T as B operand of k-step t (keys 16 t ..): (keys 2 c, 2 c + 1 (+ 8); head g)
 #pragma unroll
-    for (int t = 0; t < 4; ++t) {
+    for (int t = 0; t < WT; ++t) {
       float p[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -298,7 +303,7 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
     // V^T tiles of 16 values x 16 keys: matrix (lane >> 3) of the four is (values + 8 ((lane >> 3) & 1),
     // keys + 8 (lane >> 4)), its rows in shared memory are keys
 #pragma unroll
-    for (int t = 0; t < 4; ++t) {
+    for (int t = 0; t < WT; ++t) {
       const unsigned char* vrow = vbuf + (16 * t + (lane & 7) + (lane >> 4) * 8) * ROWB + ((lane >> 3) & 1) * 16;
 #pragma unroll
       for (int j = 0; j < HD / 16; ++j) {
@@ -332,11 +337,11 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
     float mm = -INFINITY;
 #pragma unroll
     for (int w = 0; w < NW; ++w)
-      mm = fmaxf(mm, (reinterpret_cast<const float*>(smem_raw + (size_t)w * BLK * ROWB) + GROWS * HD)[2 * r]);
+      mm = fmaxf(mm, (reinterpret_cast<const float*>(smem_raw + (size_t)w * WK * ROWB) + GROWS * HD)[2 * r]);
     float f[NW], lsum = 0.f;
 #pragma unroll
     for (int w = 0; w < NW; ++w) {
-      const float* wm = reinterpret_cast<const float*>(smem_raw + (size_t)w * BLK * ROWB) + GROWS * HD;
+      const float* wm = reinterpret_cast<const float*>(smem_raw + (size_t)w * WK * ROWB) + GROWS * HD;
       f[w] = wm[2 * r] == -INFINITY ? 0.f : ex2_approx(wm[2 * r] - mm);
       lsum += wm[2 * r + 1] * f[w];
     }
@@ -349,7 +354,7 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
         float sum = 0.f;
 #pragma unroll
         for (int w = 0; w < NW; ++w)
-          sum += reinterpret_cast<const float*>(smem_raw + (size_t)w * BLK * ROWB)[r * HD + d] * f[w];
+          sum += reinterpret_cast<const float*>(smem_raw + (size_t)w * WK * ROWB)[r * HD + d] * f[w];
         out[d] = __float2bfloat16_rn(sum * inv);
       }
     } else {
@@ -357,7 +362,7 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : (NW == 2 ? 6 : 12))
         float sum = 0.f;
 #pragma unroll
         for (int w = 0; w < NW; ++w)
-          sum += reinterpret_cast<const float*>(smem_raw + (size_t)w * BLK * ROWB)[r * HD + d] * f[w];
+          sum += reinterpret_cast<const float*>(smem_raw + (size_t)w * WK * ROWB)[r * HD + d] * f[w];
         if (FMS_IN(at, (size_t)gridDim.x * a.nheads * n_splits)) part_o[at * HD + d] = sum;
       }
       if (tid % TPH == 0 && FMS_IN(at, (size_t)gridDim.x * a.nheads * n_splits)) {
