@@ -256,7 +256,10 @@ class Engine:
         sequence will get, as ``decode`` takes it (graphs are kept per bound on the lengths, a power of two of 256)."""
         if not self.use_graphs:
             return
-        for n in sorted(set(decode_rows(int(k)) for k in sizes)):
+        by_rows = {}
+        for k in sorted(int(k) for k in sizes):
+            by_rows.setdefault(decode_rows(k) if self.fill_rows else k, k)  # one number of sequences for each size of step
+        for n in by_rows.values():
             if n > self.cache.slots.n_free:
                 raise ValueError(f"warm_up: {n} sequences, {self.cache.slots.n_free} slots free")
             slots = self.begin(n)

@@ -337,7 +337,7 @@ def test_a_batch_whose_requests_end_one_by_one_keeps_few_graphs(models, oracles)
 def test_warm_up_captures_the_graphs_before_the_first_request(models, oracles):
     model = models("b", "fp32")
     engine = model.new_engine(max_tokens=64 * 2 * 12, max_slots=12)
-    engine.warm_up([1, 3, 10], horizon=100)
+    engine.warm_up([1, 3, 10, 11], horizon=100)  # ten and eleven sequences are both steps of twelve rows
     assert engine.graphs_captured == 3 and engine.cache.slots.n_held == 0 and sorted(engine._decode) == [1, 3, 12]
     assert all(g.pool.n_held == 0 for g in engine.cache.groups)
     reqs = long_requests("b", 3)
