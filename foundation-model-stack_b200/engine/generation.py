@@ -184,6 +184,23 @@ def generate_batch(engine, sampler: Sampler, prompts: Sequence[Sequence[int]], r
     return outputs
 
 
+def _cache_tokens_that_fit(model) -> Optional[int]:
+    """Tokens of cache that four fifths of the device's free memory (and of what the model's own engine holds already)
+    have room for; None where that cannot be told (no CUDA device, a model without the figures)."""
+    try:
+        device = torch.device(model.device)
+        per_token = model.cache_bytes_per_token()
+        if device.type != "cuda" or per_token <= 0:
+            return None
+        free, _ = torch.cuda.mem_get_info(device)
+        held = getattr(model, "_engine", None)
+        if held is not None:
+            free += held.cache.n_blocks * 64 * per_token
+        return max(64, int(0.8 * free / per_token) // 64 * 64)
+    except Exception:
+        return None
+
+
 def generate(model, input_ids: Prompts, max_seq_len: int = 4096, max_new_tokens: int = 256,
              temperature: float = 1.0, top_k: int = 10, do_sample: bool = True, num_beams: int = 1,
              use_cache: bool = True, contiguous_cache: bool = False,
@@ -250,7 +267,14 @@ def generate(model, input_ids: Prompts, max_seq_len: int = 4096, max_new_tokens:
     else:
         longest = max(len(p) for p in prompts) + max_new_tokens
         want = cache_tokens or sum((len(p) + max_new_tokens + 63) // 64 * 64 for p in prompts[: batch_size or len(prompts)])
-        engine = model.engine(min_tokens=max(want, (longest + 63) // 64 * 64), min_slots=min(len(prompts), batch_size or len(prompts)))
+        slots = min(len(prompts), batch_size or len(prompts))
+        if not cache_tokens:
+            # no more than the device has room for: requests beyond it wait for the next batch
+            fits = _cache_tokens_that_fit(model)
+            if fits is not None and want > fits:
+                slots = max(1, min(slots, int(slots * fits / want)))
+                want = fits
+        engine = model.engine(min_tokens=max(want, (longest + 63) // 64 * 64), min_slots=slots)
     cache = getattr(engine, "cache", None)
     capacity = cache.n_blocks * 64 if cache is not None else 1 << 60
     max_slots = cache.max_slots if cache is not None else len(prompts)

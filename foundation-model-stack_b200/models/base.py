@@ -62,6 +62,15 @@ class Model:
 
         return Engine(self, max_tokens=max_tokens, max_slots=max_slots, sampling=sampling, **engine_options)
 
+    def cache_bytes_per_token(self) -> int:
+        """Bytes of cache that one token of one sequence takes over all layers (keys and values of every layer whose
+        mixer keeps them; a windowed layer counts like any other: every group of the cache is given the same number of
+        blocks)."""
+        from ..cache.requests import KVRequest
+
+        itemsize = 4 if self.dtype == torch.float32 else 2
+        return sum(2 * r.kvheads * r.head_dim * itemsize for r in self.decoder.cache_requests() if isinstance(r, KVRequest))
+
     def engine(self, min_tokens: int = 0, min_slots: int = 0):
         """The model's own engine, made on first use and made anew when it is too small."""
         e = self._engine

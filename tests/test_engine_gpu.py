@@ -334,6 +334,26 @@ def test_a_batch_whose_requests_end_one_by_one_keeps_few_graphs(models, oracles)
     engine.check()
 
 
+def test_generate_asks_for_no_more_cache_than_the_device_has_room_for(tiny_folders, oracles, monkeypatch):
+    """Twelve requests whose cache would take twelve blocks, on a device that (the test says) has room for five: the
+    model's own engine is made for what fits, the requests run in several batches, and the tokens are the plain loop's."""
+    from fms_b200.models import get_model
+    from fms_b200.utils.generation import generate
+
+    model = get_model("hf_pretrained", model_path=tiny_folders["b"], device_type="cuda", data_type="fp32")
+    per_token = model.cache_bytes_per_token()
+    cfg = TINY["b"][0]
+    assert per_token == 2 * cfg["num_hidden_layers"] * cfg["num_key_value_heads"] * (cfg["hidden_size"] // cfg["num_attention_heads"]) * 4
+    monkeypatch.setattr(torch.cuda, "mem_get_info", lambda device=None: (int(5 * 64 * per_token / 0.8) + 1, 1 << 40))
+    g = torch.Generator().manual_seed(31)
+    prompts = [torch.randint(0, cfg["vocab_size"], (int(k),), generator=g).tolist() for k in torch.randint(1, 50, (12,), generator=g)]
+    out = generate(model, [torch.tensor(p) for p in prompts], max_new_tokens=5, do_sample=False)
+    engine = model.engine()
+    assert engine.cache.n_blocks == 5 and engine.cache.max_slots <= 5 and engine.cache.slots.n_held == 0
+    for o, p in zip(out, prompts):
+        assert o.tolist() == pl.plain_generate(oracles["b"], p, 5)
+
+
 def test_warm_up_captures_the_graphs_before_the_first_request(models, oracles):
     model = models("b", "fp32")
     engine = model.new_engine(max_tokens=64 * 2 * 12, max_slots=12)
